@@ -1,0 +1,68 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions, launch checks.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define VOB_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes of the C entry points
+#define VOB_F32 0
+#define VOB_BF16 1
+
+// bits of the device-side error word (a kernel that meets a bad index skips the access and sets a bit)
+#define VOB_ERR_TOKEN_ID 1
+#define VOB_ERR_POSITION 2
+#define VOB_ERR_SLOT 4
+#define VOB_ERR_PAGE 8
+#define VOB_ERR_ROW 16
+
+// host-side status codes (beyond cudaError values, which are < 1000)
+#define VOB_BAD_ARGUMENT 2001
+#define VOB_UNSUPPORTED 2002
+
+namespace vob {
+
+template <typename T> __device__ __forceinline__ float to_f(T x);
+template <> __device__ __forceinline__ float to_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// x rounded to the storage type and back: identity for float.
+template <typename T> __device__ __forceinline__ float round_to(float x) { return to_f<T>(from_f<T>(x)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of NT threads (NT a multiple of 32, at most 1024); every thread gets the result.
+// The order of additions depends on NT only.
+template <int NT>
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floats */) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < NT / 32; ++i) t += scratch[i];
+  return t;
+}
+
+inline int launch_status() {
+  cudaError_t e = cudaGetLastError();
+  return static_cast<int>(e);
+}
+
+}  // namespace vob

@@ -1,0 +1,269 @@
+// Row-wise kernels of the forward pass: embedding gather, residual add + RMSNorm,
+// bias + per-head RMSNorm + rotation + paged key/value write, SiLU(gate) * up.
+//
+// Every kernel is a template over the storage type (float for the true 32-bit path,
+// bfloat16 for serving).  Sums, norms and rotation are computed in float in both; with
+// bfloat16 the values are rounded exactly where the reference rounds them
+// (vllm-oxide, crates/vllm-oxide/src/layers/rmsnorm.rs:51-81, layers/rope.rs:129-159,
+// layers/activation.rs:17-21).  The order of additions in a row's reduction depends only
+// on the row's width, never on what else is in the batch.
+#include "common.cuh"
+
+namespace vob {
+
+// ---------------------------------------------------------------- embedding gather
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, T* __restrict__ out,
+                                 int H, int V, int* err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  if (id < 0 || id >= V) {
+    if (threadIdx.x == 0) atomicOr(err, VOB_ERR_TOKEN_ID);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)t * H + i] = from_f<T>(0.f);
+    return;
+  }
+  const T* src = table + (size_t)id * H;
+  T* dst = out + (size_t)t * H;
+  if ((H * sizeof(T)) % 16 == 0) {
+    const int4* s4 = reinterpret_cast<const int4*>(src);
+    int4* d4 = reinterpret_cast<int4*>(dst);
+    const int n = H * sizeof(T) / 16;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) d4[i] = s4[i];
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+// ---------------------------------------------------------------- residual add + RMSNorm
+// One block per output row.  s = x + residual in float; residual' = s rounded to T (written
+// in place unless a row list is given); y = round_T(s / sqrt(mean(s^2) + eps)) * w, the
+// product rounded to T once more.  With `rows`, output row r is computed from source row
+// rows[r] and the residual is left untouched (used for the last norm, on wanted rows only).
+template <typename T, int NT>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const float* __restrict__ w, T* __restrict__ y,
+                                   const int* __restrict__ rows, int H, int num_src_rows, float eps, int has_residual,
+                                   int* err) {
+  extern __shared__ float srow[];  // H floats
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  int src = r;
+  if (rows) {
+    src = rows[r];
+    if (src < 0 || src >= num_src_rows) {
+      if (threadIdx.x == 0) atomicOr(err, VOB_ERR_ROW);
+      return;
+    }
+  }
+  const T* xr = x + (size_t)src * H;
+  T* rr = residual + (size_t)src * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += NT) {
+    float s = to_f<T>(xr[i]);
+    if (has_residual) s += to_f<T>(rr[i]);
+    srow[i] = s;
+    ss += s * s;
+    if (!rows) rr[i] = from_f<T>(s);
+  }
+  const float total = block_sum<NT>(ss, scratch);
+  const float denom = sqrtf(total / (float)H + eps);
+  T* yr = y + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += NT) yr[i] = from_f<T>(round_to<T>(srow[i] / denom) * w[i]);
+}
+
+// ---------------------------------------------------------------- SiLU(gate) * up
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / I;
+    const int i = (int)(idx - t * I);
+    const float g = to_f<T>(gu[t * 2 * I + i]);
+    const float u = to_f<T>(gu[t * 2 * I + I + i]);
+    const float s = round_to<T>(g / (1.f + expf(-g)));
+    out[idx] = from_f<T>(s * u);
+  }
+}
+
+// ---------------------------------------------------------------- bias + head norm + rotation + cache write
+// One warp per (token, head) over the merged q|k|v row.  q heads are normalised and rotated in
+// place; k heads are normalised, rotated and written to the key cache at the token's slot; v
+// heads are copied to the value cache.  cos_sin is [max_pos, hd] float: cos of hd/2 angles, then
+// sin.  A slot of -1 writes nothing.
+template <typename T>
+__global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __restrict__ bias,
+                                             const int* __restrict__ positions, const int* __restrict__ slots,
+                                             const float* __restrict__ wq, const float* __restrict__ wk,
+                                             const float* __restrict__ cos_sin, T* __restrict__ kcache,
+                                             T* __restrict__ vcache, int nh, int kvh, int hd, float eps, int max_pos,
+                                             long num_slots, int write_kv, int* err) {
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  const int total_heads = nh + 2 * kvh;
+  if (head >= total_heads) return;
+  const int pos = positions[t];
+  const int slot = slots ? slots[t] : -1;
+  const int width = total_heads * hd;
+  T* row = qkv + (size_t)t * width + (size_t)head * hd;
+  const T* brow = bias ? bias + (size_t)head * hd : nullptr;
+  const bool is_q = head < nh, is_k = !is_q && head < nh + kvh;
+  if (!is_q && (!write_kv || slot < 0)) return;
+  if (!is_q && slot >= num_slots) {
+    if (lane == 0) atomicOr(err, VOB_ERR_SLOT);
+    return;
+  }
+  if (!is_q && !is_k) {  // value head: bias, then copy
+    T* dst = vcache + ((size_t)slot * kvh + (head - nh - kvh)) * hd;
+    for (int i = lane; i < hd; i += 32) {
+      float v = to_f<T>(row[i]);
+      if (brow) v = round_to<T>(v + to_f<T>(brow[i]));
+      dst[i] = from_f<T>(v);
+    }
+    return;
+  }
+  if (pos < 0 || pos >= max_pos) {
+    if (lane == 0) atomicOr(err, VOB_ERR_POSITION);
+    return;
+  }
+  const int half = hd >> 1;
+  const float* w = is_q ? wq : wk;
+  constexpr int MAXP = 8;  // pairs per lane: hd <= 512
+  float x1[MAXP], x2[MAXP];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXP; ++j) {
+    const int i = lane + 32 * j;
+    if (i < half) {
+      float a = to_f<T>(row[i]), b = to_f<T>(row[i + half]);
+      if (brow) { a = round_to<T>(a + to_f<T>(brow[i])); b = round_to<T>(b + to_f<T>(brow[i + half])); }
+      x1[j] = a; x2[j] = b;
+      ss += a * a + b * b;
+    }
+  }
+  if (w) {
+    ss = warp_sum(ss);
+    const float denom = sqrtf(ss / (float)hd + eps);
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j) {
+      const int i = lane + 32 * j;
+      if (i < half) {
+        x1[j] = round_to<T>(round_to<T>(x1[j] / denom) * w[i]);
+        x2[j] = round_to<T>(round_to<T>(x2[j] / denom) * w[i + half]);
+      }
+    }
+  }
+  const float* cs = cos_sin + (size_t)pos * hd;
+  T* dst = is_q ? row : kcache + ((size_t)slot * kvh + (head - nh)) * hd;
+#pragma unroll
+  for (int j = 0; j < MAXP; ++j) {
+    const int i = lane + 32 * j;
+    if (i < half) {
+      const float c = cs[i], s = cs[i + half];
+      dst[i] = from_f<T>(x1[j] * c - x2[j] * s);
+      dst[i + half] = from_f<T>(x2[j] * c + x1[j] * s);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- page copy (utility)
+template <typename T>
+__global__ void copy_pages_kernel(T* cache, const int* __restrict__ pairs, size_t page_elems) {
+  const int src = pairs[2 * blockIdx.x], dst = pairs[2 * blockIdx.x + 1];
+  for (size_t i = (size_t)blockIdx.y * blockDim.x + threadIdx.x; i < page_elems; i += (size_t)gridDim.y * blockDim.x)
+    cache[(size_t)dst * page_elems + i] = cache[(size_t)src * page_elems + i];
+}
+
+}  // namespace vob
+
+using namespace vob;
+
+VOB_API int vob_embedding(const void* table, const int* ids, void* out, int T, int H, int V, int dtype, int* err,
+                          cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (dtype == VOB_F32)
+    embedding_kernel<float><<<T, 128, 0, stream>>>((const float*)table, ids, (float*)out, H, V, err);
+  else if (dtype == VOB_BF16)
+    embedding_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>((const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, H, V, err);
+  else
+    return VOB_BAD_ARGUMENT;
+  return launch_status();
+}
+
+template <typename T>
+static int add_rmsnorm_launch(const void* x, void* residual, const float* w, void* y, const int* rows, int n_out, int H,
+                              int num_src_rows, float eps, int has_residual, int* err, cudaStream_t stream) {
+  constexpr int NT = 256;
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) return VOB_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  add_rmsnorm_kernel<T, NT><<<n_out, NT, smem, stream>>>((const T*)x, (T*)residual, w, (T*)y, rows, H, num_src_rows, eps,
+                                                         has_residual, err);
+  return launch_status();
+}
+
+// y[n_out, H]; x and residual [num_src_rows, H]; rows may be null (then n_out == num_src_rows).
+VOB_API int vob_add_rmsnorm(const void* x, void* residual, const float* w, void* y, const int* rows, int n_out, int H,
+                            int num_src_rows, float eps, int has_residual, int dtype, int* err, cudaStream_t stream) {
+  if (n_out <= 0) return 0;
+  if (H <= 0 || (has_residual && !residual)) return VOB_BAD_ARGUMENT;
+  if (!has_residual && !rows && !residual) return VOB_BAD_ARGUMENT;  // residual' = x is written there
+  if (dtype == VOB_F32) return add_rmsnorm_launch<float>(x, residual, w, y, rows, n_out, H, num_src_rows, eps, has_residual, err, stream);
+  if (dtype == VOB_BF16) return add_rmsnorm_launch<__nv_bfloat16>(x, residual, w, y, rows, n_out, H, num_src_rows, eps, has_residual, err, stream);
+  return VOB_BAD_ARGUMENT;
+}
+
+VOB_API int vob_silu_mul(const void* gu, void* out, int T, int I, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const size_t total = (size_t)T * I;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (dtype == VOB_F32)
+    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, I, total);
+  else if (dtype == VOB_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
+  else
+    return VOB_BAD_ARGUMENT;
+  return launch_status();
+}
+
+VOB_API int vob_qk_norm_rope_kv_write(void* qkv, const void* bias, const int* positions, const int* slots,
+                                      const float* wq, const float* wk, const float* cos_sin, void* kcache, void* vcache,
+                                      int T, int nh, int kvh, int hd, float eps, int max_pos, long num_slots,
+                                      int write_kv, int dtype, int* err, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (hd <= 0 || hd % 2 || hd > 512) return VOB_UNSUPPORTED;
+  if ((wq == nullptr) != (wk == nullptr)) return VOB_BAD_ARGUMENT;
+  const int warps = 4;
+  dim3 grid(T, (nh + 2 * kvh + warps - 1) / warps);
+  if (dtype == VOB_F32)
+    qk_norm_rope_kv_write_kernel<float><<<grid, warps * 32, 0, stream>>>(
+        (float*)qkv, (const float*)bias, positions, slots, wq, wk, cos_sin, (float*)kcache, (float*)vcache, nh, kvh, hd,
+        eps, max_pos, num_slots, write_kv, err);
+  else if (dtype == VOB_BF16)
+    qk_norm_rope_kv_write_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
+        (__nv_bfloat16*)qkv, (const __nv_bfloat16*)bias, positions, slots, wq, wk, cos_sin, (__nv_bfloat16*)kcache,
+        (__nv_bfloat16*)vcache, nh, kvh, hd, eps, max_pos, num_slots, write_kv, err);
+  else
+    return VOB_BAD_ARGUMENT;
+  return launch_status();
+}
+
+// pairs: [n_pairs][2] = (source page, destination page); one cache plane of page_elems elements per page.
+VOB_API int vob_copy_pages(void* cache, const int* pairs, int n_pairs, long page_elems, int dtype, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  dim3 grid(n_pairs, 8);
+  if (dtype == VOB_F32)
+    copy_pages_kernel<float><<<grid, 256, 0, stream>>>((float*)cache, pairs, (size_t)page_elems);
+  else if (dtype == VOB_BF16)
+    copy_pages_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((__nv_bfloat16*)cache, pairs, (size_t)page_elems);
+  else
+    return VOB_BAD_ARGUMENT;
+  return launch_status();
+}
+
+VOB_API const char* vob_error_string(int code) {
+  if (code == VOB_BAD_ARGUMENT) return "bad argument to a vllm_oxide_b200 kernel launcher";
+  if (code == VOB_UNSUPPORTED) return "size not supported by this vllm_oxide_b200 kernel";
+  return cudaGetErrorString((cudaError_t)code);
+}

@@ -1,0 +1,227 @@
+// Sampling on the device: one block per row of float logits, token id out.
+//
+// The pipeline is the reference's (vllm-oxide, crates/vllm-oxide/src/sampler.rs:207-261):
+// greedy short-circuit (temperature 0 or top_k 1) -> logits * (1/T) -> top-k (ties at the
+// threshold are kept, sampler.rs:349-364) -> top-p over the survivors -> Gumbel-max
+// argmax(x + g), g = -log(-log(u)).  Argmax ties go to the lowest index (sampler.rs:293-305).
+// Two things are this engine's own:
+//   * the uniform numbers come from a counter-based generator keyed per row (the caller
+//     derives the key from seed, request and step), so a request's tokens do not depend on
+//     what shares its batch (the reference draws all rows from one generator, sampler.rs:265-287);
+//   * top-p keeps every token whose logit is >= the logit of the boundary token, the first
+//     one in descending order at which the cumulative probability reaches p (the reference
+//     keeps a prefix of its sort, which is the same set unless equal logits straddle the
+//     boundary).  Probability mass is summed as 40-bit fixed point integers, so the set does
+//     not depend on the order of summation.
+#include "common.cuh"
+
+namespace vob {
+
+constexpr int SAMPLE_THREADS = 1024;
+
+__device__ __forceinline__ uint32_t ordered_key(float x) {
+  const uint32_t b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ unsigned long long pack_candidate(float value, int index) {
+  return ((unsigned long long)ordered_key(value) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)index);
+}
+
+__device__ __forceinline__ unsigned long long block_max_u64(unsigned long long v, unsigned long long* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = other > v ? other : v;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  unsigned long long r = 0;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) r = scratch[i] > r ? scratch[i] : r;
+  return r;
+}
+
+// uniform in (0,1), 24 bits, from (row key, token index)
+__device__ __forceinline__ float counter_uniform(unsigned long long key, uint32_t index) {
+  unsigned long long z = key + ((unsigned long long)index + 1ull) * 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z = z ^ (z >> 31);
+  return ((float)(uint32_t)(z >> 40) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+__device__ __forceinline__ unsigned long long fixed_mass(float x, float maxv) {
+  return (unsigned long long)(expf(x - maxv) * 1099511627776.0f);  // 2^40
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, long ld, int V, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const unsigned long long* __restrict__ keys, int* __restrict__ out) {
+  __shared__ unsigned long long scratch[32];
+  __shared__ unsigned int hist[256];
+  __shared__ unsigned long long mass[256];
+  __shared__ unsigned int s_prefix, s_remaining_k;
+  __shared__ unsigned long long s_remaining_mass;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const float* l = logits + (size_t)row * ld;
+  const float temp = temperature[row];
+  const int k = top_k[row];
+  const float p = top_p[row];
+
+  if (temp <= 0.f || k == 1) {  // greedy
+    unsigned long long best = 0;
+    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+      const unsigned long long c = pack_candidate(l[i], i);
+      best = c > best ? c : best;
+    }
+    best = block_max_u64(best, scratch);
+    if (tid == 0) out[row] = (int)(0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull));
+    return;
+  }
+  const float inv_t = 1.0f / temp;
+
+  // ---- top-k: key of the k-th largest scaled logit (0 keeps everything)
+  uint32_t thr = 0;
+  if (k >= 1 && k < V) {
+    if (tid == 0) { s_prefix = 0; s_remaining_k = (unsigned)k; }
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      if (tid < 256) hist[tid] = 0;
+      __syncthreads();
+      const uint32_t prefix = s_prefix;
+      const uint32_t mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+      for (int i = tid; i < V; i += SAMPLE_THREADS) {
+        const uint32_t key = ordered_key(l[i] * inv_t);
+        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned need = s_remaining_k, cum = 0;
+        int b = 255;
+        for (; b > 0; --b) {
+          if (cum + hist[b] >= need) break;
+          cum += hist[b];
+        }
+        s_remaining_k = need - cum;
+        s_prefix = prefix | ((uint32_t)b << shift);
+      }
+      __syncthreads();
+    }
+    thr = s_prefix;
+  }
+
+  // ---- maximum of the scaled logits (always a survivor)
+  unsigned long long best = 0;
+  for (int i = tid; i < V; i += SAMPLE_THREADS) {
+    const unsigned long long c = pack_candidate(l[i] * inv_t, i);
+    best = c > best ? c : best;
+  }
+  best = block_max_u64(best, scratch);
+  const int imax = (int)(0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull));
+  const float maxv = l[imax] * inv_t;
+
+  // ---- top-p over the survivors
+  if (p > 0.f && p < 1.f) {
+    unsigned long long z = 0;
+    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+      const float x = l[i] * inv_t;
+      if (ordered_key(x) >= thr) z += fixed_mass(x, maxv);
+    }
+    // integer sum over the block: any order gives the same total
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+    __syncthreads();
+    if ((tid & 31) == 0) scratch[tid >> 5] = z;
+    __syncthreads();
+    if (tid == 0) {
+      unsigned long long total = 0;
+      for (int i = 0; i < SAMPLE_THREADS / 32; ++i) total += scratch[i];
+      unsigned long long target = (unsigned long long)((double)p * (double)total);
+      if (target < 1) target = 1;
+      s_remaining_mass = target;
+      s_prefix = 0;
+    }
+    __syncthreads();
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      if (tid < 256) mass[tid] = 0;
+      __syncthreads();
+      const uint32_t prefix = s_prefix;
+      const uint32_t mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+      for (int i = tid; i < V; i += SAMPLE_THREADS) {
+        const float x = l[i] * inv_t;
+        const uint32_t key = ordered_key(x);
+        if (key >= thr && (key & mask) == prefix) atomicAdd(&mass[(key >> shift) & 255u], fixed_mass(x, maxv));
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned long long need = s_remaining_mass, cum = 0;
+        int b = 255;
+        for (; b > 0; --b) {
+          if (cum + mass[b] >= need) break;
+          cum += mass[b];
+        }
+        s_remaining_mass = need - cum;
+        s_prefix = prefix | ((uint32_t)b << shift);
+      }
+      __syncthreads();
+    }
+    const uint32_t thr_p = s_prefix;
+    thr = thr_p > thr ? thr_p : thr;
+  }
+
+  // ---- Gumbel-max over the survivors
+  const unsigned long long key_row = keys[row];
+  best = 0;
+  for (int i = tid; i < V; i += SAMPLE_THREADS) {
+    const float x = l[i] * inv_t;
+    if (ordered_key(x) < thr) continue;
+    const float u = counter_uniform(key_row, (uint32_t)i);
+    const float g = -logf(-logf(u));
+    const unsigned long long c = pack_candidate(x + g, i);
+    best = c > best ? c : best;
+  }
+  best = block_max_u64(best, scratch);
+  if (tid == 0) out[row] = (int)(0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull));
+}
+
+// Penalties before everything else (sampler.rs:320-345): for each distinct token seen so far,
+// logit /= repetition (when != 0), logit -= presence, logit -= frequency * count.
+__global__ void penalties_kernel(float* logits, long ld, int V, const int* __restrict__ row_of, const int* __restrict__ token,
+                                 const int* __restrict__ count, const float* __restrict__ presence,
+                                 const float* __restrict__ frequency, const float* __restrict__ repetition, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int r = row_of[i], tk = token[i];
+  if (tk < 0 || tk >= V) return;
+  float v = logits[(size_t)r * ld + tk];
+  if (repetition[r] != 0.f) v /= repetition[r];
+  v -= presence[r];
+  if (frequency[r] != 0.f) v -= frequency[r] * (float)count[i];
+  logits[(size_t)r * ld + tk] = v;
+}
+
+}  // namespace vob
+
+using namespace vob;
+
+VOB_API int vob_sample(const float* logits, long ld, int R, int V, const float* temperature, const int* top_k,
+                       const float* top_p, const unsigned long long* keys, int* out, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (V <= 0) return VOB_BAD_ARGUMENT;
+  sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, keys, out);
+  return launch_status();
+}
+
+// (row, token, count) triples: one per distinct token of a row's history; a triple must appear once.
+VOB_API int vob_apply_penalties(float* logits, long ld, int V, const int* row_of, const int* token, const int* count,
+                                const float* presence, const float* frequency, const float* repetition, int n,
+                                cudaStream_t stream) {
+  if (n <= 0) return 0;
+  penalties_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, ld, V, row_of, token, count, presence, frequency,
+                                                        repetition, n);
+  return launch_status();
+}

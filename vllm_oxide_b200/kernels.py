@@ -1,0 +1,148 @@
+"""ctypes bindings of libvob_kernels.so: one Python function per C entry point.
+
+The library is built in-tree at first use.  There is no fallback: without a CUDA device,
+without nvcc or without the built library every call raises `KernelError`.  Tensors are
+passed as raw device pointers; every launch goes to torch's current stream, so launches
+made inside `torch.cuda.graph(...)` are captured.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1}
+
+ERR_BITS = {1: "a token id outside the vocabulary", 2: "a position beyond max_position_embeddings",
+            4: "a cache slot outside the pool", 8: "a block-table entry that names no page",
+            16: "a wanted row outside the batch"}
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        try:
+            path = _build.build_kernels()
+            _lib = ctypes.CDLL(path)
+        except (OSError, _build.BuildError) as e:
+            raise KernelError(f"the CUDA kernel library of vllm_oxide_b200 is not available: {e}") from e
+        _lib.vob_error_string.restype = ctypes.c_char_p
+        _lib.vob_error_string.argtypes = [ctypes.c_int]
+    return _lib
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {lib().vob_error_string(code).decode()} (code {code})")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_CODES[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("vllm_oxide_b200 kernels run on CUDA tensors only; there is no CPU path")
+
+
+def describe_error_word(word: int) -> str:
+    return "; ".join(msg for bit, msg in ERR_BITS.items() if word & bit) or f"unknown error bits {word}"
+
+
+def embedding(table, ids, out, num_tokens: int, err) -> None:
+    _cuda(table, ids, out)
+    V, H = table.shape
+    _check(lib().vob_embedding(_p(table), _p(ids), _p(out), num_tokens, H, V, _code(table.dtype), _p(err), _stream()),
+           "embedding")
+
+
+def add_rmsnorm(x, residual, weight, y, eps: float, has_residual: bool, err, rows=None, n_out: Optional[int] = None):
+    """y = RMSNorm(x + residual) * weight; residual updated in place (unless `rows` selects source rows)."""
+    _cuda(x, residual, weight, y, rows)
+    assert weight.dtype == torch.float32
+    H = x.shape[-1]
+    n_src = x.shape[0]
+    n = n_src if n_out is None else n_out
+    _check(lib().vob_add_rmsnorm(_p(x), _p(residual), _p(weight), _p(y), _p(rows), n, H, n_src,
+                                 ctypes.c_float(eps), int(has_residual), _code(x.dtype), _p(err), _stream()),
+           "add_rmsnorm")
+
+
+def silu_mul(gate_up, out, num_tokens: int) -> None:
+    _cuda(gate_up, out)
+    I = out.shape[-1]
+    _check(lib().vob_silu_mul(_p(gate_up), _p(out), num_tokens, I, _code(out.dtype), _stream()), "silu_mul")
+
+
+def qk_norm_rope_kv_write(qkv, bias, positions, slots, wq, wk, cos_sin, kcache, vcache, num_tokens, nh, kvh, hd,
+                          eps, write_kv: bool, err) -> None:
+    _cuda(qkv, positions, slots, cos_sin, kcache, vcache)
+    num_slots = kcache.shape[0] * kcache.shape[1] if kcache is not None else 0
+    _check(lib().vob_qk_norm_rope_kv_write(_p(qkv), _p(bias), _p(positions), _p(slots), _p(wq), _p(wk), _p(cos_sin),
+                                           _p(kcache), _p(vcache), num_tokens, nh, kvh, hd, ctypes.c_float(eps),
+                                           cos_sin.shape[0], ctypes.c_long(num_slots), int(write_kv),
+                                           _code(qkv.dtype), _p(err), _stream()), "qk_norm_rope_kv_write")
+
+
+def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, token_req, positions, num_tokens, nh, kvh,
+                            hd, window: int, scale: float, err) -> None:
+    _cuda(q, out, kcache, vcache, block_tables, token_req, positions)
+    _check(lib().vob_paged_attention_generic(_p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache),
+                                             _p(block_tables), block_tables.shape[-1], _p(token_req), _p(positions),
+                                             num_tokens, nh, kvh, hd, kcache.shape[1], window, ctypes.c_float(scale),
+                                             ctypes.c_long(kcache.shape[0]), _code(q.dtype), _p(err), _stream()),
+           "paged_attention_generic")
+
+
+def gemm_f32(a, w, out, bias=None) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T in true float32."""
+    _cuda(a, w, out)
+    assert a.dtype == w.dtype == out.dtype == torch.float32
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape[0] == M and out.shape[1] == N
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(lib().vob_gemm_f32(_p(a), ctypes.c_long(a.stride(0)), _p(w), ctypes.c_long(w.stride(0)), _p(out),
+                              ctypes.c_long(out.stride(0)), _p(bias), M, N, K, _stream()), "gemm_f32")
+
+
+def sample(logits, temperature, top_k, top_p, keys, out, num_rows: int) -> None:
+    _cuda(logits, temperature, top_k, top_p, keys, out)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    _check(lib().vob_sample(_p(logits), ctypes.c_long(logits.stride(0)), num_rows, logits.shape[1], _p(temperature),
+                            _p(top_k), _p(top_p), _p(keys), _p(out), _stream()), "sample")
+
+
+def apply_penalties(logits, row_of, token, count, presence, frequency, repetition, n: int) -> None:
+    _cuda(logits, row_of, token, count)
+    _check(lib().vob_apply_penalties(_p(logits), ctypes.c_long(logits.stride(0)), logits.shape[1], _p(row_of),
+                                     _p(token), _p(count), _p(presence), _p(frequency), _p(repetition), n, _stream()),
+           "apply_penalties")
+
+
+def copy_pages(cache_plane, pairs, n_pairs: int) -> None:
+    _cuda(cache_plane, pairs)
+    page_elems = cache_plane[0].numel()
+    _check(lib().vob_copy_pages(_p(cache_plane), _p(pairs), n_pairs, ctypes.c_long(page_elems),
+                                _code(cache_plane.dtype), _stream()), "copy_pages")

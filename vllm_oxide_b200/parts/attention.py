@@ -1,0 +1,95 @@
+"""Grouped-query attention over the paged cache, with optional per-head q/k norm, bias and window.
+
+The order is the reference's (vllm-oxide, crates/vllm-oxide/src/models/qwen3.rs:160-213):
+merged q|k|v product, split, RMSNorm over head_dim of q and of k, rotation of q and k, keys
+(after norm and rotation) and values written to the cache, attention with scale
+1/sqrt(head_dim), output product.  Unlike the reference's prefill, which reads only the keys of
+the current step (crates/vllm-oxide/src/attention/flash_attn.rs:15-37), every query here reads
+its keys from the pages, so portions, cache hits, recomputation and decoding are one case.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels
+from ..weights.loader import TensorSpec
+from .base import CacheSpec, Mixer, register_part
+from .linear import linear
+
+
+class Attention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, eps: float,
+                 qkv_bias: bool, qk_norm: bool, window: Optional[int], position: str, prefix: str,
+                 positions: dict, dtype, device, **_):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
+        if head_dim % 16 or head_dim > 512:
+            raise ValueError(f"head_dim {head_dim} is not supported by the attention kernels "
+                             f"(a multiple of 16 up to 512)")
+        self.H, self.nh, self.kvh, self.hd = hidden_size, num_heads, num_kv_heads, head_dim
+        self.eps, self.qkv_bias, self.qk_norm = float(eps), qkv_bias, qk_norm
+        self.window = int(window or 0)
+        self.rope = positions[position]
+        self.prefix, self.dtype, self.device = prefix, dtype, device
+        self.scale = 1.0 / math.sqrt(head_dim)   # qwen3.rs:204
+        self.wqkv = self.wo = self.bqkv = self.wq_norm = self.wk_norm = None
+
+    # ---- tensors
+    def _names(self):
+        p = self.prefix
+        return {k: f"{p}{k}" for k in ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight",
+                                       "q_proj.bias", "k_proj.bias", "v_proj.bias", "q_norm.weight", "k_norm.weight")}
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        n, q, kv = self._names(), self.nh * self.hd, self.kvh * self.hd
+        specs = [TensorSpec(n["q_proj.weight"], (q, self.H), "matrix", self.H),
+                 TensorSpec(n["k_proj.weight"], (kv, self.H), "matrix", self.H),
+                 TensorSpec(n["v_proj.weight"], (kv, self.H), "matrix", self.H),
+                 TensorSpec(n["o_proj.weight"], (self.H, q), "matrix", q)]
+        if self.qkv_bias:
+            specs += [TensorSpec(n["q_proj.bias"], (q,), "bias"), TensorSpec(n["k_proj.bias"], (kv,), "bias"),
+                      TensorSpec(n["v_proj.bias"], (kv,), "bias")]
+        if self.qk_norm:
+            specs += [TensorSpec(n["q_norm.weight"], (self.hd,), "norm"),
+                      TensorSpec(n["k_norm.weight"], (self.hd,), "norm")]
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = self._names()
+        # rows of q, then k, then v (crates/vllm-oxide/src/layers/linear.rs:109-119)
+        self.wqkv = torch.cat([tensors[n["q_proj.weight"]], tensors[n["k_proj.weight"]],
+                               tensors[n["v_proj.weight"]]], dim=0).contiguous()
+        self.wo = tensors[n["o_proj.weight"]].contiguous()
+        if self.qkv_bias:
+            self.bqkv = torch.cat([tensors[n["q_proj.bias"]], tensors[n["k_proj.bias"]],
+                                   tensors[n["v_proj.bias"]]], dim=0).contiguous()
+        if self.qk_norm:
+            self.wq_norm = tensors[n["q_norm.weight"]].contiguous()
+            self.wk_norm = tensors[n["k_norm.weight"]].contiguous()
+
+    def cache_spec(self) -> CacheSpec:
+        return CacheSpec(self.kvh, self.hd, self.window)
+
+    # ---- one step
+    def forward(self, x, ctx, cache, state=None, write_cache: bool = True):
+        T = x.shape[0]
+        width = (self.nh + 2 * self.kvh) * self.hd
+        qkv = linear(x, self.wqkv, ctx.ws.get("qkv", T, width, x.dtype))
+        g = cache.group
+        kernels.qk_norm_rope_kv_write(qkv, self.bqkv, ctx.positions, ctx.slot_mapping[g], self.wq_norm, self.wk_norm,
+                                      self.rope.cos_sin, cache.k, cache.v, T, self.nh, self.kvh, self.hd, self.eps,
+                                      write_cache, ctx.err)
+        attn = ctx.ws.get("attn_out", T, self.nh * self.hd, x.dtype)
+        self.attend(qkv, width, attn, cache, ctx, T)
+        return linear(attn, self.wo, ctx.ws.get("attn_proj", T, self.H, x.dtype))
+
+    def attend(self, qkv, q_stride, out, cache, ctx, T):
+        kernels.paged_attention_generic(qkv, q_stride, out, cache.k, cache.v, ctx.block_tables[cache.group],
+                                        ctx.token_req, ctx.positions, T, self.nh, self.kvh, self.hd, self.window,
+                                        self.scale, ctx.err)
+
+
+register_part("mixer", "attention", Attention)

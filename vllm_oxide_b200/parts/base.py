@@ -1,0 +1,157 @@
+"""Interfaces of the parts a model is put together from, and the registries that name them.
+
+A model is a list of blocks; a block arranges a token mixer, a feed-forward and norms; a
+mixer may use a position encoding.  Every part takes its sizes and constants as
+constructor parameters and is chosen by kind name, layer by layer, from a `PartSpec`.  No
+part knows which model it is in: it sees its own tensors (by the checkpoint names it is
+given), the step's batch, its cache plane or state, and a workspace for activations.
+
+Interfaces (duck-typed; the base classes document them):
+
+  Norm.forward(x, residual, ctx, rows=None)   -> (y, residual)   fused add + norm
+  PositionEncoding                              a table plus what the mixer's kernel needs of it
+  Mixer.forward(x, ctx, cache, state)          -> [T, hidden]
+  FeedForward.forward(x, ctx)                  -> [T, hidden]
+  Block.forward(hidden, residual, ctx, cache, state) -> (hidden, residual)
+
+and, for every part that owns tensors:
+
+  tensor_specs() -> [TensorSpec]      what it needs from the checkpoint
+  load(tensors: {name: tensor})       called once with exactly those tensors
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..weights.loader import TensorSpec
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """Which part, and its parameters: the configuration's choice for one place in one layer."""
+    kind: str
+    params: dict = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class CacheSpec:
+    """What a mixer needs of the paged cache: keys and values of `kv_heads * head_dim` elements per
+    token, all positions (window 0) or the last `window`.  Planes with equal specs share a group:
+    one page pool and one block table per request."""
+    kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size that a mixer keeps beside (or instead of) the paged cache."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class CachePlane:
+    """One layer's keys and values: [num_pages, block_size, kv_heads, head_dim] each."""
+    k: torch.Tensor
+    v: torch.Tensor
+    group: int
+    block_size: int
+
+
+class Workspace:
+    """Activation buffers with fixed addresses: allocated once for the largest step and handed out
+    by name, so that a step captured in a CUDA graph finds them where they were."""
+
+    def __init__(self, max_rows: int, device, dtype: torch.dtype):
+        self.max_rows, self.device, self.dtype = max_rows, device, dtype
+        self._buffers: Dict[tuple, torch.Tensor] = {}
+
+    def get(self, name: str, rows: int, cols: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        dtype = dtype or self.dtype
+        key = (name, cols, dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.shape[0] < rows:
+            cap = max(rows, self.max_rows)
+            buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:rows]
+
+    def get_rows(self, name: str, rows: int, cols: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """A buffer whose row count follows demand (wanted rows, not tokens): it grows when asked for
+        more rows than it has, and never shrinks."""
+        dtype = dtype or self.dtype
+        key = (name, cols, dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.shape[0] < rows:
+            buf = torch.empty((max(rows, 1), cols), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:rows]
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._buffers.values())
+
+
+class Part:
+    def tensor_specs(self) -> List[TensorSpec]:
+        return []
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
+
+
+class Norm(Part):
+    def forward(self, x, residual, ctx, rows=None, n_rows=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    pass
+
+
+class Mixer(Part):
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, x, ctx, cache: Optional[CachePlane], state: Optional[torch.Tensor], write_cache: bool = True):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, ctx):
+        raise NotImplementedError
+
+
+class Block(Part):
+    def forward(self, hidden, residual, ctx, cache, state, write_cache=True):
+        raise NotImplementedError
+
+
+# ------------------------------------------------------------------ registries
+_REGISTRIES: Dict[str, Dict[str, Callable]] = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}}
+
+
+def register_part(family: str, kind: str, factory: Callable) -> None:
+    """Makes `factory(**params, **common)` available under (family, kind).  Families: norm, position,
+    mixer, feed_forward, block.  Registering a kind twice replaces it (tests register toy parts)."""
+    if family not in _REGISTRIES:
+        raise KeyError(f"unknown part family {family!r}; families are {sorted(_REGISTRIES)}")
+    _REGISTRIES[family][kind] = factory
+
+
+def build_part(family: str, spec: PartSpec, **common):
+    try:
+        factory = _REGISTRIES[family][spec.kind]
+    except KeyError:
+        raise KeyError(f"no {family} part of kind {spec.kind!r}; known: {sorted(_REGISTRIES[family])}") from None
+    return factory(**spec.params, **common)
+
+
+def known_parts(family: str) -> List[str]:
+    return sorted(_REGISTRIES[family])

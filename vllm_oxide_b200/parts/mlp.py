@@ -1,0 +1,40 @@
+"""SwiGLU feed-forward: down( silu(gate(x)) * up(x) ) with gate and up merged into one product
+(vllm-oxide, crates/vllm-oxide/src/models/qwen3.rs:60-87, crates/vllm-oxide/src/layers/activation.rs:17-21)."""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import kernels
+from ..weights.loader import TensorSpec
+from .base import FeedForward, register_part
+from .linear import linear
+
+
+class SwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, **_):
+        self.H, self.I, self.prefix = hidden_size, intermediate_size, prefix
+        self.wgu = self.wdown = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p = self.prefix
+        return [TensorSpec(p + "gate_proj.weight", (self.I, self.H), "matrix", self.H),
+                TensorSpec(p + "up_proj.weight", (self.I, self.H), "matrix", self.H),
+                TensorSpec(p + "down_proj.weight", (self.H, self.I), "matrix", self.I)]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        p = self.prefix
+        # rows of gate, then up (crates/vllm-oxide/src/layers/linear.rs:132-138)
+        self.wgu = torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]], dim=0).contiguous()
+        self.wdown = tensors[p + "down_proj.weight"].contiguous()
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        gu = linear(x, self.wgu, ctx.ws.get("gate_up", T, 2 * self.I, x.dtype))
+        act = ctx.ws.get("act", T, self.I, x.dtype)
+        kernels.silu_mul(gu, act, T)
+        return linear(act, self.wdown, ctx.ws.get("mlp_out", T, self.H, x.dtype))
+
+
+register_part("feed_forward", "swiglu", SwiGLU)

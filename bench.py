@@ -1,0 +1,279 @@
+"""Decode and prefill throughput of the engine at Qwen3-8B sizes (bf16, random weights, one B200).
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step.  The default run has the layer sizes of the 8B configuration, a batch
+of 8 requests whose context starts at 2,048 tokens, and prints ONE JSON line:
+  value     decoded tokens per second, timed on the device with CUDA events around K steps;
+  e2e       the same through the Python entry point (LLM.add_request / LLM.step): pinned host
+            buffers in, sampled tokens out, every step;
+  prefill   one 2,048-token prompt in one step; frac = flops / time / peak;
+  roofline  the decode step's bytes (every weight once + the cache of the live requests) / time
+            against the measured copy bandwidth;
+  points    decode at batch 1 and 64.
+Every timed step reads 15 GB of weights, far more than the 126 MB L2, so nothing stays cached
+between iterations.  Peaks come from MEASURED_PEAKS.json beside this file when present.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096, num_attention_heads=32,
+                num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0,
+                rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=False, hidden_act="silu",
+                attention_bias=False, torch_dtype="bfloat16")
+PROMPT_LEN, NEW_TOKENS, CONTEXT, BLOCK = 2048, 256, 4096, 256
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            d = json.load(open(path))
+            flat = {}
+            def walk(x):
+                if isinstance(x, dict):
+                    for k, v in x.items():
+                        if isinstance(v, (int, float)):
+                            flat.setdefault(k, float(v))
+                        else:
+                            walk(v)
+            walk(d)
+            if "hbm_gbs" in flat and "bf16_tflops" in flat:
+                return dict(hbm_gbs=flat["hbm_gbs"], bf16_tflops=flat["bf16_tflops"],
+                            bf16_tflops_sustained=flat.get("bf16_tflops_sustained"), source="measured")
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        self.result = dict(sm_mhz=None, sm_max_mhz=None, reasons=[])
+        if self.proc is None:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if sm:
+            self.result = dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons))
+
+
+def model_numbers(c):
+    H, L, nh, kvh, hd, I, V = (c["hidden_size"], c["num_hidden_layers"], c["num_attention_heads"], c["num_key_value_heads"],
+                               c["head_dim"], c["intermediate_size"], c["vocab_size"])
+    per_layer = (nh + 2 * kvh) * hd * H + nh * hd * H + 3 * I * H
+    linear_params = L * per_layer
+    weight_bytes = 2 * (linear_params + V * H) + 4 * (L * (2 * H + 2 * hd) + H)   # bf16 matrices + lm_head, f32 norms
+    kv_bytes_per_token = 2 * L * kvh * hd * 2
+    return dict(linear_params=linear_params, weight_bytes=weight_bytes, kv_bytes_per_token=kv_bytes_per_token,
+                lm_head_params=V * H, L=L, nh=nh, hd=hd)
+
+
+def prefill_flops(c, T):
+    n = model_numbers(c)
+    linear = 2 * T * n["linear_params"] + 2 * n["lm_head_params"]          # lm_head on one row
+    attention = n["L"] * 4 * n["nh"] * n["hd"] * (T * (T + 1) // 2)         # causal QK^T and PV
+    return linear + attention
+
+
+def decode_run(llm, batch, steps, warmup, start_ctx):
+    """K decode steps of `batch` requests whose context starts at `start_ctx`, timed on the device.
+    The cache content does not matter for the time: pages are taken without a prefill."""
+    import torch
+    from vllm_oxide_b200 import host, kernels
+    mgr, core, sampler = llm.cache.manager, llm.core, llm.sampler
+    ids = list(range(10_000, 10_000 + batch))
+    for rid in ids:
+        assert mgr.add_request(rid) and mgr.ensure(rid, 0, start_ctx)
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, llm.model.vocab_size, (batch, steps + warmup), generator=g).tolist()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    temp, topk, topp, keys = [0.0] * batch, [0] * batch, [1.0] * batch, [0] * batch
+    pos = start_ctx
+    launches0 = 0
+    for i in range(steps + warmup):
+        if i == warmup:
+            torch.cuda.synchronize()
+            launches0 = kernels.launch_count
+            ev0.record()
+        entries = []
+        for b, rid in enumerate(ids):
+            assert mgr.ensure(rid, pos, 1)
+            entries.append(host.BatchEntry(rid, pos, [toks[b][i]], [0]))
+        logits = core.run(entries)
+        sampler.forward(logits, temp, topk, topp, keys)
+        pos += 1
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / steps
+    launches = kernels.launch_count - launches0
+    core.check_errors()
+    for rid in ids:
+        mgr.free_request(rid)
+    mean_ctx = start_ctx + warmup + (steps + 1) / 2
+    return ms, launches, mean_ctx
+
+
+def e2e_run(llm, batch, steps, warmup):
+    """The same metric through the public calls: prompts of 2,048 host token ids in, tokens out each step."""
+    import torch
+    from vllm_oxide_b200 import SamplingParams
+    g = torch.Generator().manual_seed(1)
+    prompts = torch.randint(0, llm.model.vocab_size, (batch, PROMPT_LEN), generator=g).tolist()
+    before = llm.scheduler.stats.prefill_tokens
+    for p in prompts:
+        llm.add_request(p, SamplingParams(temperature=0.0, max_tokens=steps + warmup + 16, ignore_eos=True))
+    while llm.scheduler.stats.prefill_tokens - before < batch * PROMPT_LEN:
+        llm.step()                            # prompts, in portions under the token budget
+    for _ in range(warmup):
+        llm.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    h2d = d2h = 0
+    for _ in range(steps):
+        llm.step()                            # pinned batch arrays in, sampled tokens out
+        h2d += llm.core.h2d_bytes_last + 20 * batch
+        d2h += 4 * batch + 4
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert llm.scheduler.num_running == batch, "a request finished inside the timed region"
+    while llm.is_running():
+        llm.step()
+    return batch * steps / dt, h2d // steps, d2h // steps
+
+
+def prefill_run(llm, T, reps=3, warmup=2):
+    import torch
+    from vllm_oxide_b200 import host
+    mgr, core = llm.cache.manager, llm.core
+    g = torch.Generator().manual_seed(2)
+    best = None
+    for i in range(reps + warmup):
+        toks = torch.randint(0, llm.model.vocab_size, (T,), generator=g).tolist()
+        rid = 20_000 + i
+        assert mgr.add_request(rid) and mgr.ensure(rid, 0, T)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        ev0.record()
+        core.run([host.BatchEntry(rid, 0, toks, [T - 1])])
+        ev1.record()
+        torch.cuda.synchronize()
+        mgr.free_request(rid)
+        if i >= warmup:
+            ms = ev0.elapsed_time(ev1)
+            best = ms if best is None else min(best, ms)
+    core.check_errors()
+    return best
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (reported)")
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate on candle: no Rust toolchain or "
+                          "network here, and pip finds neither setup.py nor pyproject.toml in it"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (use --gpus 1)")
+        return 2
+    import torch
+    from vllm_oxide_b200 import LLM, EngineOptions
+
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+    cfg = dict(QWEN3_8B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    n = model_numbers(cfg)
+    max_batch = 64 if not args.skip_points else args.batch
+    pages_per_req = (PROMPT_LEN + NEW_TOKENS + BLOCK - 1) // BLOCK + 1
+    opts = EngineOptions(max_model_len=CONTEXT, block_size=BLOCK, num_kv_blocks=max_batch * pages_per_req + 16,
+                         max_num_seqs=max(max_batch, 8), max_num_batched_tokens=8192, dtype="bfloat16")
+    llm = LLM.from_config(cfg, opts, seed=0, init_scheme="0.02")
+
+    prefill_ms = prefill_run(llm, PROMPT_LEN)
+    with ClockSampler() as clocks:
+        ms, launches, mean_ctx = decode_run(llm, args.batch, steps, warmup, PROMPT_LEN)
+    value = args.batch * 1000.0 / ms
+    step_bytes = n["weight_bytes"] + args.batch * mean_ctx * n["kv_bytes_per_token"]
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    e2e, h2d, d2h = e2e_run(llm, args.batch, steps, warmup)
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            pms, _, _ = decode_run(llm, b, min(steps, 32), warmup, PROMPT_LEN)
+            points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+    flops = prefill_flops(cfg, PROMPT_LEN)
+    line = {
+        "metric": "decode tok/s (Qwen3-8B sizes, bf16, batch 8, context 2048+)", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B sizes", "layers": cfg["num_hidden_layers"], "layers_of_config": 36,
+                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 12288, "vocab": 151936,
+                   "global_batch": args.batch, "seq_len": PROMPT_LEN, "new_tokens": NEW_TOKENS, "context": CONTEXT,
+                   "block_size": BLOCK, "parallelism": "single GPU", "l2": "every step reads 15 GB of weights (inputs larger than L2)",
+                   "peaks": pk["source"]},
+        "clocks": clocks.result,
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PROMPT_LEN * 1000.0 / prefill_ms, 1), "tokens": PROMPT_LEN, "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

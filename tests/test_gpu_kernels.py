@@ -1,0 +1,346 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the engine's."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen3_plain as P
+from plain import sampler_plain as S
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+def err_word():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [72, 1000])
+def test_embedding(dtype, H):
+    from vllm_oxide_b200 import kernels
+    V = 301
+    table = torch.randn(V, H, device=DEV).to(dtype)
+    ids = torch.tensor([0, 300, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, H, dtype=dtype, device=DEV)
+    err = err_word()
+    kernels.embedding(table, ids, out, 5, err)
+    assert torch.equal(out, P.embedding(table.cpu(), ids.cpu(), dtype).to(DEV)) and err.item() == 0
+    bad = torch.tensor([3, 301], dtype=torch.int32, device=DEV)
+    kernels.embedding(table, bad, out, 2, err)
+    assert err.item() == 1 and torch.equal(out[0], table[3]) and out[1].abs().max() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [100, 4104, 13000])
+def test_add_rmsnorm(dtype, H):
+    from vllm_oxide_b200 import kernels
+    T, eps = 7, 3e-6
+    x = torch.randn(T, H, device=DEV).to(dtype)
+    res = (3 * torch.randn(T, H, device=DEV)).to(dtype)
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).float()
+    wq = w.to(dtype)   # the plain formula multiplies in the model dtype; use a weight that is exact in it
+    y = torch.empty_like(x)
+    r = res.clone()
+    err = err_word()
+    kernels.add_rmsnorm(x, r, wq.float(), y, eps, True, err)
+    ry, rr = P.add_rms_norm(x.cpu(), res.cpu(), wq.cpu(), eps, dtype)
+    assert torch.allclose(y.cpu().float(), ry.float(), **tol(dtype))
+    assert torch.equal(r.cpu(), rr) if dtype == torch.bfloat16 else torch.allclose(r.cpu(), rr, atol=1e-6)
+    # without a residual: residual' = x
+    r2 = torch.zeros_like(x)
+    kernels.add_rmsnorm(x, r2, wq.float(), y, eps, False, err)
+    ry, _ = P.add_rms_norm(x.cpu(), None, wq.cpu(), eps, dtype)
+    assert torch.allclose(y.cpu().float(), ry.float(), **tol(dtype)) and torch.equal(r2, x)
+    # wanted rows only, residual untouched; the same row gives the same bits as in the full call
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    r3 = res.clone()
+    yr = torch.empty(3, H, dtype=dtype, device=DEV)
+    kernels.add_rmsnorm(x, r3, wq.float(), yr, eps, True, err, rows=rows, n_out=3)
+    full = torch.empty_like(x)
+    kernels.add_rmsnorm(x, res.clone(), wq.float(), full, eps, True, err)
+    assert torch.equal(yr, full[rows.long()]) and torch.equal(r3, res) and err.item() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    from vllm_oxide_b200 import kernels
+    T, I = 5, 333
+    gu = (4 * torch.randn(T, 2 * I, device=DEV)).to(dtype)
+    gu[0, 0], gu[0, 1] = -50.0, 0.0
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    kernels.silu_mul(gu, out, T)
+    g, u = gu[:, :I].cpu(), gu[:, I:].cpu()
+    it = torch.float32
+    ref = ((g.to(it) / (1 + torch.exp(-g.to(it)))).to(dtype) * u)
+    assert torch.allclose(out.cpu().float(), ref.float(), **tol(dtype))
+    assert out[0, 0].abs() < 1e-6 and out[0, 1] == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,kvh,hd", [(5, 5, 16), (6, 2, 48), (8, 1, 80), (4, 4, 256)])
+@pytest.mark.parametrize("norm,bias", [(True, False), (False, True)])
+def test_qk_norm_rope_kv_write(dtype, nh, kvh, hd, norm, bias):
+    from vllm_oxide_b200 import kernels
+    T, bs, pages, eps, max_pos, theta = 9, 16, 6, 2e-6, 300, 12345.0
+    width = (nh + 2 * kvh) * hd
+    qkv = torch.randn(T, width, device=DEV).to(dtype)
+    b = (0.1 * torch.randn(width, device=DEV)).to(dtype) if bias else None
+    wq = (1 + 0.1 * torch.randn(hd, device=DEV)).to(dtype).float() if norm else None
+    wk = (1 + 0.1 * torch.randn(hd, device=DEV)).to(dtype).float() if norm else None
+    pos = torch.tensor([0, 1, 2, 299, 150, 7, 64, 65, 31], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([5, 95, 17, -1, 40, 41, 0, 63, 64], dtype=torch.int32, device=DEV)
+    table = P.rope_table(hd, max_pos, theta)
+    kc = torch.full((pages, bs, kvh, hd), 7.0, device=DEV).to(dtype)
+    vc = torch.full((pages, bs, kvh, hd), 7.0, device=DEV).to(dtype)
+    out = qkv.clone()
+    err = err_word()
+    kernels.qk_norm_rope_kv_write(out, b, pos, slots, wq, wk, table.to(DEV), kc, vc, T, nh, kvh, hd, eps, True, err)
+    assert err.item() == 0
+    x = qkv.cpu()
+    if bias:
+        x = x + b.cpu()
+    q, k, v = P.split_qkv(x, nh, kvh, hd)
+    if norm:
+        q = P.head_rms_norm(q, wq.cpu().to(dtype), eps, dtype)
+        k = P.head_rms_norm(k, wk.cpu().to(dtype), eps, dtype)
+    q = P.apply_rope(q, pos.cpu(), table, dtype)
+    k = P.apply_rope(k, pos.cpu(), table, dtype)
+    got_q = out[:, :nh * hd].reshape(T, nh, hd).cpu()
+    assert torch.allclose(got_q.float(), q.float(), **tol(dtype))
+    kflat, vflat = kc.reshape(pages * bs, kvh, hd).cpu(), vc.reshape(pages * bs, kvh, hd).cpu()
+    written = torch.zeros(pages * bs, dtype=torch.bool)
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        written[s] = True
+        assert torch.allclose(kflat[s].float(), k[t].float(), **tol(dtype))
+        assert torch.equal(vflat[s], v[t].to(dtype))
+    assert (kflat[~written] == 7).all() and (vflat[~written] == 7).all()     # nothing else was touched
+    # a reader of another layer's cache writes nothing
+    kc2 = torch.zeros_like(kc)
+    kernels.qk_norm_rope_kv_write(qkv.clone(), b, pos, slots, wq, wk, table.to(DEV), kc2, kc2, T, nh, kvh, hd, eps, False, err)
+    assert kc2.abs().max() == 0
+    # positions beyond the table and slots beyond the pool are refused, not read
+    badpos = pos.clone(); badpos[0] = 300
+    kernels.qk_norm_rope_kv_write(qkv.clone(), b, badpos, slots, wq, wk, table.to(DEV), kc, vc, T, nh, kvh, hd, eps, True, err)
+    assert err.item() & 2
+    err.zero_()
+    badslot = slots.clone(); badslot[1] = pages * bs
+    kernels.qk_norm_rope_kv_write(qkv.clone(), b, pos, badslot, wq, wk, table.to(DEV), kc, vc, T, nh, kvh, hd, eps, True, err)
+    assert err.item() & 4
+
+
+def paged_setup(dtype, kvh, hd, bs, ctx_lens, g):
+    """Random keys/values for requests of the given context lengths, scattered over shuffled pages."""
+    B = len(ctx_lens)
+    pages_per = [(c + bs - 1) // bs for c in ctx_lens]
+    num_pages = sum(pages_per) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    P_max = max(pages_per)
+    bt = torch.full((B, P_max), -1, dtype=torch.int32)
+    kc = torch.randn(num_pages, bs, kvh, hd, generator=g).to(dtype)   # unused slots hold noise on purpose
+    vc = torch.randn(num_pages, bs, kvh, hd, generator=g).to(dtype)
+    ks, vs = [], []
+    it = iter(perm)
+    for b, c in enumerate(ctx_lens):
+        k = torch.randn(c, kvh, hd, generator=g).to(dtype)
+        v = torch.randn(c, kvh, hd, generator=g).to(dtype)
+        for p in range(pages_per[b]):
+            page = next(it)
+            bt[b, p] = page
+            n = min(bs, c - p * bs)
+            kc[page, :n] = k[p * bs:p * bs + n]
+            vc[page, :n] = v[p * bs:p * bs + n]
+        ks.append(k); vs.append(v)
+    return kc, vc, bt, ks, vs
+
+
+def run_attention(fn, dtype, nh, kvh, hd, bs, window, q_lens, ctx_lens, seed=0, craft=None):
+    """Queries are the last q_len positions of each request. Returns (got, want) [T, nh*hd]."""
+    g = torch.Generator().manual_seed(seed)
+    kc, vc, bt, ks, vs = paged_setup(dtype, kvh, hd, bs, ctx_lens, g)
+    T = sum(q_lens)
+    q = torch.randn(T, nh, hd, generator=g).to(dtype)
+    token_req = torch.tensor([b for b, n in enumerate(q_lens) for _ in range(n)], dtype=torch.int32)
+    positions = torch.tensor([c - n + i for n, c in zip(q_lens, ctx_lens) for i in range(n)], dtype=torch.int32)
+    if craft is not None:
+        craft(q, ks, vs, kc, vc, bt, positions)
+    want = torch.empty(T, nh * hd, dtype=dtype)
+    t0 = 0
+    for b, (n, c) in enumerate(zip(q_lens, ctx_lens)):
+        # plain attention over the whole request, then keep the rows of the queries
+        qfull = torch.zeros(c, nh, hd, dtype=dtype)
+        qfull[c - n:] = q[t0:t0 + n]
+        o = P.attention(qfull, ks[b], vs[b], torch.arange(c), window or None, dtype)
+        want[t0:t0 + n] = o[c - n:]
+        t0 += n
+    out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+    err = err_word()
+    cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    fn(q=q.to(DEV), out=out, kc=kc.to(DEV), vc=vc.to(DEV), bt=bt.to(DEV), token_req=token_req.to(DEV),
+       positions=positions.to(DEV), cu_q=cu_q.to(DEV), ctx=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
+       T=T, nh=nh, kvh=kvh, hd=hd, window=window, err=err)
+    assert err.item() == 0
+    return out.cpu().float(), want.float()
+
+
+def generic_attention(q, out, kc, vc, bt, token_req, positions, T, nh, kvh, hd, window, err, **_):
+    from vllm_oxide_b200 import kernels
+    kernels.paged_attention_generic(q.reshape(T, nh * hd), nh * hd, out, kc, vc, bt, token_req, positions, T, nh, kvh, hd,
+                                    window, 1.0 / math.sqrt(hd), err)
+
+
+ATT_CASES = [  # nh, kvh, hd, block_size, window, q_lens, ctx_lens
+    (4, 2, 16, 16, 0, [1, 5, 40], [1, 37, 40]),
+    (6, 1, 48, 32, 0, [1, 1, 1], [700, 33, 64]),
+    (8, 2, 128, 64, 0, [130, 1], [333, 129]),
+    (3, 3, 80, 16, 24, [1, 30, 2], [100, 61, 24]),
+    (5, 5, 32, 16, 7, [50], [50]),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ATT_CASES)
+def test_attention_generic(dtype, case):
+    nh, kvh, hd, bs, window, q_lens, ctx_lens = case
+    got, want = run_attention(generic_attention, dtype, nh, kvh, hd, bs, window, q_lens, ctx_lens)
+    assert torch.allclose(got, want, **(dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)))
+
+
+def craft_spike(key_pos):
+    """Makes one far key dominate every query's scores: the output must be that key's value."""
+    def craft(q, ks, vs, kc, vc, bt, positions):
+        hd = q.shape[-1]
+        bs = kc.shape[1]
+        q[:] = 0
+        q[..., 0] = 8.0
+        for b in range(len(ks)):
+            ks[b][:] = 0.01 * ks[b]
+            ks[b][key_pos, :, 0] = 8.0 * math.sqrt(hd)
+            vs[b][key_pos] = 5.0
+            for p in range((ks[b].shape[0] + bs - 1) // bs):
+                n = min(bs, ks[b].shape[0] - p * bs)
+                kc[bt[b, p], :n] = ks[b][p * bs:p * bs + n]
+                vc[bt[b, p], :n] = vs[b][p * bs:p * bs + n]
+    return craft
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key_pos,window,expect_hit", [
+    (3, 0, True),        # a far key among hundreds
+    (15, 0, True), (16, 0, True),            # the last slot of a page, the first slot of the next
+    (800 - 64, 64, True), (800 - 65, 64, False),   # the window's edge: just inside, just outside
+])
+def test_attention_generic_reads_the_right_far_key(dtype, key_pos, window, expect_hit):
+    got, want = run_attention(generic_attention, dtype, 2, 1, 32, 16, window, [1], [800], craft=craft_spike(key_pos))
+    assert torch.allclose(got, want, atol=3e-2)
+    assert (got.mean() > 4.9) == expect_hit
+
+
+def test_attention_generic_does_not_depend_on_the_batch():
+    """The same query gives the same bits alone, beside other requests, and from other pages."""
+    a_got, _ = run_attention(generic_attention, torch.float32, 4, 2, 64, 16, 0, [3], [200], seed=5)
+    g = torch.Generator().manual_seed(5)
+    kc, vc, bt, ks, vs = paged_setup(torch.float32, 2, 64, 16, [200], g)
+    q = torch.randn(3, 4, 64, generator=g)
+    # the same request, now second in a batch of three and on pages chosen by another permutation
+    g2 = torch.Generator().manual_seed(99)
+    kc2, vc2, bt2, ks2, vs2 = paged_setup(torch.float32, 2, 64, 16, [50, 200, 9], g2)
+    for p in range(13):
+        n = min(16, 200 - p * 16)
+        kc2[bt2[1, p], :n] = ks[0][p * 16:p * 16 + n]
+        vc2[bt2[1, p], :n] = vs[0][p * 16:p * 16 + n]
+    qq = torch.cat([torch.randn(1, 4, 64, generator=g2), q, torch.randn(2, 4, 64, generator=g2)])
+    token_req = torch.tensor([0, 1, 1, 1, 2, 2], dtype=torch.int32, device=DEV)
+    positions = torch.tensor([49, 197, 198, 199, 7, 8], dtype=torch.int32, device=DEV)
+    out = torch.empty(6, 256, device=DEV)
+    err = err_word()
+    generic_attention(qq.to(DEV), out, kc2.to(DEV), vc2.to(DEV), bt2.to(DEV), token_req, positions, 6, 4, 2, 64, 0, err)
+    assert torch.equal(out[1:4].cpu(), a_got)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 331, 80), (65, 130, 200), (200, 64, 4097)])
+def test_gemm_f32(M, N, K):
+    from vllm_oxide_b200 import kernels
+    a = torch.randn(M, K, device=DEV)
+    w = torch.randn(N, K, device=DEV)
+    out = torch.empty(M, N, device=DEV)
+    kernels.gemm_f32(a, w, out)
+    ref = (a.double() @ w.double().t())
+    assert (out.double() - ref).abs().max() <= 2e-6 * math.sqrt(K) * 16
+    # a row alone gives the same bits as the row in the batch
+    one = torch.empty(1, N, device=DEV)
+    kernels.gemm_f32(a[M // 2:M // 2 + 1].contiguous(), w, one)
+    assert torch.equal(one[0], out[M // 2])
+
+
+def test_gemm_f32_is_not_reduced_precision():
+    from vllm_oxide_b200 import kernels
+    # 1 + 2^-12 squared needs more than TF32's 10 mantissa bits
+    a = torch.full((4, 8), 1 + 2.0 ** -12, device=DEV)
+    w = torch.full((4, 8), 1 + 2.0 ** -12, device=DEV)
+    out = torch.empty(4, 4, device=DEV)
+    kernels.gemm_f32(a, w, out)
+    assert abs(out[0, 0].item() - 8 * (1 + 2.0 ** -12) ** 2) < 1e-6
+
+
+@pytest.mark.parametrize("V", [331, 4099, 151936])
+def test_sampler_against_the_plain_sampler(V):
+    from vllm_oxide_b200.sampling import Sampler, row_key
+    g = torch.Generator().manual_seed(V)
+    R = 12
+    logits = (3 * torch.randn(R, V, generator=g)).float()
+    logits[0, 5] = logits[0, 200] = logits[0].max() + 1          # a tie at the top: lowest index wins
+    temperature = [0.0, 0.8, 1.0, 1.0, 1.3, 0.7, 1.0, 1.0, 0.5, 2.0, 1.0, 1.0]
+    top_k = [0, 0, 8, 1, 0, 50, 0, 3, 0, 20, V, 0]
+    top_p = [1.0, 1.0, 1.0, 1.0, 0.9, 0.5, 0.2, 0.9, 1.0, 0.95, 0.3, 0.0]
+    keys = [row_key(7, r, 3 * r) for r in range(R)]
+    s = Sampler(DEV, 4)
+    got = s.forward(logits.to(DEV), temperature, top_k, top_p, keys).cpu().tolist()
+    want = [S.sample_row(logits[r].numpy(), temperature[r], top_k[r] or None, top_p[r] if top_p[r] < 1 else None, keys[r])
+            for r in range(R)]
+    assert got == want
+    assert got[0] == 5 and got[3] == int(torch.argmax(logits[3]))
+    for r in range(R):
+        if temperature[r] > 0 and top_k[r] != 1:
+            _, keep = S.surviving_mask(logits[r].numpy(), temperature[r], top_k[r] or None, top_p[r] if 0 < top_p[r] < 1 else None)
+            assert keep[got[r]]
+
+
+def test_sampler_rows_do_not_depend_on_the_batch_and_follow_the_distribution():
+    from vllm_oxide_b200.sampling import Sampler, row_key
+    s = Sampler(DEV, 4)
+    probs = torch.tensor([0.6, 0.25, 0.1, 0.05])
+    logits = probs.log().repeat(3000, 1).to(DEV)
+    keys = [row_key(1, 9, i) for i in range(3000)]
+    toks = s.forward(logits, [1.0] * 3000, [0] * 3000, [1.0] * 3000, keys).cpu()
+    freq = torch.bincount(toks, minlength=4).float() / 3000
+    assert (freq - probs).abs().max() < 0.03
+    alone = s.forward(logits[17:18], [1.0], [0], [1.0], keys[17:18]).cpu()
+    assert alone[0] == toks[17]
+
+
+def test_penalties_kernel():
+    from vllm_oxide_b200.sampling import Sampler
+    s = Sampler(DEV, 4)
+    logits = torch.full((2, 6), 4.0, device=DEV)
+    s.apply_penalties(logits, [[1, 1, 1, 2], None], [0.5, 0.0], [0.25, 0.0], [2.0, 0.0])
+    want = S.apply_penalties(np.full(6, 4.0, np.float32), [1, 1, 1, 2], 0.5, 0.25, 2.0)
+    assert np.allclose(logits[0].cpu().numpy(), want) and (logits[1] == 4).all()
+
+
+def test_copy_pages():
+    from vllm_oxide_b200 import kernels
+    plane = torch.randn(6, 16, 2, 8, device=DEV)
+    before = plane.clone()
+    pairs = torch.tensor([[0, 4], [2, 5]], dtype=torch.int32, device=DEV)
+    kernels.copy_pages(plane, pairs, 2)
+    assert torch.equal(plane[4], before[0]) and torch.equal(plane[5], before[2]) and torch.equal(plane[:4], before[:4])

@@ -1,0 +1,240 @@
+"""Trace replay against the plain implementation: the same requests whole, with the last 32 tokens
+decoded one by one, in portions of changing size, and mixed with other requests over so few pages
+that pages are used again; in 32-bit and in bfloat16."""
+import json
+import os
+import random
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT, TINY, tokens_for
+from plain import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+NAMES = ["A", "B", "C"]
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"A": [7, 33, 1, 64, 150], "B": [1, 5, 31, 32, 33, 100], "C": [3, 70, 41, 129, 16]}
+
+_plain_cache = {}
+
+
+def plain_logits(plain_models, name, tokens, dtype):
+    """Plain logits at every position.  For float32 the float64 run (the truth a 32-bit path is held to);
+    for bfloat16 the pair (float64 run, plain bfloat16 run): the second measures what rounding to
+    bfloat16 at every operation costs on this very sequence."""
+    key = (name, tuple(tokens), dtype)
+    if key not in _plain_cache:
+        cfg, w = plain_models[name]
+        truth = P.forward_logits(cfg, w, tokens, torch.float64).numpy()
+        if dtype == "float32":
+            _plain_cache[key] = truth
+        else:
+            _plain_cache[key] = Both(truth, P.forward_logits(cfg, w, tokens, torch.bfloat16).double().numpy())
+    return _plain_cache[key]
+
+
+class Both:
+    """Truth and the plain bfloat16 run; slicing slices both."""
+
+    def __init__(self, truth, rounded):
+        self.truth, self.rounded = truth, rounded
+
+    def __getitem__(self, idx):
+        return Both(self.truth[idx], self.rounded[idx])
+
+    def __len__(self):
+        return len(self.truth)
+
+
+def check(got, want, dtype, what):
+    """32-bit: within 2e-5 of the logits' scale of the float64 run.
+    bfloat16: the engine must be as close to the float64 run as the plain bfloat16 run is: at most 1.5 times
+    its root-mean-square error and 2.5 times its worst error (two runs that round at every operation, in
+    different orders, differ from each other by about 1.4 times that error)."""
+    got = np.asarray(got, np.float64)
+    if dtype == "float32":
+        want = np.asarray(want, np.float64)
+        assert got.shape == want.shape, what
+        worst = np.abs(got - want).max() / np.abs(want).max()
+        assert worst < 2e-5, f"{what}: {worst:.3e} of scale"
+        return
+    truth, rounded = want.truth, want.rounded
+    assert got.shape == truth.shape, what
+    rms = lambda d: np.sqrt((d ** 2).mean())
+    floor_rms, floor_worst = rms(rounded - truth), np.abs(rounded - truth).max()
+    got_rms, got_worst = rms(got - truth), np.abs(got - truth).max()
+    assert got_rms <= 1.5 * floor_rms and got_worst <= 2.5 * floor_worst, \
+        f"{what}: rms {got_rms:.3e} vs plain bfloat16 {floor_rms:.3e}; worst {got_worst:.3e} vs {floor_worst:.3e}"
+
+
+def check_same(a, b, dtype, what):
+    """Two cuts of the same work: equal beyond rounding (32-bit kernels give the same bits)."""
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    scale = np.abs(a).max()
+    worst = np.abs(a - b).max() / scale
+    assert worst < (1e-6 if dtype == "float32" else 0.03), f"{what}: {worst:.3e} of scale"
+
+
+def runner(model_folders, name, dtype, max_tokens):
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    return TraceRunner(model_folders[name], dtype, max_tokens, TINY[name]["block_size"])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_and_decode_and_portions(model_folders, plain_models, name, dtype):
+    bs = TINY[name]["block_size"]
+    for i, n in enumerate(LENGTHS[name]):
+        toks = tokens_for(name, n, salt=i)
+        want = plain_logits(plain_models, name, toks, dtype)
+        pool = (n + bs - 1) // bs * bs
+        # whole, every position wanted
+        r = runner(model_folders, name, dtype, pool)
+        whole = r.step([dict(id="w", tokens=toks, want=list(range(n)))], ["w"])
+        check(whole, want, dtype, f"{name} len {n} whole")
+        assert r.manager.num_free_blocks(0) == pool // bs and r.manager.check_invariants() == ""
+        # most of it in one step, the last 32 one by one
+        cut = max(1, n - 32)
+        r = runner(model_folders, name, dtype, pool)
+        rows = [r.step([dict(id="d", tokens=toks[:cut], want=[cut - 1])], [])[0]]
+        for t in range(cut, n):
+            rows.append(r.step([dict(id="d", tokens=[toks[t]], want=[0])], ["d"] if t == n - 1 else [])[0])
+        check(np.stack(rows), want[cut - 1:], dtype, f"{name} len {n} decode")
+        check_same(np.stack(rows), whole[cut - 1:], dtype, f"{name} len {n} decode vs whole")
+        # portions of changing size, down to two tokens
+        rng = random.Random(n)
+        r = runner(model_folders, name, dtype, pool)
+        got, pos = [], 0
+        sizes = [2, 3, 17, 2, bs, bs + 1, 5, 2, 64]
+        while pos < n:
+            m = min(sizes[len(got) % len(sizes)] if rng.random() < 0.7 else rng.randrange(2, 40), n - pos)
+            got.append(r.step([dict(id="p", tokens=toks[pos:pos + m], want=list(range(m)))], []))
+            pos += m
+        check(np.concatenate(got), want, dtype, f"{name} len {n} portions")
+        check_same(np.concatenate(got), whole, dtype, f"{name} len {n} portions vs whole")
+
+
+def mixed_schedule(name, lengths, seed):
+    """Steps for up to four live requests: portions of some beside decoded tokens of others; a request
+    may sit out a step. Returns (steps, requests, peak of live tokens rounded up to pages)."""
+    rng = random.Random(seed)
+    bs = TINY[name]["block_size"]
+    reqs = {f"r{i}": tokens_for(name, n, salt=50 + i) for i, n in enumerate(lengths)}
+    waiting = list(reqs)
+    live, pos, steps, peak = [], {}, [], 0
+    while waiting or live:
+        while waiting and len(live) < 4 and (not live or rng.random() < 0.6):
+            rid = waiting.pop(0)
+            live.append(rid); pos[rid] = 0
+        entries, end = [], []
+        for rid in list(live):
+            if len(live) > 1 and rng.random() < 0.25:
+                continue                                          # left out of this step
+            n, p = len(reqs[rid]), pos[rid]
+            left = n - p
+            if left <= 32 or rng.random() < 0.3:
+                m = 1                                             # decoding
+            else:
+                m = min(left, rng.choice([2, 2, 3, 5, bs - 1, bs, bs + 1, 40]))
+            entries.append(dict(id=rid, tokens=reqs[rid][p:p + m], want=list(range(m)), _at=p))
+            pos[rid] += m
+        peak = max(peak, sum((pos[r] + bs - 1) // bs * bs for r in live))
+        for e in entries:
+            if pos[e["id"]] == len(reqs[e["id"]]):
+                end.append(e["id"]); live.remove(e["id"])
+        if entries:
+            steps.append(dict(step=len(steps), entries=entries, end=end))
+    return steps, reqs, peak
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_mixed_batches_with_pages_used_again(model_folders, plain_models, name, dtype):
+    lengths = [90, 40, 66, 35, 120, 50, 77, 34, 45]
+    steps, reqs, peak = mixed_schedule(name, lengths, seed=3)
+    bs = TINY[name]["block_size"]
+    total_pages = sum((len(t) + bs - 1) // bs for t in reqs.values())
+    assert peak // bs < 0.7 * total_pages                         # the pool is far smaller than all requests
+    r = runner(model_folders, name, dtype, peak)
+    got = {rid: [None] * len(t) for rid, t in reqs.items()}
+    assert any(len(s["entries"]) >= 3 for s in steps)
+    assert any(len({len(e["tokens"]) == 1 for e in s["entries"]}) == 2 for s in steps)   # portions beside decodes
+    for s in steps:
+        out = r.step([{k: v for k, v in e.items() if k != "_at"} for e in s["entries"]], s["end"])
+        row = 0
+        for e in s["entries"]:
+            for w in e["want"]:
+                got[e["id"]][e["_at"] + w] = out[row]
+                row += 1
+        assert row == out.shape[0]
+        assert r.manager.check_invariants() == ""
+    assert r.manager.num_free_blocks(0) == peak // bs             # everything was given back
+    for rid, toks in reqs.items():
+        check(np.stack(got[rid]), plain_logits(plain_models, name, toks, dtype), dtype, f"{name} mixed {rid}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(model_folders, plain_models, dtype):
+    """300 tokens decoded one by one across many pages (and, in C, far past the window)."""
+    for name in ["A", "C"]:
+        toks = tokens_for(name, 320, salt=9)
+        want = plain_logits(plain_models, name, toks, dtype)
+        r = runner(model_folders, name, dtype, 320)
+        rows = [r.step([dict(id="x", tokens=toks[:20], want=[19])], [])[0]]
+        for t in range(20, 320):
+            rows.append(r.step([dict(id="x", tokens=[toks[t]], want=[0])], [])[0])
+        check(np.stack(rows), want[19:], dtype, f"{name} long decode")
+        if name == "C":     # the window group holds only what the window needs
+            held = [b for b in r.manager.block_table(0, 1) if b >= 0]
+            assert len(held) <= (24 + 16) // 16 + 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_first_tokens_of_a_sequence(model_folders, plain_models, name, dtype):
+    toks = tokens_for(name, 4, salt=77)
+    want = plain_logits(plain_models, name, toks, dtype)
+    r = runner(model_folders, name, dtype, 64)
+    rows = [r.step([dict(id="f", tokens=[t], want=[0])], [])[0] for t in toks]
+    check(np.stack(rows), want, dtype, f"{name} first tokens one by one")
+    r = runner(model_folders, name, dtype, 64)
+    rows = r.step([dict(id="f", tokens=toks[:2], want=[0, 1])], [])
+    rows = np.concatenate([rows, r.step([dict(id="f", tokens=toks[2:], want=[0, 1])], ["f"])])
+    check(rows, want, dtype, f"{name} first tokens two by two")
+
+
+def test_the_program_itself(model_folders, plain_models, tmp_path):
+    """bin/trace_run as a user calls it: steps on stdin, `done <step>` lines, <step>.f32 files."""
+    name, dtype = "B", "float32"
+    a, b = tokens_for(name, 40, salt=1), tokens_for(name, 21, salt=2)
+    steps = [
+        dict(step=0, entries=[dict(id="a", tokens=a[:30], want=[29])], end=[]),
+        dict(step=1, entries=[dict(id="a", tokens=a[30:31], want=[0]), dict(id="b", tokens=b[:20], want=[])], end=[]),
+        dict(step=2, entries=[dict(id="b", tokens=b[20:], want=[0])], end=["b"]),
+        dict(step=3, entries=[dict(id="a", tokens=a[31:], want=[0, 8])], end=["a"]),
+    ]
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_folders[name],
+                           "--dtype", dtype, "--out", str(out), "--max-tokens", "128", "--block-size", "32"],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+    V = TINY[name]["config"]["vocab_size"]
+    pa, pb = plain_logits(plain_models, name, a, dtype), plain_logits(plain_models, name, b, dtype)
+    read = lambda i: np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)
+    check(read(0), pa[29:30], dtype, "step 0")
+    check(read(1), pa[30:31], dtype, "step 1")
+    check(read(2), pb[20:21], dtype, "step 2")
+    check(read(3), pa[[31, 39]], dtype, "step 3")
+    assert sorted(os.listdir(out)) == ["0.f32", "1.f32", "2.f32", "3.f32"]
+
+
+def test_running_out_of_pages_is_an_error_not_a_wrong_result(model_folders):
+    r = runner(model_folders, "A", "float32", 32)
+    r.step([dict(id="a", tokens=list(range(30)), want=[])], [])
+    with pytest.raises(RuntimeError, match="no pages left"):
+        r.step([dict(id="b", tokens=list(range(10)), want=[])], [])

@@ -1,0 +1,197 @@
+"""Generality of the parts: a toy architecture, defined HERE, is registered, built and stepped
+without a change to the framework's files.
+
+The toy model has a mixer with state of its own (a decaying sum per request, kept in the cache
+manager's state slots, no pages), names one attention layer twice in its order (each run with a
+cache plane of its own), and lets a last attention layer read the keys and values that the first
+run wrote.  It is compared, whole and in portions and mixed with another request, with a plain
+implementation written below from the plain parts.
+"""
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+
+H, NH, KVH, HD, I, V, EPS, THETA, MAXPOS, DECAY = 48, 3, 1, 16, 72, 97, 1e-5, 1000.0, 256, 0.75
+
+
+def register_toy():
+    from vllm_oxide_b200.models import ExecStep, ModelPlan, register_architecture
+    from vllm_oxide_b200.parts import Mixer, PartSpec, StateSpec, register_part
+    from vllm_oxide_b200.weights import TensorSpec
+
+    class DecayMixer(Mixer):
+        """y_t = (s_t) W^T with s_t = decay * s_{t-1} + x_t, s kept per request in a state slot."""
+
+        def __init__(self, hidden_size, decay, prefix, **_):
+            self.H, self.decay, self.prefix = hidden_size, decay, prefix
+
+        def tensor_specs(self):
+            return [TensorSpec(self.prefix + "mix.weight", (self.H, self.H), "matrix", self.H)]
+
+        def load(self, tensors):
+            self.w = tensors[self.prefix + "mix.weight"]
+
+        def state_spec(self):
+            return StateSpec((self.H,), torch.float32)
+
+        def forward(self, x, ctx, cache, state, write_cache=True):
+            assert cache is None and state is not None
+            cu = ctx.host_view("cu_q")
+            slots = ctx.host_view("state_slots")
+            out = torch.empty_like(x)
+            for r in range(ctx.num_requests):
+                s = state[int(slots[r])].clone()
+                for t in range(int(cu[r]), int(cu[r + 1])):
+                    s = self.decay * s + x[t].float()
+                    out[t] = (s @ self.w.float().t()).to(x.dtype)
+                state[int(slots[r])] = s
+            return out
+
+    register_part("mixer", "toy_decay", DecayMixer)
+
+    @dataclass
+    class ToyConfig:
+        raw: dict
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+    def norm(name):
+        return PartSpec("rmsnorm", dict(size=H, eps=EPS, weight_name=name))
+
+    def toy_plan(cfg):
+        def attn_layer(i):
+            p = f"toy.layers.{i}."
+            return PartSpec("pre_norm", dict(
+                mixer=PartSpec("attention", dict(hidden_size=H, num_heads=NH, num_kv_heads=KVH, head_dim=HD, eps=EPS,
+                                                 qkv_bias=False, qk_norm=True, window=None, position="rope",
+                                                 prefix=p + "self_attn.")),
+                feed_forward=PartSpec("swiglu", dict(hidden_size=H, intermediate_size=I, prefix=p + "mlp.")),
+                input_norm=norm(p + "input_layernorm.weight"), post_mixer_norm=norm(p + "post_attention_layernorm.weight")))
+        decay_layer = PartSpec("pre_norm", dict(
+            mixer=PartSpec("toy_decay", dict(hidden_size=H, decay=DECAY, prefix="toy.layers.1.")),
+            feed_forward=PartSpec("swiglu", dict(hidden_size=H, intermediate_size=I, prefix="toy.layers.1.mlp.")),
+            input_norm=norm("toy.layers.1.input_layernorm.weight"),
+            post_mixer_norm=norm("toy.layers.1.post_attention_layernorm.weight")))
+        return ModelPlan(
+            architecture="ToyDecayForCausalLM", hidden_size=H, vocab_size=V, max_position=MAXPOS,
+            embedding_name="toy.embed.weight", lm_head_name=None, final_norm=norm("toy.norm.weight"),
+            positions={"rope": PartSpec("rope", dict(head_dim=HD, max_position=MAXPOS, theta=THETA))},
+            layers=[attn_layer(0), decay_layer, attn_layer(2)],
+            # layer 0 runs twice (planes 0 and 2); layer 2 reads what the first run of layer 0 wrote
+            order=[ExecStep(0, 0), ExecStep(1, 1), ExecStep(0, 2), ExecStep(2, 0, write_cache=False)])
+
+    register_architecture("ToyDecayForCausalLM", ToyConfig.from_dict, toy_plan)
+
+
+def plain_toy(weights, tokens, dt):
+    """The toy model, whole sequence, from the plain parts."""
+    ids = torch.as_tensor(tokens)
+    pos = torch.arange(len(tokens))
+    table = P.rope_table(HD, MAXPOS, THETA)
+    hidden, residual = P.embedding(weights["toy.embed.weight"], ids, dt), None
+    kept = {}
+
+    def attn_block(i, hidden, residual, write_to=None, read_from=None):
+        p = f"toy.layers.{i}."
+        normed, residual = P.add_rms_norm(hidden, residual, weights[p + "input_layernorm.weight"], EPS, dt)
+        q = P.linear(normed, weights[p + "self_attn.q_proj.weight"], dt)
+        k = P.linear(normed, weights[p + "self_attn.k_proj.weight"], dt)
+        v = P.linear(normed, weights[p + "self_attn.v_proj.weight"], dt)
+        q, k, v = P.split_qkv(torch.cat([q, k, v], -1), NH, KVH, HD)
+        q = P.apply_rope(P.head_rms_norm(q, weights[p + "self_attn.q_norm.weight"], EPS, dt), pos, table, dt)
+        k = P.apply_rope(P.head_rms_norm(k, weights[p + "self_attn.k_norm.weight"], EPS, dt), pos, table, dt)
+        if write_to is not None:
+            kept[write_to] = (k, v)
+        if read_from is not None:
+            k, v = kept[read_from]
+        a = P.linear(P.attention(q, k, v, pos, None, dt), weights[p + "self_attn.o_proj.weight"], dt)
+        normed, residual = P.add_rms_norm(a, residual, weights[p + "post_attention_layernorm.weight"], EPS, dt)
+        return P.swiglu(normed, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"],
+                        weights[p + "mlp.down_proj.weight"], dt), residual
+
+    hidden, residual = attn_block(0, hidden, residual, write_to=0)
+    normed, residual = P.add_rms_norm(hidden, residual, weights["toy.layers.1.input_layernorm.weight"], EPS, dt)
+    s = torch.zeros(H, dtype=torch.float32 if dt != torch.float64 else dt)
+    mixed = torch.empty_like(normed)
+    for t in range(len(tokens)):
+        s = DECAY * s + normed[t].to(s.dtype)
+        mixed[t] = (s @ weights["toy.layers.1.mix.weight"].to(dt).to(s.dtype).t()).to(dt)
+    normed, residual = P.add_rms_norm(mixed, residual, weights["toy.layers.1.post_attention_layernorm.weight"], EPS, dt)
+    hidden = P.swiglu(normed, weights["toy.layers.1.mlp.gate_proj.weight"], weights["toy.layers.1.mlp.up_proj.weight"],
+                      weights["toy.layers.1.mlp.down_proj.weight"], dt)
+    hidden, residual = attn_block(0, hidden, residual, write_to=2)
+    hidden, residual = attn_block(2, hidden, residual, read_from=0)
+    hf, _ = P.add_rms_norm(hidden, residual, weights["toy.norm.weight"], EPS, dt)
+    return P.linear(hf, weights["toy.embed.weight"], dt).double().numpy()
+
+
+@pytest.fixture(scope="module")
+def toy_folder(tmp_path_factory):
+    register_toy()
+    from vllm_oxide_b200.engine.loading import write_random_model_folder
+    folder = str(tmp_path_factory.mktemp("toy"))
+    write_random_model_folder(folder, dict(architectures=["ToyDecayForCausalLM"]), 11, "fan_in", torch.float32)
+    return folder
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_steps_like_its_plain_form(toy_folder, dtype):
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    _, weights = P.read_folder(toy_folder)
+    g = torch.Generator().manual_seed(4)
+    a = torch.randint(0, V, (75,), generator=g).tolist()
+    b = torch.randint(0, V, (40,), generator=g).tolist()
+    dt = torch.float64 if dtype == "float32" else torch.bfloat16
+    want_a, want_b = plain_toy(weights, a, dt), plain_toy(weights, b, dt)
+
+    def close(got, want, what):
+        scale = np.abs(want).max()
+        worst = np.abs(np.asarray(got, np.float64) - want).max() / scale
+        assert worst < (2e-5 if dtype == "float32" else 0.04), f"{what}: {worst:.3e}"
+
+    r = TraceRunner(toy_folder, dtype, 128, 16)
+    assert len(r.cache.planes) == 3 and r.cache.planes[1] is None and r.cache.states[1].shape[1:] == (H,)
+    assert r.cache.states[0] is None and len(r.cache.groups) == 1 and r.cache.groups[0].planes == [0, 2]
+    close(r.step([dict(id="a", tokens=a, want=list(range(75)))], ["a"]), want_a, "whole")
+    # in portions, mixed with a second request whose state lives in another slot; b reuses a's slot later
+    r = TraceRunner(toy_folder, dtype, 128, 16)
+    got_a, got_b = [], []
+    got_a.append(r.step([dict(id="a", tokens=a[:30], want=list(range(30)))], []))
+    out = r.step([dict(id="a", tokens=a[30:33], want=[0, 1, 2]), dict(id="b", tokens=b[:17], want=list(range(17)))], [])
+    got_a.append(out[:3]); got_b.append(out[3:])
+    for t in range(33, 75):
+        out = r.step([dict(id="a", tokens=[a[t]], want=[0])] + ([dict(id="b", tokens=[b[t - 16]], want=[0])] if t - 16 < 40 else []),
+                     ["a"] if t == 74 else [])
+        got_a.append(out[:1])
+        if out.shape[0] > 1:
+            got_b.append(out[1:])
+    close(np.concatenate(got_a), want_a, "portions a")
+    close(np.concatenate(got_b), want_b[:len(np.concatenate(got_b))], "portions b")
+    # a new request takes the slot that a gave back: its state must start from zero
+    c = r.step([dict(id="c", tokens=b, want=list(range(40)))], ["c"])
+    close(c, want_b, "state slot used again")
+
+
+def test_unknown_parts_and_bad_orders_are_refused():
+    register_toy()
+    from vllm_oxide_b200.models import ExecStep, ModelPlan
+    from vllm_oxide_b200.parts import PartSpec, build_part, known_parts
+    assert "toy_decay" in known_parts("mixer") and "attention" in known_parts("mixer")
+    with pytest.raises(KeyError, match="no mixer part of kind 'nope'"):
+        build_part("mixer", PartSpec("nope"))
+    plan = ModelPlan("x", 8, 8, 8, "e", None, PartSpec("rmsnorm"), {}, [PartSpec("pre_norm")],
+                     [ExecStep(0, 0, write_cache=False)])
+    with pytest.raises(ValueError, match="before any run has written"):
+        plan.validate()
+    plan.order = [ExecStep(0, 0), ExecStep(0, 0)]
+    with pytest.raises(ValueError, match="written by two runs"):
+        plan.validate()

@@ -144,6 +144,19 @@ PYBIND11_MODULE(_host, m) {
       .def("schedule", &Scheduler::schedule)
       .def("postprocess", &Scheduler::postprocess)
       .def("last_entries", &Scheduler::last_entries)
+      // For every scheduled request that wants logits, in entry order:
+      // (id, generated so far, temperature, top_k, top_p, seed, has penalties).
+      .def("sample_requests", [](const Scheduler& s) {
+        std::vector<std::tuple<int64_t, int, float, int, float, uint64_t, bool>> out;
+        for (const auto& e : s.last_entries()) {
+          if (!e.wants_logits) continue;
+          const Sequence& q = s.sequence(e.id);
+          const SamplingParams& p = q.params;
+          out.emplace_back(q.id, q.num_generated(), p.temperature, p.top_k, p.top_p, p.seed,
+                           p.presence_penalty != 0.f || p.frequency_penalty != 0.f || p.repetition_penalty != 0.f);
+        }
+        return out;
+      })
       // The scheduled portions as batch entries (tokens taken from the sequences; a request that
       // wants logits asks for its last place).
       .def("batch_entries", [](const Scheduler& s) {

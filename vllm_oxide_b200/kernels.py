@@ -40,7 +40,12 @@ def lib():
     return _lib
 
 
+launch_count = 0   # launches of this package's own kernels since import (bench.py reports the difference)
+
+
 def _check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if code != 0:
         raise KernelError(f"{what}: {lib().vob_error_string(code).decode()} (code {code})")
 

@@ -215,6 +215,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (reported)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one phase and print its time only (for short profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate on candle: no Rust toolchain or "
@@ -239,6 +241,13 @@ def main() -> int:
                          max_num_seqs=max(max_batch, 8), max_num_batched_tokens=8192, dtype="bfloat16")
     llm = LLM.from_config(cfg, opts, seed=0, init_scheme="0.02")
 
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "ms": prefill_run(llm, PROMPT_LEN, reps=1, warmup=1)}))
+        return 0
+    if args.only == "decode":
+        ms, launches, _ = decode_run(llm, args.batch, steps, warmup, PROMPT_LEN)
+        print(json.dumps({"only": "decode", "ms_per_step": ms, "gpu_launches": launches}))
+        return 0
     prefill_ms = prefill_run(llm, PROMPT_LEN)
     with ClockSampler() as clocks:
         ms, launches, mean_ctx = decode_run(llm, args.batch, steps, warmup, PROMPT_LEN)

@@ -267,6 +267,110 @@ def test_attention_generic_does_not_depend_on_the_batch():
     assert torch.equal(out[1:4].cpu(), a_got)
 
 
+def decode_attention(num_splits):
+    def fn(q, out, kc, vc, bt, cu_q, ctx, T, nh, kvh, hd, window, err, **_):
+        from vllm_oxide_b200 import kernels
+        B = ctx.shape[0]
+        n = kernels.attention_decode_scratch_floats(hd, B, nh, num_splits)
+        scratch = torch.full((max(n, 1),), float("nan"), device=DEV)
+        kernels.attention_decode(q.reshape(T, nh * hd), nh * hd, out, kc, vc, bt, cu_q, ctx, B, nh, kvh, hd, window,
+                                 1.0 / math.sqrt(hd), num_splits, scratch if n else None, err)
+    return fn
+
+
+DECODE_CASES = [  # nh, kvh, hd, block_size, window, ctx_lens, splits
+    (32, 8, 128, 256, 0, [2048, 1, 700, 64, 65, 63], 4),
+    (16, 8, 128, 16, 0, [300, 129], 1),
+    (6, 1, 32, 32, 0, [100, 5, 31, 32, 33], 3),
+    (4, 2, 16, 16, 0, [40, 1, 17], 2),
+    (3, 3, 48, 16, 24, [100, 24, 25, 3], 2),
+    (16, 1, 64, 64, 0, [513, 77], 5),
+    (8, 2, 256, 64, 100, [400, 99, 101], 3),
+    (5, 5, 80, 48, 0, [200], 7),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_CASES)
+def test_attention_decode(case):
+    nh, kvh, hd, bs, window, ctx_lens, splits = case
+    got, want = run_attention(decode_attention(splits), torch.bfloat16, nh, kvh, hd, bs, window, [1] * len(ctx_lens), ctx_lens)
+    assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("key_pos,window,expect_hit", [(3, 0, True), (255, 0, True), (256, 0, True), (511, 0, True),
+                                                       (800 - 64, 64, True), (800 - 65, 64, False), (799, 0, True)])
+def test_attention_decode_reads_the_right_far_key(key_pos, window, expect_hit):
+    got, want = run_attention(decode_attention(4), torch.bfloat16, 8, 2, 64, 16, window, [1], [800], craft=craft_spike(key_pos))
+    assert torch.allclose(got, want, atol=3e-2)
+    assert (got.mean() > 4.9) == expect_hit
+
+
+def prefill_attention(q, out, kc, vc, bt, cu_q, ctx, T, nh, kvh, hd, window, err, **_):
+    from vllm_oxide_b200 import kernels
+    B = ctx.shape[0]
+    max_q = int((cu_q[1:] - cu_q[:-1]).max())
+    kernels.attention_prefill(q.reshape(T, nh * hd), nh * hd, out, kc, vc, bt, cu_q, ctx, B, max_q, nh, kvh, hd, window,
+                              1.0 / math.sqrt(hd), err)
+
+
+PREFILL_CASES = [  # nh, kvh, hd, block_size, window, q_lens, ctx_lens
+    (32, 8, 128, 256, 0, [300, 2, 64], [300, 2, 700]),
+    (16, 8, 128, 16, 0, [17, 130], [80, 130]),
+    (6, 1, 32, 32, 0, [5, 31, 32, 33, 100], [5, 31, 40, 33, 228]),
+    (4, 2, 16, 16, 0, [40, 2, 17], [40, 19, 17]),
+    (3, 3, 48, 16, 24, [30, 2, 70], [61, 24, 170]),
+    (16, 1, 64, 64, 0, [65, 3], [513, 77]),
+    (8, 2, 256, 64, 100, [150, 20], [400, 99]),
+    (5, 5, 80, 48, 7, [50], [50]),
+]
+
+
+@pytest.mark.parametrize("case", PREFILL_CASES)
+def test_attention_prefill(case):
+    nh, kvh, hd, bs, window, q_lens, ctx_lens = case
+    got, want = run_attention(prefill_attention, torch.bfloat16, nh, kvh, hd, bs, window, q_lens, ctx_lens)
+    assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("key_pos,window,expect_hit", [(3, 0, True), (63, 0, True), (64, 0, True), (791, 0, True),
+                                                       (792 - 63, 64, True), (792 - 64, 64, False)])
+def test_attention_prefill_reads_the_right_far_key(key_pos, window, expect_hit):
+    """Eight queries at positions 792..799: the first one decides whether the key is inside its window."""
+    got, want = run_attention(prefill_attention, torch.bfloat16, 8, 2, 64, 16, window, [8], [800], craft=craft_spike(key_pos))
+    assert torch.allclose(got, want, atol=3e-2)
+    assert (got[0].mean() > 4.9) == expect_hit
+
+
+def test_attention_decode_and_prefill_share_a_mixed_batch():
+    def both(q, out, kc, vc, bt, token_req, positions, cu_q, ctx, T, nh, kvh, hd, window, err, **_):
+        out.fill_(777.0)
+        decode_attention(2)(q=q, out=out, kc=kc, vc=vc, bt=bt, cu_q=cu_q, ctx=ctx, T=T, nh=nh, kvh=kvh, hd=hd,
+                            window=window, err=err)
+        assert (out[1:6] == 777).all() and (out[0] != 777).all() and (out[6] != 777).all()
+        prefill_attention(q=q, out=out, kc=kc, vc=vc, bt=bt, cu_q=cu_q, ctx=ctx, T=T, nh=nh, kvh=kvh, hd=hd,
+                          window=window, err=err)
+
+    got, want = run_attention(both, torch.bfloat16, 12, 4, 64, 16, 0, [1, 5, 1], [90, 40, 130])
+    assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_decode_leaves_portions_to_the_other_kernel():
+    """In a mixed batch the decode kernel writes only the rows of one-token requests; the plain kernel,
+    told to skip those, writes the rest; together they give the whole batch."""
+    from vllm_oxide_b200 import kernels
+
+    def both(q, out, kc, vc, bt, token_req, positions, cu_q, ctx, T, nh, kvh, hd, window, err, **_):
+        out.fill_(777.0)
+        decode_attention(3)(q=q, out=out, kc=kc, vc=vc, bt=bt, cu_q=cu_q, ctx=ctx, T=T, nh=nh, kvh=kvh, hd=hd,
+                            window=window, err=err)
+        assert (out[1:6] == 777).all() and (out[0] != 777).all() and (out[6] != 777).all()
+        kernels.paged_attention_generic(q.reshape(T, nh * hd), nh * hd, out, kc, vc, bt, token_req, positions, T, nh, kvh,
+                                        hd, window, 1.0 / math.sqrt(hd), err, skip_single_cu_q=cu_q)
+
+    got, want = run_attention(both, torch.bfloat16, 8, 4, 64, 16, 0, [1, 5, 1], [90, 40, 130])
+    assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 331, 80), (65, 130, 200), (200, 64, 4097)])
 def test_gemm_f32(M, N, K):
     from vllm_oxide_b200 import kernels

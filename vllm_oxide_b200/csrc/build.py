@@ -88,9 +88,16 @@ def host_sources():
     return [os.path.join(d, f) for f in sorted(os.listdir(d)) if f.endswith((".cpp", ".hpp"))]
 
 
-def kernel_sources():
+# Sources compiled once per head size (-DVOB_HD=<n>) into a library of their own.
+PER_HEAD_DIM = ("attention_decode.cu", "attention_prefill.cu")
+DEFAULT_HEAD_DIMS = (64, 128)
+
+
+def kernel_sources(per_head_dim: bool = False):
     d = os.path.join(_HERE, "kernels")
-    return [os.path.join(d, f) for f in sorted(os.listdir(d)) if f.endswith((".cu", ".cuh", ".h"))]
+    names = [f for f in sorted(os.listdir(d)) if f.endswith((".cu", ".cuh", ".h"))]
+    names = [f for f in names if not f.endswith(".cu") or (f in PER_HEAD_DIM) == per_head_dim]
+    return [os.path.join(d, f) for f in names]
 
 
 def host_library_path() -> str:
@@ -99,6 +106,10 @@ def host_library_path() -> str:
 
 def kernel_library_path() -> str:
     return os.path.join(_PKG, "libvob_kernels.so")
+
+
+def attention_library_path(head_dim: int) -> str:
+    return os.path.join(_PKG, f"libvob_attn_hd{head_dim}.so")
 
 
 def build_host(force: bool = False) -> str:
@@ -125,48 +136,60 @@ def build_host(force: bool = False) -> str:
         return out
 
 
-def build_kernels(force: bool = False) -> str:
+def _build_cuda_library(out: str, srcs, tag: str, defines, what: str, force: bool) -> str:
     with _LOCK:
         os.makedirs(_BUILD, exist_ok=True)
-        out = kernel_library_path()
-        srcs = kernel_sources()
+        flags = NVCC_FLAGS + list(defines)
         headers = [s for s in srcs if not s.endswith(".cu")]
         cus = [s for s in srcs if s.endswith(".cu")]
-        header_hash = _hash_files(headers, " ".join(NVCC_FLAGS))
-        nvcc = None
+        header_hash = _hash_files(headers, " ".join(flags))
         todo, objs, stamps = [], [], []
         for cu in cus:
-            obj = os.path.join(_BUILD, os.path.basename(cu)[:-3] + ".o")
+            obj = os.path.join(_BUILD, os.path.basename(cu)[:-3] + tag + ".o")
             objs.append(obj)
             stamp = _hash_files([cu], header_hash)
             stamps.append(stamp)
             if force or not os.path.isfile(obj) or _read(obj + ".stamp") != stamp:
                 todo.append((cu, obj, stamp))
         link_stamp = hashlib.sha256("".join(stamps).encode()).hexdigest()
-        if not todo and os.path.isfile(out) and _read(os.path.join(_BUILD, "kernels.stamp")) == link_stamp:
+        link_stamp_path = os.path.join(_BUILD, os.path.basename(out) + ".stamp")
+        if not todo and os.path.isfile(out) and _read(link_stamp_path) == link_stamp:
             return out
         nvcc = _nvcc()
         if todo:
-            _log(f"compiling {len(todo)} CUDA source file(s) for sm_100a (first call only) ...")
+            _log(f"compiling {len(todo)} CUDA source file(s) of {what} for sm_100a (first call only) ...")
 
             def compile_one(item):
                 cu, obj, stamp = item
-                _run([nvcc, *NVCC_FLAGS, f"-I{os.path.join(_HERE, 'kernels')}", "-c", cu, "-o", obj],
-                     os.path.basename(cu))
+                _run([nvcc, *flags, f"-I{os.path.join(_HERE, 'kernels')}", "-c", cu, "-o", obj], os.path.basename(cu))
                 with open(obj + ".stamp", "w") as f:
                     f.write(stamp)
                 _log(f"compiled {os.path.basename(cu)}")
             with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
                 list(ex.map(compile_one, todo))
         tmp = out + f".tmp{os.getpid()}"
-        _run([nvcc, "-shared", "-o", tmp, *objs, "-lcudart"], "libvob_kernels.so (link)")
+        _run([nvcc, "-shared", "-o", tmp, *objs, "-lcudart"], os.path.basename(out) + " (link)")
         os.replace(tmp, out)
-        with open(os.path.join(_BUILD, "kernels.stamp"), "w") as f:
+        with open(link_stamp_path, "w") as f:
             f.write(link_stamp)
-        _log("CUDA kernels ready")
+        _log(f"{what} ready")
         return out
+
+
+def build_kernels(force: bool = False) -> str:
+    return _build_cuda_library(kernel_library_path(), kernel_sources(False), "", [], "the CUDA kernels", force)
+
+
+def build_attention(head_dim: int, force: bool = False) -> str:
+    """The tensor-core attention kernels for one head size (a multiple of 16, at most 256)."""
+    if head_dim % 16 or not 16 <= head_dim <= 256:
+        raise BuildError(f"the tensor-core attention kernels take head sizes in steps of 16 up to 256, not {head_dim}")
+    return _build_cuda_library(attention_library_path(head_dim), kernel_sources(True), f"_hd{head_dim}",
+                               [f"-DVOB_HD={head_dim}"], f"the attention kernels for head size {head_dim}", force)
 
 
 def build_all(force: bool = False) -> None:
     build_host(force)
     build_kernels(force)
+    for hd in DEFAULT_HEAD_DIMS:
+        build_attention(hd, force)

@@ -1,0 +1,201 @@
+// Decode attention over the paged cache in bfloat16: one query token per request, keys split
+// over several blocks, the query heads of a key/value head processed together.
+//
+// Grid (split, kv head, request), 128 threads.  A block owns a contiguous range of the keys the
+// query may read (lo..pos, lo = max(0, pos - window + 1)), walks it in tiles of 64 keys brought
+// into shared memory with cp.async (3 stages; every cache row is found through the block table,
+// so any page size works), and each of its 4 warps takes 16 keys of a tile: Q.K^T and P.V run on
+// tensor cores (m16n8k16) with the group's query heads as the 16 rows, the softmax is online in
+// float.  The warps are merged through shared memory; with several splits the block writes a
+// normalised partial result and its log-sum-exp to scratch memory, and a second kernel merges the
+// splits.  Requests that bring more than one token are skipped (the prefill kernel takes them).
+// Compiled once per head size (-DVOB_HD).
+#include "attention_mma.cuh"
+
+namespace vob {
+
+constexpr int DEC_TILE = 64;   // keys per tile
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_STAGES = HD <= 128 ? 3 : 2;
+constexpr int DEC_STAGE_BYTES = 2 * DEC_TILE * ROW_BYTES;   // K tile, then V tile
+
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __nv_bfloat16* __restrict__ out,
+                        const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
+                        const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
+                        const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
+                        long num_pages, float* __restrict__ part_o, float* __restrict__ part_lse, int* err) {
+  extern __shared__ __align__(16) char smem[];
+  const int split = blockIdx.x, num_splits = gridDim.x, kh = blockIdx.y, b = blockIdx.z;
+  const int t = cu_q[b];
+  if (cu_q[b + 1] - t != 1) return;                    // not a decoding request
+  const int G = nh / kvh;
+  const int pos = context_lens[b] - 1;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int n_keys = pos + 1 - lo;
+  const int chunk = ((n_keys + num_splits - 1) / num_splits + DEC_TILE - 1) / DEC_TILE * DEC_TILE;
+  const int start = lo + split * chunk;
+  const int end = min(pos + 1, start + chunk);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const int* table = block_tables + (size_t)b * table_stride;
+
+  // the group's query heads as rows 0..G-1 of a 16-row tile (other rows zero), in A-fragment layout
+  uint32_t qf[KSTEPS][4];
+  {
+    const __nv_bfloat16* qrow0 = q + (size_t)t * q_stride + (size_t)(kh * G + g) * HD;
+    const __nv_bfloat16* qrow1 = qrow0 + (size_t)8 * HD;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      const int d = ks * 16 + tq * 2;
+      qf[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + d) : 0u;
+      qf[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + d) : 0u;
+      qf[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + d + 8) : 0u;
+      qf[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + d + 8) : 0u;
+    }
+  }
+  WarpSoftmax st;
+  st.clear();
+  const float sc = scale * LOG2E;
+  const int n_tiles = start < end ? (end - start + DEC_TILE - 1) / DEC_TILE : 0;
+#pragma unroll
+  for (int s = 0; s < DEC_STAGES - 1; ++s) {
+    if (s < n_tiles)
+      load_kv_tile<DEC_TILE, DEC_WARPS * 32>(smem + s * DEC_STAGE_BYTES, kcache, vcache, table, block_size, kvh, kh, start + s * DEC_TILE, start, end,
+                       num_pages, err);
+    cp_async_commit();
+  }
+  for (int it = 0; it < n_tiles; ++it) {
+    const int nxt = it + DEC_STAGES - 1;
+    if (nxt < n_tiles)
+      load_kv_tile<DEC_TILE, DEC_WARPS * 32>(smem + (nxt % DEC_STAGES) * DEC_STAGE_BYTES, kcache, vcache, table, block_size, kvh, kh,
+                       start + nxt * DEC_TILE, start, end, num_pages, err);
+    cp_async_commit();
+    cp_async_wait<DEC_STAGES - 1>();
+    __syncthreads();
+    const char* stage = smem + (it % DEC_STAGES) * DEC_STAGE_BYTES;
+    const int k0 = start + it * DEC_TILE + warp * 16;
+    if (k0 < end) {
+      float s[2][4];
+      qk_16keys(qf, stage + warp * 16 * ROW_BYTES, lane, s);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int key = k0 + i * 8 + tq * 2;
+        s[i][0] = key < end ? s[i][0] * sc : -INFINITY;
+        s[i][1] = key + 1 < end ? s[i][1] * sc : -INFINITY;
+        s[i][2] = key < end ? s[i][2] * sc : -INFINITY;
+        s[i][3] = key + 1 < end ? s[i][3] * sc : -INFINITY;
+      }
+      softmax_pv_16keys(st, s, stage + DEC_TILE * ROW_BYTES + warp * 16 * ROW_BYTES, lane);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // merge the warps: shared memory now holds, per warp, m[16], l[16] and o[16][HD]
+  float* wm = reinterpret_cast<float*>(smem);                 // [DEC_WARPS][16]
+  float* wl = wm + DEC_WARPS * 16;                            // [DEC_WARPS][16]
+  float* wo = wl + DEC_WARPS * 16;                            // [DEC_WARPS][16][HD]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 1);
+    st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 2);
+  }
+  if (tq == 0) {
+    wm[warp * 16 + g] = st.m[0]; wm[warp * 16 + g + 8] = st.m[1];
+    wl[warp * 16 + g] = st.l[0]; wl[warp * 16 + g + 8] = st.l[1];
+  }
+#pragma unroll
+  for (int j = 0; j < DTILES; ++j) {
+    float* r0 = wo + ((size_t)warp * 16 + g) * HD + j * 8 + tq * 2;
+    float* r1 = wo + ((size_t)warp * 16 + g + 8) * HD + j * 8 + tq * 2;
+    r0[0] = st.o[j][0]; r0[1] = st.o[j][1];
+    r1[0] = st.o[j][2]; r1[1] = st.o[j][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32) {
+    const int r = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, wm[w * 16 + r]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float f = wm[w * 16 + r] == -INFINITY ? 0.f : exp2f(wm[w * 16 + r] - M);
+      L += wl[w * 16 + r] * f;
+      O += wo[((size_t)w * 16 + r) * HD + d] * f;
+    }
+    const float val = L > 0.f ? O / L : 0.f;
+    const int head = kh * G + r;
+    if (num_splits == 1) {
+      out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(val);
+    } else {
+      const size_t p = ((size_t)b * nh + head) * num_splits + split;
+      part_o[p * HD + d] = val;
+      if (d == 0) part_lse[p] = L > 0.f ? M + log2f(L) : -INFINITY;
+    }
+  }
+}
+
+// Merges the splits of every (decoding request, head): weights 2^(lse - max lse).
+__global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                                __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q, int nh,
+                                                int num_splits) {
+  const int b = blockIdx.y, head = blockIdx.x;
+  const int t = cu_q[b];
+  if (cu_q[b + 1] - t != 1) return;
+  const size_t base = ((size_t)b * nh + head) * num_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_lse[base + s]);
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float W = 0.f, O = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float lse = part_lse[base + s];
+      const float w = lse == -INFINITY ? 0.f : exp2f(lse - M);
+      W += w;
+      O += w * part_o[(base + s) * HD + d];
+    }
+    out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(W > 0.f ? O / W : 0.f);
+  }
+}
+
+}  // namespace vob
+
+using namespace vob;
+
+VOB_API int vob_attention_decode_head_dim() { return HD; }
+
+// Floats of scratch memory a launch with these sizes needs (0 with one split).
+VOB_API long vob_attention_decode_scratch_floats(int num_requests, int nh, int num_splits) {
+  return num_splits > 1 ? (long)num_requests * nh * num_splits * (HD + 1) : 0;
+}
+
+// q rows of q_stride elements (head h at h*HD); out [T, nh*HD]; caches [num_pages, block_size, kvh, HD];
+// block_tables [B, table_stride]; cu_q [B+1]; context_lens [B]; scratch: see above.
+VOB_API int vob_attention_decode(const void* q, long q_stride, void* out, const void* kcache, const void* vcache,
+                                 const int* block_tables, int table_stride, const int* cu_q, const int* context_lens,
+                                 int num_requests, int nh, int kvh, int block_size, int window, float scale,
+                                 long num_pages, int num_splits, float* scratch, int* err, cudaStream_t stream) {
+  if (num_requests <= 0) return 0;
+  if (kvh <= 0 || nh % kvh || nh / kvh > 16 || block_size <= 0 || num_splits < 1 || num_splits > 65535) return VOB_UNSUPPORTED;
+  if (num_splits > 1 && !scratch) return VOB_BAD_ARGUMENT;
+  static bool configured = false;
+  const int merge_bytes = (2 * DEC_WARPS * 16 + DEC_WARPS * 16 * HD) * (int)sizeof(float);
+  const int smem = DEC_STAGES * DEC_STAGE_BYTES > merge_bytes ? DEC_STAGES * DEC_STAGE_BYTES : merge_bytes;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  float* part_o = scratch;
+  float* part_lse = scratch ? scratch + (size_t)num_requests * nh * num_splits * HD : nullptr;
+  dim3 grid(num_splits, kvh, num_requests);
+  attention_decode_kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(
+      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,
+      block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, part_o, part_lse, err);
+  int rc = launch_status();
+  if (rc || num_splits == 1) return rc;
+  attention_decode_combine_kernel<<<dim3(nh, num_requests), HD < 128 ? 64 : 128, 0, stream>>>(
+      part_o, part_lse, (__nv_bfloat16*)out, cu_q, nh, num_splits);
+  return launch_status();
+}

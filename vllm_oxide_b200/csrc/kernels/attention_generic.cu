@@ -56,8 +56,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 paged_attention_generic_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ out,
                                const T* __restrict__ kcache, const T* __restrict__ vcache,
                                const int* __restrict__ block_tables, int table_stride,
-                               const int* __restrict__ token_req, const int* __restrict__ positions, int nh, int kvh,
-                               int hd, int block_size, int window, float scale, long num_pages, int* err) {
+                               const int* __restrict__ token_req, const int* __restrict__ positions,
+                               const int* __restrict__ skip_single_cu_q, int nh, int kvh, int hd, int block_size,
+                               int window, float scale, long num_pages, int* err) {
   extern __shared__ float smem[];
   float* qs = smem;                        // [hd]
   float* accs = smem + hd;                 // [ATT_WARPS][hd]
@@ -65,6 +66,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, long q_stride, T* __rest
   const int t = blockIdx.x, h = blockIdx.y;
   const int req = token_req[t];
   if (req < 0) return;
+  if (skip_single_cu_q && skip_single_cu_q[req + 1] - skip_single_cu_q[req] == 1) return;  // the decode kernel's
   const int pos = positions[t];
   const int kh = h / (nh / kvh);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -143,7 +145,8 @@ using namespace vob;
 // block_tables [B, table_stride]; token_req [T] (-1: padding); positions [T].
 VOB_API int vob_paged_attention_generic(const void* q, long q_stride, void* out, const void* kcache, const void* vcache,
                                         const int* block_tables, int table_stride, const int* token_req,
-                                        const int* positions, int T, int nh, int kvh, int hd, int block_size,
+                                        const int* positions, const int* skip_single_cu_q, int T, int nh, int kvh, int hd,
+                                        int block_size,
                                         int window, float scale, long num_pages, int dtype, int* err,
                                         cudaStream_t stream) {
   if (T <= 0) return 0;
@@ -153,12 +156,12 @@ VOB_API int vob_paged_attention_generic(const void* q, long q_stride, void* out,
   if (dtype == VOB_F32)
     paged_attention_generic_kernel<float><<<grid, ATT_WARPS * 32, smem, stream>>>(
         (const float*)q, q_stride, (float*)out, (const float*)kcache, (const float*)vcache, block_tables, table_stride,
-        token_req, positions, nh, kvh, hd, block_size, window, scale, num_pages, err);
+        token_req, positions, skip_single_cu_q, nh, kvh, hd, block_size, window, scale, num_pages, err);
   else if (dtype == VOB_BF16)
     paged_attention_generic_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache,
-        (const __nv_bfloat16*)vcache, block_tables, table_stride, token_req, positions, nh, kvh, hd, block_size, window,
-        scale, num_pages, err);
+        (const __nv_bfloat16*)vcache, block_tables, table_stride, token_req, positions, skip_single_cu_q, nh, kvh, hd,
+        block_size, window, scale, num_pages, err);
   else
     return VOB_BAD_ARGUMENT;
   return launch_status();

@@ -55,8 +55,22 @@ class StepContext:
         return self.host[off:off + sizes[name]]
 
 
+GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
+
+
+class _DecodeGraph:
+    """One captured decode step for a padded batch size: its layout, buffers, graph and logits."""
+
+    def __init__(self, layout, ws, dev):
+        self.layout, self.ws, self.dev = layout, ws, dev
+        self.graph = None
+        self.logits = None
+        self.launches = 0     # this package's kernel launches inside the graph
+
+
 class EngineCore:
-    def __init__(self, model, cache: PagedCache, max_num_batched_tokens: int, max_num_seqs: int, max_model_len: int):
+    def __init__(self, model, cache: PagedCache, max_num_batched_tokens: int, max_num_seqs: int, max_model_len: int,
+                 use_graphs: bool = True):
         self.model, self.cache = model, cache
         self.device = model.device
         self.manager = cache.manager
@@ -72,6 +86,11 @@ class EngineCore:
         model.bind(cache.planes, cache.states)
         self._copied = torch.cuda.Event() if torch.device(self.device).type == "cuda" else None
         self.h2d_bytes_last = 0
+        # Steps in which every request brings one token are replayed from CUDA graphs, one per padded
+        # batch size, when every part of the model launches the same kernels whatever the batch holds.
+        self.use_graphs = bool(use_graphs and getattr(model, "graph_safe", False))
+        self._graphs = {}
+        self.graph_replays = 0
 
     # ---- building a step
     def build_context(self, entries: Sequence["host.BatchEntry"]) -> StepContext:
@@ -95,11 +114,74 @@ class EngineCore:
         self.h2d_bytes_last = layout.total * 4
         return StepContext(layout, self._dev_buf, self._host_np, counts, self.ws, self.err)
 
+    # ---- decode steps from CUDA graphs
+    def _graph_bucket(self, entries) -> Optional[int]:
+        if not self.use_graphs or any(len(e.tokens) != 1 for e in entries):
+            return None
+        for b in GRAPH_BUCKETS:
+            if b >= len(entries):
+                return b if b <= max(self.max_seqs, 1) * 2 else None
+        return None
+
+    def _fill_fixed(self, g: _DecodeGraph, entries) -> "host.BatchCounts":
+        if self._copied is not None:
+            self._copied.synchronize()
+        counts = host.fill_step_batch(self.manager, list(entries), g.layout, self._host_np)
+        L = g.layout
+        fresh = [int(s) for s, f in zip(self._host_np[L.state_slots:L.state_slots + counts.num_requests],
+                                        self._host_np[L.state_fresh:L.state_fresh + counts.num_requests]) if f]
+        self.cache.zero_states(fresh)
+        g.dev[:L.total].copy_(self._host_buf[:L.total], non_blocking=True)
+        if self._copied is not None:
+            self._copied.record()
+        self.h2d_bytes_last = L.total * 4
+        return counts
+
+    def _graph_context(self, g: _DecodeGraph, counts) -> StepContext:
+        ctx = StepContext(g.layout, g.dev, self._host_np, counts, g.ws, self.err,
+                          launch_tokens=g.layout.T, launch_rows=g.layout.R)
+        # what the host knows of a decode step must not depend on the step, or the capture would bake it in
+        ctx.num_decode = ctx.num_requests = g.layout.B
+        ctx.max_q, ctx.max_context = 1, self.max_model_len
+        return ctx
+
+    def _run_graph(self, bucket: int, entries) -> torch.Tensor:
+        g = self._graphs.get(bucket)
+        if g is None:
+            layout = host.BatchLayout(bucket, bucket, bucket, self.num_groups, self.max_pages)
+            g = _DecodeGraph(layout, Workspace(bucket, self.device, self.model.dtype),
+                             torch.empty(layout.total, dtype=torch.int32, device=self.device))
+            counts = self._fill_fixed(g, entries)
+            ctx = self._graph_context(g, counts)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):          # once outside capture: buffers, library handles, attributes
+                hidden, residual = self.model.forward(ctx)
+                self.model.compute_logits(hidden, residual, ctx)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g.graph = torch.cuda.CUDAGraph()
+            before = kernels.launch_count
+            with torch.cuda.graph(g.graph):
+                hidden, residual = self.model.forward(ctx)
+                g.logits = self.model.compute_logits(hidden, residual, ctx)
+            g.launches = kernels.launch_count - before
+            self._graphs[bucket] = g
+        else:
+            counts = self._fill_fixed(g, entries)
+        g.graph.replay()
+        kernels.launch_count += g.launches
+        self.graph_replays += 1
+        return g.logits[:counts.num_rows]
+
     # ---- one step
     def run(self, entries: Sequence["host.BatchEntry"]) -> torch.Tensor:
         """Float32 logits [wanted rows, vocab] in the order of the entries and of their `want`."""
         if not entries:
             return torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
+        bucket = self._graph_bucket(entries)
+        if bucket is not None:
+            return self._run_graph(bucket, entries)
         ctx = self.build_context(entries)
         hidden, residual = self.model.forward(ctx)
         if ctx.num_rows == 0:

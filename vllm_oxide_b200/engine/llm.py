@@ -74,7 +74,8 @@ class LLM:
                              f"max_position_embeddings {plan.max_position}")
         o = self.options
         self.cache = self._make_cache()
-        self.core = EngineCore(self.model, self.cache, o.max_num_batched_tokens, o.max_num_seqs, o.max_model_len)
+        self.core = EngineCore(self.model, self.cache, o.max_num_batched_tokens, o.max_num_seqs, o.max_model_len,
+                               use_graphs=not o.enforce_eager)
         eos = plan.eos_token_id if plan.eos_token_id is not None else -1
         self.scheduler = host.Scheduler(self.cache.manager, o.max_num_batched_tokens, o.max_num_seqs, o.max_model_len, eos)
         self.sampler = Sampler(device, min(o.max_num_seqs, 512))
@@ -112,7 +113,7 @@ class LLM:
         pages = n_req * ((per_req + o.block_size - 1) // o.block_size)
         cache = PagedCache(self.model.cache_specs(), self.model.state_specs(), self.dtype, self.device, o.block_size,
                            pages, max(n_req, 1), prefix_caching=False)
-        core = EngineCore(self.model, cache, n_req * per_req, max(n_req, 1), o.max_model_len)
+        core = EngineCore(self.model, cache, n_req * per_req, max(n_req, 1), o.max_model_len, use_graphs=False)
         entries = []
         for r in range(n_req):
             cache.manager.add_request(r)

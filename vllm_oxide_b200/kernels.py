@@ -40,6 +40,26 @@ def lib():
     return _lib
 
 
+_attn_libs = {}
+
+
+def attention_lib(head_dim: int):
+    """The tensor-core attention library for one head size, built at first use."""
+    if head_dim not in _attn_libs:
+        try:
+            L = ctypes.CDLL(_build.build_attention(head_dim))
+        except (OSError, _build.BuildError) as e:
+            raise KernelError(f"the attention kernels for head size {head_dim} are not available: {e}") from e
+        L.vob_attention_decode_scratch_floats.restype = ctypes.c_long
+        _attn_libs[head_dim] = L
+    return _attn_libs[head_dim]
+
+
+def has_fast_attention(dtype, head_dim: int, group: int) -> bool:
+    """Whether the tensor-core attention kernels take this case; the plain kernel takes the rest."""
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256 and group <= 16
+
+
 launch_count = 0   # launches of this package's own kernels since import (bench.py reports the difference)
 
 
@@ -111,13 +131,41 @@ def qk_norm_rope_kv_write(qkv, bias, positions, slots, wq, wk, cos_sin, kcache, 
 
 
 def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, token_req, positions, num_tokens, nh, kvh,
-                            hd, window: int, scale: float, err) -> None:
+                            hd, window: int, scale: float, err, skip_single_cu_q=None) -> None:
+    """Every token of the batch; with `skip_single_cu_q` (the batch's cu_q) the tokens of requests that
+    bring exactly one token are left to the decode kernel."""
     _cuda(q, out, kcache, vcache, block_tables, token_req, positions)
     _check(lib().vob_paged_attention_generic(_p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache),
                                              _p(block_tables), block_tables.shape[-1], _p(token_req), _p(positions),
-                                             num_tokens, nh, kvh, hd, kcache.shape[1], window, ctypes.c_float(scale),
-                                             ctypes.c_long(kcache.shape[0]), _code(q.dtype), _p(err), _stream()),
-           "paged_attention_generic")
+                                             _p(skip_single_cu_q), num_tokens, nh, kvh, hd, kcache.shape[1], window,
+                                             ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), _code(q.dtype),
+                                             _p(err), _stream()), "paged_attention_generic")
+
+
+def attention_decode_scratch_floats(head_dim: int, num_requests: int, nh: int, num_splits: int) -> int:
+    return int(attention_lib(head_dim).vob_attention_decode_scratch_floats(num_requests, nh, num_splits))
+
+
+def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, nh, kvh, hd,
+                     window: int, scale: float, num_splits: int, scratch, err) -> None:
+    """Requests that bring exactly one token; the others are skipped."""
+    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, scratch)
+    assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    _check(attention_lib(hd).vob_attention_decode(
+        _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables), block_tables.shape[-1],
+        _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[1], window, ctypes.c_float(scale),
+        ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(err), _stream()), "attention_decode")
+
+
+def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, max_q, nh, kvh,
+                      hd, window: int, scale: float, err) -> None:
+    """Requests that bring more than one token; the others are skipped."""
+    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens)
+    assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    _check(attention_lib(hd).vob_attention_prefill(
+        _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables), block_tables.shape[-1],
+        _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, kcache.shape[1], window, ctypes.c_float(scale),
+        ctypes.c_long(kcache.shape[0]), _p(err), _stream()), "attention_prefill")
 
 
 def gemm_f32(a, w, out, bias=None) -> None:

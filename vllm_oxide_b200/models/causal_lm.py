@@ -29,6 +29,7 @@ class CausalLM:
         common = dict(positions=self.positions, dtype=dtype, device=device)
         self.blocks = [build_part("block", spec, **common) for spec in plan.layers]
         self.final_norm = build_part("norm", plan.final_norm, **common)
+        self.graph_safe = all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
         self.embedding = None
         self.lm_head = None
         self.planes: List[Optional[CachePlane]] = [None] * plan.num_planes()

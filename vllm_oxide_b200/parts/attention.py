@@ -21,6 +21,8 @@ from .linear import linear
 
 
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, eps: float,
                  qkv_bias: bool, qk_norm: bool, window: Optional[int], position: str, prefix: str,
                  positions: dict, dtype, device, **_):
@@ -87,9 +89,32 @@ class Attention(Mixer):
         return linear(attn, self.wo, ctx.ws.get("attn_proj", T, self.H, x.dtype))
 
     def attend(self, qkv, q_stride, out, cache, ctx, T):
-        kernels.paged_attention_generic(qkv, q_stride, out, cache.k, cache.v, ctx.block_tables[cache.group],
-                                        ctx.token_req, ctx.positions, T, self.nh, self.kvh, self.hd, self.window,
-                                        self.scale, ctx.err)
+        """bfloat16: decoding requests (one token) go to the split-key tensor-core kernel, requests with a
+        portion to the tensor-core kernel for portions.  The 32-bit path, and sizes those kernels refuse,
+        go to the plain kernel."""
+        tables = ctx.block_tables[cache.group]
+        if not kernels.has_fast_attention(qkv.dtype, self.hd, self.nh // self.kvh):
+            kernels.paged_attention_generic(qkv, q_stride, out, cache.k, cache.v, tables, ctx.token_req, ctx.positions, T,
+                                            self.nh, self.kvh, self.hd, self.window, self.scale, ctx.err)
+            return
+        B = ctx.launch_requests
+        if ctx.num_decode > 0:
+            keys = ctx.max_context if self.window == 0 else min(ctx.max_context, self.window)
+            splits = decode_splits(B, self.kvh, keys)
+            n = kernels.attention_decode_scratch_floats(self.hd, B, self.nh, splits)
+            scratch = ctx.ws.get_flat("attention_decode_scratch", n, torch.float32) if n else None
+            kernels.attention_decode(qkv, q_stride, out, cache.k, cache.v, tables, ctx.cu_q, ctx.context_lens, B, self.nh,
+                                     self.kvh, self.hd, self.window, self.scale, splits, scratch, ctx.err)
+        if ctx.max_q > 1:
+            kernels.attention_prefill(qkv, q_stride, out, cache.k, cache.v, tables, ctx.cu_q, ctx.context_lens, B,
+                                      ctx.max_q, self.nh, self.kvh, self.hd, self.window, self.scale, ctx.err)
+
+
+def decode_splits(num_requests: int, kv_heads: int, max_keys: int) -> int:
+    """Splits of the key range per (request, kv head): enough blocks to fill 148 SMs about four times over,
+    but at least 128 keys per split."""
+    want = -(-592 // max(1, num_requests * kv_heads))
+    return max(1, min(want, -(-max_keys // 128)))
 
 
 register_part("mixer", "attention", Attention)

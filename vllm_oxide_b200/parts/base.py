@@ -91,11 +91,24 @@ class Workspace:
             self._buffers[key] = buf
         return buf[:rows]
 
+    def get_flat(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """Scratch memory of a kernel: a flat buffer that grows on demand."""
+        key = (name, 0, dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < numel:
+            buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:numel]
+
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
 
 
 class Part:
+    # True when forward() launches the same kernels, with the same arguments, whatever the step's batch
+    # holds (everything that varies is read on the device): such a part can be captured in a CUDA graph.
+    graph_safe = False
+
     def tensor_specs(self) -> List[TensorSpec]:
         return []
 

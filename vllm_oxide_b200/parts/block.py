@@ -22,6 +22,7 @@ class PreNormBlock(Block):
         self.post_mixer_norm = build_part("norm", post_mixer_norm, **common)
         self.feed_forward = build_part("feed_forward", feed_forward, **common)
         self._parts = [self.input_norm, self.mixer, self.post_mixer_norm, self.feed_forward]
+        self.graph_safe = all(p.graph_safe for p in self._parts)
 
     def tensor_specs(self) -> List[TensorSpec]:
         return [s for p in self._parts for s in p.tensor_specs()]

@@ -13,6 +13,8 @@ from .linear import linear
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, **_):
         self.H, self.I, self.prefix = hidden_size, intermediate_size, prefix
         self.wgu = self.wdown = None

@@ -11,6 +11,8 @@ from .base import Norm, register_part
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     """(y, residual') = (RMSNorm(x + residual) * w, x + residual); with residual None, residual' = x.
 
     The residual buffer is updated in place.  With `rows` the norm is computed only for those

@@ -199,3 +199,51 @@ VOB_API int vob_attention_decode(const void* q, long q_stride, void* out, const 
       part_o, part_lse, (__nv_bfloat16*)out, cu_q, nh, num_splits);
   return launch_status();
 }
+
+// ------------------------------------------------------------------------------------------------
+// The same computation for callers that cannot allocate: see attention_decode_noalloc.h.
+#include "attention_decode_noalloc.h"
+
+namespace vob {
+// Partial results of the split-key kernel, inside the library.  In host code this name is only a
+// stand-in for the symbol, never a device address: the address is looked up below.
+static __device__ __align__(256) float g_decode_noalloc_scratch[VOB_DECODE_NOALLOC_MAX_FLOATS];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_decode_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+}  // namespace vob
+
+VOB_API long vob_attention_decode_noalloc_max_floats(void) { return VOB_DECODE_NOALLOC_MAX_FLOATS; }
+
+VOB_API const char* vob_attention_decode_noalloc_error(int code) {
+  if (code == VOB_NOALLOC_TOO_LARGE)
+    return "vob_attention_decode_noalloc: num_requests * nh * num_splits * (head size + 1) floats exceed the built-in "
+           "scratch array (VOB_DECODE_NOALLOC_MAX_FLOATS); use fewer splits or vob_attention_decode with your own scratch";
+  if (code == VOB_NOALLOC_NO_DEVICE) return "vob_attention_decode_noalloc: the current device index is out of range";
+  if (code == VOB_BAD_ARGUMENT) return "vob_attention_decode_noalloc: bad argument";
+  if (code == VOB_UNSUPPORTED) return "vob_attention_decode_noalloc: size not supported by the decode kernel";
+  return cudaGetErrorString((cudaError_t)code);
+}
+
+VOB_API int vob_attention_decode_noalloc(const void* q, long q_stride, void* out, const void* kcache, const void* vcache,
+                                         const int* block_tables, int table_stride, const int* cu_q,
+                                         const int* context_lens, int num_requests, int nh, int kvh, int block_size,
+                                         int window, float scale, long num_pages, int num_splits, int* err,
+                                         cudaStream_t stream) {
+  if (num_requests <= 0) return 0;
+  if (num_splits < 1 || nh <= 0) return VOB_BAD_ARGUMENT;
+  const long need = vob_attention_decode_scratch_floats(num_requests, nh, num_splits);
+  if (need > VOB_DECODE_NOALLOC_MAX_FLOATS) return VOB_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return VOB_NOALLOC_NO_DEVICE;
+  if (!g_decode_noalloc_ptr[dev]) {   // set-up, once per device, with that device current
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_decode_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_decode_noalloc_ptr[dev] = ptr;
+  }
+  return vob_attention_decode(q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q, context_lens,
+                              num_requests, nh, kvh, block_size, window, scale, num_pages, num_splits,
+                              g_decode_noalloc_ptr[dev], err, stream);
+}

@@ -33,9 +33,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __nv
   const int pos = context_lens[b] - 1;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int n_keys = pos + 1 - lo;
-  const int chunk = ((n_keys + num_splits - 1) / num_splits + DEC_TILE - 1) / DEC_TILE * DEC_TILE;
-  const int start = lo + split * chunk;
-  const int end = min(pos + 1, start + chunk);
+  // the key range in tiles of 64 from lo; split s takes tiles [s*n/S, (s+1)*n/S): within one tile of each other
+  const int all_tiles = (n_keys + DEC_TILE - 1) / DEC_TILE;
+  const int tile_begin = (int)((long)split * all_tiles / num_splits);
+  const int tile_end = (int)((long)(split + 1) * all_tiles / num_splits);
+  const int start = lo + tile_begin * DEC_TILE;
+  const int end = min(pos + 1, lo + tile_end * DEC_TILE);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int* table = block_tables + (size_t)b * table_stride;

@@ -39,7 +39,35 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
 // in place unless a row list is given); y = round_T(s / sqrt(mean(s^2) + eps)) * w, the
 // product rounded to T once more.  With `rows`, output row r is computed from source row
 // rows[r] and the residual is left untouched (used for the last norm, on wanted rows only).
-template <typename T, int NT>
+template <typename T> struct Vec16;
+template <> struct Vec16<float> { static constexpr int N = 4; };
+template <> struct Vec16<__nv_bfloat16> { static constexpr int N = 8; };
+
+template <typename T> __device__ __forceinline__ void load16(const T* p, float (&v)[Vec16<T>::N]);
+template <> __device__ __forceinline__ void load16<float>(const float* p, float (&v)[4]) {
+  const float4 r = *reinterpret_cast<const float4*>(p);
+  v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+}
+template <> __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 r = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+}
+template <typename T> __device__ __forceinline__ void store16(T* p, const float (&v)[Vec16<T>::N]);
+template <> __device__ __forceinline__ void store16<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 r;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+  *reinterpret_cast<uint4*>(p) = r;
+}
+
+// VEC: 16-byte accesses (the row width must be a multiple of 16 bytes); otherwise one element at a time.
+template <typename T, int NT, bool VEC>
 __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const float* __restrict__ w, T* __restrict__ y,
                                    const int* __restrict__ rows, int H, int num_src_rows, float eps, int has_residual,
                                    int* err) {
@@ -56,18 +84,45 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const f
   }
   const T* xr = x + (size_t)src * H;
   T* rr = residual + (size_t)src * H;
+  T* yr = y + (size_t)r * H;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += NT) {
-    float s = to_f<T>(xr[i]);
-    if (has_residual) s += to_f<T>(rr[i]);
-    srow[i] = s;
-    ss += s * s;
-    if (!rows) rr[i] = from_f<T>(s);
+  if (VEC) {
+    constexpr int N = Vec16<T>::N;
+    for (int i = threadIdx.x * N; i < H; i += NT * N) {
+      float s[N];
+      load16<T>(xr + i, s);
+      if (has_residual) {
+        float q[N];
+        load16<T>(rr + i, q);
+#pragma unroll
+        for (int j = 0; j < N; ++j) s[j] += q[j];
+      }
+#pragma unroll
+      for (int j = 0; j < N; ++j) { srow[i + j] = s[j]; ss += s[j] * s[j]; }
+      if (!rows) store16<T>(rr + i, s);
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += NT) {
+      float s = to_f<T>(xr[i]);
+      if (has_residual) s += to_f<T>(rr[i]);
+      srow[i] = s;
+      ss += s * s;
+      if (!rows) rr[i] = from_f<T>(s);
+    }
   }
   const float total = block_sum<NT>(ss, scratch);
   const float denom = sqrtf(total / (float)H + eps);
-  T* yr = y + (size_t)r * H;
-  for (int i = threadIdx.x; i < H; i += NT) yr[i] = from_f<T>(round_to<T>(srow[i] / denom) * w[i]);
+  if (VEC) {
+    constexpr int N = Vec16<T>::N;
+    for (int i = threadIdx.x * N; i < H; i += NT * N) {
+      float o[N];
+#pragma unroll
+      for (int j = 0; j < N; ++j) o[j] = round_to<T>(srow[i + j] / denom) * w[i + j];
+      store16<T>(yr + i, o);
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += NT) yr[i] = from_f<T>(round_to<T>(srow[i] / denom) * w[i]);
+  }
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
@@ -194,12 +249,18 @@ static int add_rmsnorm_launch(const void* x, void* residual, const float* w, voi
   constexpr int NT = 256;
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return VOB_UNSUPPORTED;
+  const bool vec = ((size_t)H * sizeof(T)) % 16 == 0 && ((uintptr_t)x | (uintptr_t)residual | (uintptr_t)y) % 16 == 0;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                        : cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  add_rmsnorm_kernel<T, NT><<<n_out, NT, smem, stream>>>((const T*)x, (T*)residual, w, (T*)y, rows, H, num_src_rows, eps,
-                                                         has_residual, err);
+  if (vec)
+    add_rmsnorm_kernel<T, NT, true><<<n_out, NT, smem, stream>>>((const T*)x, (T*)residual, w, (T*)y, rows, H, num_src_rows,
+                                                                 eps, has_residual, err);
+  else
+    add_rmsnorm_kernel<T, NT, false><<<n_out, NT, smem, stream>>>((const T*)x, (T*)residual, w, (T*)y, rows, H, num_src_rows,
+                                                                  eps, has_residual, err);
   return launch_status();
 }
 

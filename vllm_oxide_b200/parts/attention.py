@@ -111,10 +111,11 @@ class Attention(Mixer):
 
 
 def decode_splits(num_requests: int, kv_heads: int, max_keys: int) -> int:
-    """Splits of the key range per (request, kv head): enough blocks to fill 148 SMs about four times over,
-    but at least 128 keys per split."""
-    want = -(-592 // max(1, num_requests * kv_heads))
-    return max(1, min(want, -(-max_keys // 128)))
+    """Splits of the key range per (request, kv head): as many as keep every block resident at once
+    (two blocks per SM on 148 SMs), but at least two 64-key tiles per split."""
+    tiles = -(-max_keys // 64)
+    fit = (2 * 148) // max(1, num_requests * kv_heads)
+    return max(1, min(fit, tiles // 2))
 
 
 register_part("mixer", "attention", Attention)

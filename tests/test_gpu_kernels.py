@@ -81,6 +81,15 @@ def test_silu_mul(dtype):
     ref = ((g.to(it) / (1 + torch.exp(-g.to(it)))).to(dtype) * u)
     assert torch.allclose(out.cpu().float(), ref.float(), **tol(dtype))
     assert out[0, 0].abs() < 1e-6 and out[0, 1] == 0
+    if I % 8 == 0 or True:
+        I2 = 336
+        gu2 = (4 * torch.randn(T, 2 * I2, device=DEV)).to(dtype)
+        out2 = torch.empty(T, I2, dtype=dtype, device=DEV)
+        kernels.silu_mul(gu2, out2, T, interleaved=True)
+        v = gu2.cpu().reshape(T, I2 // 8, 2, 8)
+        g2, u2 = v[:, :, 0].reshape(T, I2), v[:, :, 1].reshape(T, I2)
+        ref2 = ((g2.float() / (1 + torch.exp(-g2.float()))).to(dtype) * u2)
+        assert torch.allclose(out2.cpu().float(), ref2.float(), **tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -448,3 +457,57 @@ def test_copy_pages():
     pairs = torch.tensor([[0, 4], [2, 5]], dtype=torch.int32, device=DEV)
     kernels.copy_pages(plane, pairs, 2)
     assert torch.equal(plane[4], before[0]) and torch.equal(plane[5], before[2]) and torch.equal(plane[:4], before[:4])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 16, 16), (8, 4096, 4096), (3, 331, 80), (16, 24576 // 8, 512), (9, 100, 272),
+                                   (5, 517, 96), (16, 48, 12288), (2, 151936 // 16, 1024), (4, 40, 200), (11, 70, 8)])
+def test_gemm_skinny(M, N, K):
+    from vllm_oxide_b200 import kernels
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().to(DEV)
+    assert kernels.gemm_skinny_supported(x, w)
+    err = err_word()
+    ref = x.double() @ w.double().t()
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_skinny(x, w, out, kernels.EPI_BF16, err)
+    assert torch.allclose(out.double(), ref, rtol=1e-2, atol=1e-2)
+    assert torch.equal(out, ref.float().bfloat16()) or (out.double() - ref).abs().max() < 0.02     # one rounding of a float sum
+    outf = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.gemm_skinny(x, w, outf, kernels.EPI_F32, err)
+    assert torch.equal(outf, out.float())                                  # float logits are the bfloat16 values
+    # a strided view (rows of a wider buffer) is taken too
+    wide = torch.zeros(M, K + 64, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = x
+    out2 = torch.empty_like(out)
+    kernels.gemm_skinny(wide[:, :K], w, out2, kernels.EPI_BF16, err)
+    assert torch.equal(out2, out) and err.item() == 0
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 8, 16), (8, 12288 // 4, 1024), (7, 104, 80), (16, 200, 96), (12, 64, 4096)])
+def test_gemm_skinny_swiglu(M, I, K):
+    from vllm_oxide_b200 import kernels
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    wg = (2 * torch.randn(I, K, generator=g) / math.sqrt(K)).bfloat16()
+    wu = (torch.randn(I, K, generator=g) / math.sqrt(K)).bfloat16()
+    one = torch.eye(I).bfloat16()
+    want = P.swiglu(x, wg, wu, one, torch.bfloat16)          # down = identity: the activation itself
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = err_word()
+    if I % 8:
+        return      # the fused activation needs groups of eight outputs
+    wgu = torch.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], dim=1).reshape(2 * I, K)
+    kernels.gemm_skinny(x.to(DEV), wgu.to(DEV), out, kernels.EPI_SWIGLU, err)
+    assert torch.allclose(out.cpu().float(), want.float(), rtol=2e-2, atol=2e-2) and err.item() == 0
+
+
+def test_gemm_skinny_refuses_what_it_cannot_take():
+    from vllm_oxide_b200 import kernels
+    x = torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV)
+    assert not kernels.gemm_skinny_supported(x, w)
+    assert not kernels.gemm_skinny_supported(x[:4, 4:44], w[:, 4:44])      # rows that start off a 16-byte boundary
+    assert not kernels.gemm_skinny_supported(x[:4].float(), w.float())
+    with pytest.raises(kernels.KernelError, match="not supported"):
+        kernels.gemm_skinny(x, w, torch.zeros(17, 8, dtype=torch.bfloat16, device=DEV), kernels.EPI_BF16, err_word())

@@ -119,4 +119,11 @@ def test_merged_rows_order():
     ffn = build_part("feed_forward", PartSpec("swiglu", dict(hidden_size=8, intermediate_size=12, prefix="m.")))
     t = {s.name: torch.full(s.shape, float(i + 1)) for i, s in enumerate(ffn.tensor_specs())}
     ffn.load(t)
-    assert ffn.wgu.shape == (24, 8) and ffn.wgu[0, 0] == 1 and ffn.wgu[12, 0] == 2
+    assert ffn.wgu.shape == (24, 8) and ffn.wgu[0, 0] == 1 and ffn.wgu[12, 0] == 2 and not ffn.interleaved
+    # an intermediate size that is a multiple of 8 is stored as groups of 8 gate rows + the 8 up rows of the same outputs
+    ffn = build_part("feed_forward", PartSpec("swiglu", dict(hidden_size=4, intermediate_size=16, prefix="m.")))
+    t = {s.name: torch.arange(s.shape[0], dtype=torch.float32)[:, None].expand(s.shape) + 100 * i
+         for i, s in enumerate(ffn.tensor_specs())}
+    ffn.load(t)
+    assert ffn.interleaved and ffn.wgu[:, 0].tolist() == ([0, 1, 2, 3, 4, 5, 6, 7] + [100 + r for r in range(8)]
+                                                           + [8 + r for r in range(8)] + [108 + r for r in range(8)])

@@ -126,13 +126,17 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const f
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
+// gu holds, per token, either I gate values then I up values, or (interleaved) groups of sixteen columns:
+// eight gate values and the eight up values of the same outputs.
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved) {
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
     const int i = (int)(idx - t * I);
-    const float g = to_f<T>(gu[t * 2 * I + i]);
-    const float u = to_f<T>(gu[t * 2 * I + I + i]);
+    const int gi = interleaved ? (i >> 3) * 16 + (i & 7) : i;
+    const int ui = interleaved ? gi + 8 : I + i;
+    const float g = to_f<T>(gu[t * 2 * I + gi]);
+    const float u = to_f<T>(gu[t * 2 * I + ui]);
     const float s = round_to<T>(g / (1.f + expf(-g)));
     out[idx] = from_f<T>(s * u);
   }
@@ -275,14 +279,15 @@ VOB_API int vob_add_rmsnorm(const void* x, void* residual, const float* w, void*
   return VOB_BAD_ARGUMENT;
 }
 
-VOB_API int vob_silu_mul(const void* gu, void* out, int T, int I, int dtype, cudaStream_t stream) {
+VOB_API int vob_silu_mul(const void* gu, void* out, int T, int I, int interleaved, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (interleaved && I % 8) return VOB_BAD_ARGUMENT;
   const size_t total = (size_t)T * I;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (dtype == VOB_F32)
-    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, I, total);
+    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, I, total, interleaved);
   else if (dtype == VOB_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
+    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total, interleaved);
   else
     return VOB_BAD_ARGUMENT;
   return launch_status();

@@ -1,0 +1,265 @@
+// out[M,N] = x[M,K] * W[N,K]^T in bfloat16 for decode-sized batches (M <= 16): a weight-streaming
+// kernel.  The time of such a product is the time to read W once, so everything serves that read:
+//
+//   * persistent blocks (two per SM) walk 16-row tiles of W; a producer thread streams each tile, 256
+//     columns per stage, with TMA (cp.async.bulk.tensor through tensor maps: four [16 x 64] boxes of W
+//     and four of the tokens per stage, 128-byte swizzled, completion counted on an mbarrier) into a
+//     ring of 6-8 stages, running ahead across tile boundaries, so the copies never stop while the
+//     other warps finish a tile; rows and columns beyond the matrices arrive as zeros;
+//   * four consumer warps share the k-steps of a stage and multiply on tensor cores with W as the
+//     16-row operand and the tokens as the 8-wide one (m16n8k16, float accumulation), then sum
+//     their partial tiles through shared memory;
+//   * the epilogue is fused: round to bfloat16 (plain), or round and widen to float (logits), or
+//     SiLU(gate) * up with the gate and up rows of the same eight outputs in one tile, so the
+//     [M, 2*intermediate] tensor never exists.  Rounding follows the reference: the product is
+//     rounded to bfloat16 once; SiLU is rounded, then the product with `up` is rounded.
+//
+// Every wait on an mbarrier is bounded: a wait that runs out sets an error bit and a block-wide
+// abort flag; the block then waits (bounded again) for the copies it still has in flight and returns.
+#include "tensor_map.cuh"
+
+#define VOB_ERR_TIMEOUT 32
+
+namespace vob {
+
+constexpr int SK_KC = 256;                 // columns per stage
+constexpr int SK_SLICES = SK_KC / TMA_BOX_COLS;   // boxes of 64 columns per stage
+constexpr int SK_CONSUMERS = 4;
+constexpr int SK_THREADS = (SK_CONSUMERS + 1) * 32;
+constexpr unsigned SK_SPIN_LIMIT = 1u << 22;
+
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// False when the wait ran out (or another thread of the block gave up before).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int* err) {
+  for (unsigned i = 0; i < SK_SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicOr(err, VOB_ERR_TIMEOUT);
+  return false;
+}
+__device__ __forceinline__ void sk_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void sk_ldmatrix_x2(uint32_t (&r)[2], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void sk_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+template <int MT> struct SkStages { static constexpr int N = MT == 8 ? 8 : 6; };
+
+// tmW: W [N, K] with box [16, 64]; tmX: x [M, K] with box [MT, 64].  EPI_BF16 / EPI_F32: out [M, N] (row
+// stride ldo).  EPI_SWIGLU: the rows of W alternate in groups of eight between gate and up (gate rows
+// 8i..8i+7 of the original at 16i..16i+7, the up rows of the same outputs at 16i+8..16i+15), so a 16-row tile
+// holds both; out [M, N/2].
+template <int MT, int EPI>
+__global__ void __launch_bounds__(SK_THREADS, 2)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, void* __restrict__ out,
+                   long ldo, int M, int N, int K, int num_tiles, int* err) {
+  constexpr int S = SkStages<MT>::N;
+  constexpr int W_SLICE = 16 * 128, X_SLICE = MT * 128;
+  constexpr int STAGE_BYTES = SK_SLICES * (W_SLICE + X_SLICE);
+  extern __shared__ __align__(1024) char smem_raw[];
+  char* stages = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  float* red = reinterpret_cast<float*>(stages + S * STAGE_BYTES);          // [SK_CONSUMERS][16][MT]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + SK_CONSUMERS * 16 * MT);
+  uint64_t* empty = full + S;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + S);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_iters = (K + SK_KC - 1) / SK_KC;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], SK_CONSUMERS); }
+    *abort_flag = 0;
+    tma_prefetch_map(&tmW);
+    tma_prefetch_map(&tmX);
+  }
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  __syncthreads();
+
+  const int m_rows = M < MT ? M : MT;
+  if (warp == SK_CONSUMERS) {
+    // ------------------------------------------------ producer (one thread)
+    if (lane == 0) {
+      long it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kc = 0; kc < k_iters; ++kc, ++it) {
+          const int s = (int)(it % S);
+          if (it >= S) {
+            ok = mbar_wait(&empty[s], (unsigned)(((it / S) - 1) & 1), abort_flag, err);
+            if (!ok) break;
+          }
+          mbar_expect_tx(&full[s], (unsigned)STAGE_BYTES);
+          char* st = stages + s * STAGE_BYTES;
+#pragma unroll
+          for (int c = 0; c < SK_SLICES; ++c) {
+            tma_load_2d(st + c * W_SLICE, &tmW, kc * SK_KC + c * TMA_BOX_COLS, tile * 16, &full[s]);
+            tma_load_2d(st + SK_SLICES * W_SLICE + c * X_SLICE, &tmX, kc * SK_KC + c * TMA_BOX_COLS, 0, &full[s]);
+          }
+        }
+      }
+      // every copy this block issued must have landed before the block may exit
+      const long first = it > S ? it - S : 0;
+      for (long j = first; j < it; ++j) {
+        bool done = false;
+        for (unsigned i = 0; i < SK_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % S], (unsigned)((j / S) & 1));
+        if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+      }
+    }
+  } else {
+    // ------------------------------------------------ consumers
+    const int g = lane >> 2, tq = lane & 3;
+    const int mi = lane >> 3, r8 = lane & 7;
+    const int a_row = (mi & 1) * 8 + r8, a_chunk = mi >> 1;                       // W rows, ldmatrix x4
+    const int b_row = MT == 16 ? (mi >> 1) * 8 + r8 : r8;                         // token rows, x4 / x2
+    const int b_chunk = MT == 16 ? (mi & 1) : ((lane >> 3) & 1);
+    long it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      float acc[MT / 8][4];
+#pragma unroll
+      for (int j = 0; j < MT / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+      for (int kc = 0; kc < k_iters; ++kc, ++it) {
+        const int s = (int)(it % S);
+        bool ok = mbar_wait(&full[s], (unsigned)((it / S) & 1), abort_flag, err);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const char* st = stages + s * STAGE_BYTES;
+        const char* xt = st + SK_SLICES * W_SLICE;
+#pragma unroll
+        for (int jj = 0; jj < SK_KC / 16 / SK_CONSUMERS; ++jj) {   // columns beyond K are zeros
+          const int j = warp + jj * SK_CONSUMERS;
+          const int c = j >> 2, ch = (j & 3) * 2;
+          uint32_t a[4];
+          sk_ldmatrix_x4(a, st + c * W_SLICE + swizzled_offset(a_row, ch + a_chunk));
+          if (MT == 16) {
+            uint32_t b[4];
+            sk_ldmatrix_x4(b, xt + c * X_SLICE + swizzled_offset(b_row, ch + b_chunk));
+            sk_mma(acc[0], a, b[0], b[1]);
+            sk_mma(acc[MT / 8 - 1], a, b[2], b[3]);
+          } else {
+            uint32_t b[2];
+            sk_ldmatrix_x2(b, xt + c * X_SLICE + swizzled_offset(b_row, ch + b_chunk));
+            sk_mma(acc[0], a, b[0], b[1]);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+      }
+      // sum the four warps' partial tiles (a warp whose wait ran out still meets the others at the barriers)
+#pragma unroll
+      for (int j = 0; j < MT / 8; ++j) {
+        float* p0 = red + ((warp * 16 + g) * MT) + j * 8 + tq * 2;
+        float* p1 = red + ((warp * 16 + g + 8) * MT) + j * 8 + tq * 2;
+        p0[0] = acc[j][0]; p0[1] = acc[j][1];
+        p1[0] = acc[j][2]; p1[1] = acc[j][3];
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(SK_CONSUMERS * 32) : "memory");
+      const int tid = threadIdx.x;
+      const bool aborted = *abort_flag != 0;
+      if (aborted) {
+        // nothing is written for a tile that was not finished
+      } else if (EPI == EPI_SWIGLU) {
+        for (int idx = tid; idx < 8 * m_rows; idx += SK_CONSUMERS * 32) {
+          const int tok = idx / 8, r = idx % 8;
+          const long n = (long)tile * 8 + r;
+          if (n >= N / 2) continue;
+          float gate = 0.f, up = 0.f;
+#pragma unroll
+          for (int w = 0; w < SK_CONSUMERS; ++w) { gate += red[(w * 16 + r) * MT + tok]; up += red[(w * 16 + r + 8) * MT + tok]; }
+          gate = bf16_round(gate);
+          up = bf16_round(up);
+          const float act = bf16_round(gate / (1.f + expf(-gate)));
+          reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(act * up);
+        }
+      } else {
+        for (int idx = tid; idx < 16 * m_rows; idx += SK_CONSUMERS * 32) {
+          const int tok = idx / 16, r = idx % 16;
+          const long n = (long)tile * 16 + r;
+          if (n >= N) continue;
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < SK_CONSUMERS; ++w) v += red[(w * 16 + r) * MT + tok];
+          if (EPI == EPI_F32) reinterpret_cast<float*>(out)[(long)tok * ldo + n] = bf16_round(v);
+          else reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(v);
+        }
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(SK_CONSUMERS * 32) : "memory");
+      if (aborted) break;
+    }
+  }
+  __syncthreads();
+}
+
+template <int MT, int EPI>
+static int skinny_launch(const CUtensorMap* tmW, const CUtensorMap* tmX, void* out, long ldo, int M, int N, int K, int* err,
+                         cudaStream_t stream) {
+  constexpr int S = SkStages<MT>::N;
+  const int smem = 1024 + S * SK_SLICES * (16 + MT) * 128 + SK_CONSUMERS * 16 * MT * (int)sizeof(float) + 2 * S * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int num_tiles = (N + 15) / 16;
+  const int grid = num_tiles < 2 * 148 ? num_tiles : 2 * 148;
+  gemm_skinny_kernel<MT, EPI><<<grid, SK_THREADS, smem, stream>>>(*tmW, *tmX, out, ldo, M, N, K, num_tiles, err);
+  return launch_status();
+}
+
+}  // namespace vob
+
+using namespace vob;
+
+// Box rows the token map must have for a batch of M rows.
+VOB_API int vob_gemm_skinny_token_box(int M) { return M <= 8 ? 8 : 16; }
+
+// map_w: tensor map of W [N, K] with box rows 16; map_x: tensor map of x [M, K] with box rows
+// vob_gemm_skinny_token_box(M) (both from vob_tensor_map_bf16_2d, host memory).
+// epilogue: 0 bfloat16 out [M,N]; 1 float out [M,N] (rounded to bfloat16 first); 2 SiLU(gate)*up over rows that
+// alternate in groups of eight between gate and up, out [M,N/2] bfloat16.  Needs M <= 16.
+VOB_API int vob_gemm_skinny(const void* map_w, const void* map_x, void* out, long ldo, int M, int N, int K, int epilogue,
+                            int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16 || K <= 0 || !map_w || !map_x) return VOB_UNSUPPORTED;
+  if (epilogue == EPI_SWIGLU && N % 16) return VOB_BAD_ARGUMENT;
+  const CUtensorMap* tw = (const CUtensorMap*)map_w;
+  const CUtensorMap* tx = (const CUtensorMap*)map_x;
+  if (M <= 8) {
+    if (epilogue == EPI_BF16) return skinny_launch<8, EPI_BF16>(tw, tx, out, ldo, M, N, K, err, stream);
+    if (epilogue == EPI_F32) return skinny_launch<8, EPI_F32>(tw, tx, out, ldo, M, N, K, err, stream);
+    if (epilogue == EPI_SWIGLU) return skinny_launch<8, EPI_SWIGLU>(tw, tx, out, ldo, M, N, K, err, stream);
+  } else {
+    if (epilogue == EPI_BF16) return skinny_launch<16, EPI_BF16>(tw, tx, out, ldo, M, N, K, err, stream);
+    if (epilogue == EPI_F32) return skinny_launch<16, EPI_F32>(tw, tx, out, ldo, M, N, K, err, stream);
+    if (epilogue == EPI_SWIGLU) return skinny_launch<16, EPI_SWIGLU>(tw, tx, out, ldo, M, N, K, err, stream);
+  }
+  return VOB_BAD_ARGUMENT;
+}

@@ -1,0 +1,39 @@
+// Host side of tensor maps: encodes a CUtensorMap for a row-major bfloat16 matrix.
+// The driver's encoder is looked up at run time, so the library links against the runtime only.
+#include "tensor_map.cuh"
+
+namespace vob {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+}  // namespace vob
+
+using namespace vob;
+
+// out_map: 128 bytes, 64-byte aligned, on the host.  The box is [box_rows, 64 columns], 128-byte swizzle.
+// Needs a 16-byte aligned base, a row stride that is a multiple of 8 elements, box_rows <= 256.
+VOB_API int vob_tensor_map_bf16_2d(void* out_map, const void* base, long rows, long cols, long row_stride, int box_rows) {
+  if (!out_map || !base || rows <= 0 || cols <= 0 || box_rows <= 0 || box_rows > 256) return VOB_BAD_ARGUMENT;
+  if (((uintptr_t)base) % 16 || (row_stride * 2) % 16 || ((uintptr_t)out_map) % 64) return VOB_UNSUPPORTED;
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return VOB_UNSUPPORTED;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)TMA_BOX_COLS, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn((CUtensorMap*)out_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : VOB_BAD_ARGUMENT;
+}

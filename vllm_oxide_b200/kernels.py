@@ -24,7 +24,7 @@ DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1}
 
 ERR_BITS = {1: "a token id outside the vocabulary", 2: "a position beyond max_position_embeddings",
             4: "a cache slot outside the pool", 8: "a block-table entry that names no page",
-            16: "a wanted row outside the batch"}
+            16: "a wanted row outside the batch", 32: "a bounded wait inside a kernel ran out"}
 
 
 def lib():
@@ -114,10 +114,12 @@ def add_rmsnorm(x, residual, weight, y, eps: float, has_residual: bool, err, row
            "add_rmsnorm")
 
 
-def silu_mul(gate_up, out, num_tokens: int) -> None:
+def silu_mul(gate_up, out, num_tokens: int, interleaved: bool = False) -> None:
+    """out = SiLU(gate) * up; gate_up holds [gate | up] per token, or, interleaved, groups of 8 gate + 8 up columns."""
     _cuda(gate_up, out)
     I = out.shape[-1]
-    _check(lib().vob_silu_mul(_p(gate_up), _p(out), num_tokens, I, _code(out.dtype), _stream()), "silu_mul")
+    _check(lib().vob_silu_mul(_p(gate_up), _p(out), num_tokens, I, int(interleaved), _code(out.dtype), _stream()),
+           "silu_mul")
 
 
 def qk_norm_rope_kv_write(qkv, bias, positions, slots, wq, wk, cos_sin, kcache, vcache, num_tokens, nh, kvh, hd,
@@ -178,6 +180,53 @@ def gemm_f32(a, w, out, bias=None) -> None:
     assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
     _check(lib().vob_gemm_f32(_p(a), ctypes.c_long(a.stride(0)), _p(w), ctypes.c_long(w.stride(0)), _p(out),
                               ctypes.c_long(out.stride(0)), _p(bias), M, N, K, _stream()), "gemm_f32")
+
+
+EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
+_tensor_maps = {}
+
+
+def tensor_map(t: torch.Tensor, box_rows: int):
+    """A TMA descriptor (host memory, cached) of a row-major bfloat16 matrix with box [box_rows, 64 columns]."""
+    key = (t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows)
+    hit = _tensor_maps.get(key)
+    if hit is None:
+        raw = (ctypes.c_char * 256)()
+        addr = (ctypes.addressof(raw) + 63) & ~63
+        code = lib().vob_tensor_map_bf16_2d(ctypes.c_void_p(addr), _p(t), ctypes.c_long(t.shape[0]), ctypes.c_long(t.shape[1]),
+                                            ctypes.c_long(t.stride(0)), box_rows)
+        if code != 0:
+            raise KernelError(f"tensor map for a [{t.shape[0]}, {t.shape[1]}] matrix: {lib().vob_error_string(code).decode()}")
+        if len(_tensor_maps) > 4096:
+            _tensor_maps.clear()
+        hit = _tensor_maps[key] = (raw, ctypes.c_void_p(addr))
+    return hit[1]
+
+
+def gemm_skinny_supported(x, w) -> bool:
+    """Whether the weight-streaming kernel takes x[M,K] @ w[N,K]^T: bfloat16, M <= 16, rows that start on
+    16-byte boundaries (K need not be a multiple of anything else: the copy engine fills ragged edges with zeros)."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= 16
+            and x.stride(1) == 1 and w.stride(1) == 1 and (x.stride(0) * 2) % 16 == 0 and (w.stride(0) * 2) % 16 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(x, w, out, epilogue: int, err) -> None:
+    """out = x @ w^T for at most 16 rows of x (see gemm_skinny_supported); epilogue EPI_BF16 (out bfloat16 [M,N]),
+    EPI_F32 (out float32 [M,N], rounded to bfloat16 first) or EPI_SWIGLU (the rows of w alternate in groups of
+    eight between gate and up; out bfloat16 [M,N/2] = SiLU(gate) * up)."""
+    _cuda(x, w, out)
+    if not gemm_skinny_supported(x, w):
+        raise KernelError("gemm_skinny: this product is not supported (bfloat16, at most 16 rows, 16-byte aligned rows)")
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.stride(1) == 1 and out.shape[0] == M
+    assert out.shape[1] == (N // 2 if epilogue == EPI_SWIGLU else N)
+    assert out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16)
+    map_w = tensor_map(w, 16)
+    map_x = tensor_map(x, 8 if M <= 8 else 16)
+    _check(lib().vob_gemm_skinny(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, _p(err),
+                                 _stream()), "gemm_skinny")
 
 
 def sample(logits, temperature, top_k, top_p, keys, out, num_rows: int) -> None:

@@ -108,9 +108,12 @@ class CausalLM:
     def compute_logits(self, hidden, residual, ctx) -> torch.Tensor:
         R = ctx.launch_rows
         normed, _ = self.final_norm.forward(hidden, residual, ctx, rows=ctx.logit_rows, n_rows=R, name="final_normed")
-        logits = linear(normed, self.lm_head, ctx.ws.get_rows("logits", R, self.plan.vocab_size, self.dtype))
-        if logits.dtype == torch.float32:
-            return logits
-        out = ctx.ws.get_rows("logits_f32", R, self.plan.vocab_size, torch.float32)
-        out.copy_(logits)
+        V = self.plan.vocab_size
+        if self.dtype == torch.float32:
+            return linear(normed, self.lm_head, ctx.ws.get_rows("logits", R, V, self.dtype), ctx)
+        out = ctx.ws.get_rows("logits_f32", R, V, torch.float32)
+        if kernels.gemm_skinny_supported(normed, self.lm_head):
+            kernels.gemm_skinny(normed, self.lm_head, out, kernels.EPI_F32, ctx.err)   # rounds to bfloat16, stores float
+        else:
+            out.copy_(linear(normed, self.lm_head, ctx.ws.get_rows("logits", R, V, self.dtype), ctx))
         return out

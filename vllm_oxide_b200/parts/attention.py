@@ -79,14 +79,14 @@ class Attention(Mixer):
     def forward(self, x, ctx, cache, state=None, write_cache: bool = True):
         T = x.shape[0]
         width = (self.nh + 2 * self.kvh) * self.hd
-        qkv = linear(x, self.wqkv, ctx.ws.get("qkv", T, width, x.dtype))
+        qkv = linear(x, self.wqkv, ctx.ws.get("qkv", T, width, x.dtype), ctx)
         g = cache.group
         kernels.qk_norm_rope_kv_write(qkv, self.bqkv, ctx.positions, ctx.slot_mapping[g], self.wq_norm, self.wk_norm,
                                       self.rope.cos_sin, cache.k, cache.v, T, self.nh, self.kvh, self.hd, self.eps,
                                       write_cache, ctx.err)
         attn = ctx.ws.get("attn_out", T, self.nh * self.hd, x.dtype)
         self.attend(qkv, width, attn, cache, ctx, T)
-        return linear(attn, self.wo, ctx.ws.get("attn_proj", T, self.H, x.dtype))
+        return linear(attn, self.wo, ctx.ws.get("attn_proj", T, self.H, x.dtype), ctx)
 
     def attend(self, qkv, q_stride, out, cache, ctx, T):
         """bfloat16: decoding requests (one token) go to the split-key tensor-core kernel, requests with a

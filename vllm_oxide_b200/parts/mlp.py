@@ -18,6 +18,7 @@ class SwiGLU(FeedForward):
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, **_):
         self.H, self.I, self.prefix = hidden_size, intermediate_size, prefix
         self.wgu = self.wdown = None
+        self.interleaved = False
 
     def tensor_specs(self) -> List[TensorSpec]:
         p = self.prefix
@@ -27,16 +28,28 @@ class SwiGLU(FeedForward):
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         p = self.prefix
-        # rows of gate, then up (crates/vllm-oxide/src/layers/linear.rs:132-138)
-        self.wgu = torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]], dim=0).contiguous()
+        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        self.interleaved = self.I % 8 == 0
+        if self.interleaved:
+            # groups of eight gate rows followed by the eight up rows of the same outputs: one 16-row tile of the
+            # product then holds both halves of eight outputs, and the activation becomes the product's epilogue
+            self.wgu = torch.stack([gate.reshape(self.I // 8, 8, self.H), up.reshape(self.I // 8, 8, self.H)],
+                                   dim=1).reshape(2 * self.I, self.H).contiguous()
+        else:
+            # rows of gate, then up (crates/vllm-oxide/src/layers/linear.rs:132-138)
+            self.wgu = torch.cat([gate, up], dim=0).contiguous()
         self.wdown = tensors[p + "down_proj.weight"].contiguous()
 
     def forward(self, x, ctx):
         T = x.shape[0]
-        gu = linear(x, self.wgu, ctx.ws.get("gate_up", T, 2 * self.I, x.dtype))
         act = ctx.ws.get("act", T, self.I, x.dtype)
-        kernels.silu_mul(gu, act, T)
-        return linear(act, self.wdown, ctx.ws.get("mlp_out", T, self.H, x.dtype))
+        if self.interleaved and kernels.gemm_skinny_supported(x, self.wgu):
+            # decode-sized steps: the activation is the epilogue of the gate|up product
+            kernels.gemm_skinny(x, self.wgu, act, kernels.EPI_SWIGLU, ctx.err)
+        else:
+            gu = linear(x, self.wgu, ctx.ws.get("gate_up", T, 2 * self.I, x.dtype), ctx)
+            kernels.silu_mul(gu, act, T, self.interleaved)
+        return linear(act, self.wdown, ctx.ws.get("mlp_out", T, self.H, x.dtype), ctx)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

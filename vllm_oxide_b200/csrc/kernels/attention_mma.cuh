@@ -127,25 +127,52 @@ __device__ __forceinline__ void softmax_pv_16keys(WarpSoftmax& st, float (&s)[2]
 // Copies TILE cache rows (keys tile_start .. tile_start+TILE-1 of key/value head kh) into shared memory:
 // K rows first, V rows after them, each row found through the block table, so any page size works.
 // Rows of keys outside [begin, end) are zero-filled without a look at the block table (a window group has
-// given the pages below its window back).
+// given the pages below its window back).  A thread copies one 16-byte column of every (THREADS/CHUNKS)-th
+// row; the page of a row follows from the previous row's by stepping, without a division per row.
 template <int TILE, int THREADS>
 __device__ __forceinline__ void load_kv_tile(char* stage, const __nv_bfloat16* __restrict__ kcache,
                                              const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ table,
                                              int block_size, int kvh, int kh, int tile_start, int begin, int end,
                                              long num_pages, int* err) {
   constexpr int CHUNKS = HD / 8;                       // 16-byte chunks per row
-  for (int c = threadIdx.x; c < TILE * CHUNKS; c += THREADS) {
-    const int row = c / CHUNKS, col = c % CHUNKS;
-    const int key = tile_start + row;
-    bool valid = key >= begin && key < end;
-    long off = 0;
-    if (valid) {
-      const int page = table[key / block_size];
-      if (page < 0 || page >= num_pages) { atomicOr(err, VOB_ERR_PAGE); valid = false; }
-      else off = (((long)page * block_size + key % block_size) * kvh + kh) * HD + col * 8;
+  if constexpr (THREADS % CHUNKS == 0 && (TILE * CHUNKS) % THREADS == 0) {
+    constexpr int ROW_STEP = THREADS / CHUNKS;         // rows between two copies of a thread
+    constexpr int ITERS = TILE / ROW_STEP;
+    const int col = threadIdx.x % CHUNKS;
+    int row = threadIdx.x / CHUNKS;
+    int key = tile_start + row;
+    int page_idx = key / block_size, in_page = key - page_idx * block_size;
+    const long head_off = (long)kh * HD + col * 8;
+    const long row_elems = (long)kvh * HD;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      bool valid = key >= begin && key < end;
+      long off = 0;
+      if (valid) {
+        const int page = table[page_idx];
+        if (page < 0 || page >= num_pages) { atomicOr(err, VOB_ERR_PAGE); valid = false; }
+        else off = ((long)page * block_size + in_page) * row_elems + head_off;
+      }
+      char* dst = stage + row * ROW_BYTES + col * 16;
+      cp_async16(dst, kcache + off, valid);
+      cp_async16(dst + TILE * ROW_BYTES, vcache + off, valid);
+      row += ROW_STEP; key += ROW_STEP; in_page += ROW_STEP;
+      while (in_page >= block_size) { in_page -= block_size; ++page_idx; }
     }
-    cp_async16(stage + row * ROW_BYTES + col * 16, kcache + off, valid);
-    cp_async16(stage + TILE * ROW_BYTES + row * ROW_BYTES + col * 16, vcache + off, valid);
+  } else {
+    for (int c = threadIdx.x; c < TILE * CHUNKS; c += THREADS) {
+      const int row = c / CHUNKS, col = c % CHUNKS;
+      const int key = tile_start + row;
+      bool valid = key >= begin && key < end;
+      long off = 0;
+      if (valid) {
+        const int page = table[key / block_size];
+        if (page < 0 || page >= num_pages) { atomicOr(err, VOB_ERR_PAGE); valid = false; }
+        else off = (((long)page * block_size + key % block_size) * kvh + kh) * HD + col * 8;
+      }
+      cp_async16(stage + row * ROW_BYTES + col * 16, kcache + off, valid);
+      cp_async16(stage + TILE * ROW_BYTES + row * ROW_BYTES + col * 16, vcache + off, valid);
+    }
   }
 }
 

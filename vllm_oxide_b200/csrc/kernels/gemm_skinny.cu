@@ -1,11 +1,13 @@
 // out[M,N] = x[M,K] * W[N,K]^T in bfloat16 for decode-sized batches (M <= 16): a weight-streaming
 // kernel.  The time of such a product is the time to read W once, so everything serves that read:
 //
-//   * persistent blocks (two per SM) walk 16-row tiles of W; a producer thread streams each tile, 256
-//     columns per stage, with TMA (cp.async.bulk.tensor through tensor maps: four [16 x 64] boxes of W
-//     and four of the tokens per stage, 128-byte swizzled, completion counted on an mbarrier) into a
-//     ring of 6-8 stages, running ahead across tile boundaries, so the copies never stop while the
-//     other warps finish a tile; rows and columns beyond the matrices arrive as zeros;
+//   * persistent blocks (two per SM) walk tiles of 32 rows of W (16 when W has too few rows to give
+//     every SM a tile); a producer thread streams each tile, 256 columns per stage, with TMA
+//     (cp.async.bulk.tensor through tensor maps: four [rows x 64] boxes of W and four of the tokens per
+//     stage, 128-byte swizzled, completion counted on an mbarrier) into a ring of 4-8 stages, running
+//     ahead across tile boundaries, so the copies never stop while the other warps finish a tile; rows
+//     and columns beyond the matrices arrive as zeros.  The copy engine moves about 30 bytes per clock
+//     and SM, tokens included, so the taller tile matters: it halves the tokens' share of the copies;
 //   * four consumer warps share the k-steps of a stage and multiply on tensor cores with W as the
 //     16-row operand and the tokens as the 8-wide one (m16n8k16, float accumulation), then sum
 //     their partial tiles through shared memory;
@@ -71,23 +73,25 @@ __device__ __forceinline__ void sk_mma(float (&d)[4], const uint32_t (&a)[4], ui
 }
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
-template <int MT> struct SkStages { static constexpr int N = MT == 8 ? 8 : 6; };
+// stages of the ring: about 100 KB of shared memory per block, two blocks per SM
+template <int R, int MT> struct SkStages { static constexpr int N = (96 * 1024) / (SK_SLICES * (R + MT) * 128); };
 
-// tmW: W [N, K] with box [16, 64]; tmX: x [M, K] with box [MT, 64].  EPI_BF16 / EPI_F32: out [M, N] (row
+// tmW: W [N, K] with box [R, 64]; tmX: x [M, K] with box [MT, 64].  EPI_BF16 / EPI_F32: out [M, N] (row
 // stride ldo).  EPI_SWIGLU: the rows of W alternate in groups of eight between gate and up (gate rows
-// 8i..8i+7 of the original at 16i..16i+7, the up rows of the same outputs at 16i+8..16i+15), so a 16-row tile
-// holds both; out [M, N/2].
-template <int MT, int EPI>
+// 8i..8i+7 of the original at 16i..16i+7, the up rows of the same outputs at 16i+8..16i+15), so every 16
+// rows of a tile hold both halves of eight outputs; out [M, N/2].
+template <int R, int MT, int EPI>
 __global__ void __launch_bounds__(SK_THREADS, 2)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, void* __restrict__ out,
                    long ldo, int M, int N, int K, int num_tiles, int* err) {
-  constexpr int S = SkStages<MT>::N;
-  constexpr int W_SLICE = 16 * 128, X_SLICE = MT * 128;
+  constexpr int S = SkStages<R, MT>::N;
+  constexpr int RT = R / 16, NT = MT / 8;
+  constexpr int W_SLICE = R * 128, X_SLICE = MT * 128;
   constexpr int STAGE_BYTES = SK_SLICES * (W_SLICE + X_SLICE);
   extern __shared__ __align__(1024) char smem_raw[];
   char* stages = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  float* red = reinterpret_cast<float*>(stages + S * STAGE_BYTES);          // [SK_CONSUMERS][16][MT]
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + SK_CONSUMERS * 16 * MT);
+  float* red = reinterpret_cast<float*>(stages + S * STAGE_BYTES);          // [SK_CONSUMERS][R][MT]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + SK_CONSUMERS * R * MT);
   uint64_t* empty = full + S;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + S);
 
@@ -120,7 +124,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           char* st = stages + s * STAGE_BYTES;
 #pragma unroll
           for (int c = 0; c < SK_SLICES; ++c) {
-            tma_load_2d(st + c * W_SLICE, &tmW, kc * SK_KC + c * TMA_BOX_COLS, tile * 16, &full[s]);
+            tma_load_2d(st + c * W_SLICE, &tmW, kc * SK_KC + c * TMA_BOX_COLS, tile * R, &full[s]);
             tma_load_2d(st + SK_SLICES * W_SLICE + c * X_SLICE, &tmX, kc * SK_KC + c * TMA_BOX_COLS, 0, &full[s]);
           }
         }
@@ -142,9 +146,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const int b_chunk = MT == 16 ? (mi & 1) : ((lane >> 3) & 1);
     long it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      float acc[MT / 8][4];
+      float acc[RT][NT][4];
 #pragma unroll
-      for (int j = 0; j < MT / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+      for (int i = 0; i < RT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
       for (int kc = 0; kc < k_iters; ++kc, ++it) {
         const int s = (int)(it % S);
         bool ok = mbar_wait(&full[s], (unsigned)((it / S) & 1), abort_flag, err);
@@ -156,17 +162,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         for (int jj = 0; jj < SK_KC / 16 / SK_CONSUMERS; ++jj) {   // columns beyond K are zeros
           const int j = warp + jj * SK_CONSUMERS;
           const int c = j >> 2, ch = (j & 3) * 2;
-          uint32_t a[4];
-          sk_ldmatrix_x4(a, st + c * W_SLICE + swizzled_offset(a_row, ch + a_chunk));
+          uint32_t b[4];
           if (MT == 16) {
-            uint32_t b[4];
             sk_ldmatrix_x4(b, xt + c * X_SLICE + swizzled_offset(b_row, ch + b_chunk));
-            sk_mma(acc[0], a, b[0], b[1]);
-            sk_mma(acc[MT / 8 - 1], a, b[2], b[3]);
           } else {
-            uint32_t b[2];
-            sk_ldmatrix_x2(b, xt + c * X_SLICE + swizzled_offset(b_row, ch + b_chunk));
-            sk_mma(acc[0], a, b[0], b[1]);
+            uint32_t b2[2];
+            sk_ldmatrix_x2(b2, xt + c * X_SLICE + swizzled_offset(b_row, ch + b_chunk));
+            b[0] = b2[0]; b[1] = b2[1]; b[2] = b[3] = 0;
+          }
+#pragma unroll
+          for (int i = 0; i < RT; ++i) {
+            uint32_t a[4];
+            sk_ldmatrix_x4(a, st + c * W_SLICE + swizzled_offset(i * 16 + a_row, ch + a_chunk));
+            sk_mma(acc[i][0], a, b[0], b[1]);
+            if (MT == 16) sk_mma(acc[i][NT - 1], a, b[2], b[3]);
           }
         }
         __syncwarp();
@@ -174,38 +183,41 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       // sum the four warps' partial tiles (a warp whose wait ran out still meets the others at the barriers)
 #pragma unroll
-      for (int j = 0; j < MT / 8; ++j) {
-        float* p0 = red + ((warp * 16 + g) * MT) + j * 8 + tq * 2;
-        float* p1 = red + ((warp * 16 + g + 8) * MT) + j * 8 + tq * 2;
-        p0[0] = acc[j][0]; p0[1] = acc[j][1];
-        p1[0] = acc[j][2]; p1[1] = acc[j][3];
-      }
+      for (int i = 0; i < RT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          float* p0 = red + ((warp * R + i * 16 + g) * MT) + j * 8 + tq * 2;
+          float* p1 = red + ((warp * R + i * 16 + g + 8) * MT) + j * 8 + tq * 2;
+          p0[0] = acc[i][j][0]; p0[1] = acc[i][j][1];
+          p1[0] = acc[i][j][2]; p1[1] = acc[i][j][3];
+        }
       asm volatile("bar.sync 1, %0;\n" ::"n"(SK_CONSUMERS * 32) : "memory");
       const int tid = threadIdx.x;
       const bool aborted = *abort_flag != 0;
       if (aborted) {
         // nothing is written for a tile that was not finished
       } else if (EPI == EPI_SWIGLU) {
-        for (int idx = tid; idx < 8 * m_rows; idx += SK_CONSUMERS * 32) {
-          const int tok = idx / 8, r = idx % 8;
-          const long n = (long)tile * 8 + r;
+        for (int idx = tid; idx < (R / 2) * m_rows; idx += SK_CONSUMERS * 32) {
+          const int tok = idx / (R / 2), r = idx % (R / 2);
+          const long n = (long)tile * (R / 2) + r;
           if (n >= N / 2) continue;
+          const int gr = (r >> 3) * 16 + (r & 7);       // gate row in the tile; its up row is 8 further
           float gate = 0.f, up = 0.f;
 #pragma unroll
-          for (int w = 0; w < SK_CONSUMERS; ++w) { gate += red[(w * 16 + r) * MT + tok]; up += red[(w * 16 + r + 8) * MT + tok]; }
+          for (int w = 0; w < SK_CONSUMERS; ++w) { gate += red[(w * R + gr) * MT + tok]; up += red[(w * R + gr + 8) * MT + tok]; }
           gate = bf16_round(gate);
           up = bf16_round(up);
           const float act = bf16_round(gate / (1.f + expf(-gate)));
           reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(act * up);
         }
       } else {
-        for (int idx = tid; idx < 16 * m_rows; idx += SK_CONSUMERS * 32) {
-          const int tok = idx / 16, r = idx % 16;
-          const long n = (long)tile * 16 + r;
+        for (int idx = tid; idx < R * m_rows; idx += SK_CONSUMERS * 32) {
+          const int tok = idx / R, r = idx % R;
+          const long n = (long)tile * R + r;
           if (n >= N) continue;
           float v = 0.f;
 #pragma unroll
-          for (int w = 0; w < SK_CONSUMERS; ++w) v += red[(w * 16 + r) * MT + tok];
+          for (int w = 0; w < SK_CONSUMERS; ++w) v += red[(w * R + r) * MT + tok];
           if (EPI == EPI_F32) reinterpret_cast<float*>(out)[(long)tok * ldo + n] = bf16_round(v);
           else reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(v);
         }
@@ -217,32 +229,44 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
 }
 
-template <int MT, int EPI>
+template <int R, int MT, int EPI>
 static int skinny_launch(const CUtensorMap* tmW, const CUtensorMap* tmX, void* out, long ldo, int M, int N, int K, int* err,
                          cudaStream_t stream) {
-  constexpr int S = SkStages<MT>::N;
-  const int smem = 1024 + S * SK_SLICES * (16 + MT) * 128 + SK_CONSUMERS * 16 * MT * (int)sizeof(float) + 2 * S * 8 + 16;
+  constexpr int S = SkStages<R, MT>::N;
+  const int smem = 1024 + S * SK_SLICES * (R + MT) * 128 + SK_CONSUMERS * R * MT * (int)sizeof(float) + 2 * S * 8 + 16;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<R, MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int num_tiles = (N + 15) / 16;
+  const int num_tiles = (N + R - 1) / R;
   const int grid = num_tiles < 2 * 148 ? num_tiles : 2 * 148;
-  gemm_skinny_kernel<MT, EPI><<<grid, SK_THREADS, smem, stream>>>(*tmW, *tmX, out, ldo, M, N, K, num_tiles, err);
+  gemm_skinny_kernel<R, MT, EPI><<<grid, SK_THREADS, smem, stream>>>(*tmW, *tmX, out, ldo, M, N, K, num_tiles, err);
   return launch_status();
+}
+
+template <int R, int MT>
+static int skinny_dispatch(int epilogue, const CUtensorMap* tw, const CUtensorMap* tx, void* out, long ldo, int M, int N,
+                           int K, int* err, cudaStream_t stream) {
+  if (epilogue == EPI_BF16) return skinny_launch<R, MT, EPI_BF16>(tw, tx, out, ldo, M, N, K, err, stream);
+  if (epilogue == EPI_F32) return skinny_launch<R, MT, EPI_F32>(tw, tx, out, ldo, M, N, K, err, stream);
+  if (epilogue == EPI_SWIGLU) return skinny_launch<R, MT, EPI_SWIGLU>(tw, tx, out, ldo, M, N, K, err, stream);
+  return VOB_BAD_ARGUMENT;
 }
 
 }  // namespace vob
 
 using namespace vob;
 
+// Box rows the weight map must have for a matrix of N rows: 32, or 16 when 32-row tiles would leave SMs idle.
+VOB_API int vob_gemm_skinny_weight_box(long N) { return (N + 31) / 32 >= 148 ? 32 : 16; }
+
 // Box rows the token map must have for a batch of M rows.
 VOB_API int vob_gemm_skinny_token_box(int M) { return M <= 8 ? 8 : 16; }
 
-// map_w: tensor map of W [N, K] with box rows 16; map_x: tensor map of x [M, K] with box rows
-// vob_gemm_skinny_token_box(M) (both from vob_tensor_map_bf16_2d, host memory).
+// map_w: tensor map of W [N, K] with box rows vob_gemm_skinny_weight_box(N); map_x: tensor map of x [M, K] with box
+// rows vob_gemm_skinny_token_box(M) (both from vob_tensor_map_bf16_2d, host memory).
 // epilogue: 0 bfloat16 out [M,N]; 1 float out [M,N] (rounded to bfloat16 first); 2 SiLU(gate)*up over rows that
 // alternate in groups of eight between gate and up, out [M,N/2] bfloat16.  Needs M <= 16.
 VOB_API int vob_gemm_skinny(const void* map_w, const void* map_x, void* out, long ldo, int M, int N, int K, int epilogue,
@@ -252,14 +276,9 @@ VOB_API int vob_gemm_skinny(const void* map_w, const void* map_x, void* out, lon
   if (epilogue == EPI_SWIGLU && N % 16) return VOB_BAD_ARGUMENT;
   const CUtensorMap* tw = (const CUtensorMap*)map_w;
   const CUtensorMap* tx = (const CUtensorMap*)map_x;
-  if (M <= 8) {
-    if (epilogue == EPI_BF16) return skinny_launch<8, EPI_BF16>(tw, tx, out, ldo, M, N, K, err, stream);
-    if (epilogue == EPI_F32) return skinny_launch<8, EPI_F32>(tw, tx, out, ldo, M, N, K, err, stream);
-    if (epilogue == EPI_SWIGLU) return skinny_launch<8, EPI_SWIGLU>(tw, tx, out, ldo, M, N, K, err, stream);
-  } else {
-    if (epilogue == EPI_BF16) return skinny_launch<16, EPI_BF16>(tw, tx, out, ldo, M, N, K, err, stream);
-    if (epilogue == EPI_F32) return skinny_launch<16, EPI_F32>(tw, tx, out, ldo, M, N, K, err, stream);
-    if (epilogue == EPI_SWIGLU) return skinny_launch<16, EPI_SWIGLU>(tw, tx, out, ldo, M, N, K, err, stream);
-  }
-  return VOB_BAD_ARGUMENT;
+  const bool tall = vob_gemm_skinny_weight_box(N) == 32;
+  if (M <= 8) return tall ? skinny_dispatch<32, 8>(epilogue, tw, tx, out, ldo, M, N, K, err, stream)
+                          : skinny_dispatch<16, 8>(epilogue, tw, tx, out, ldo, M, N, K, err, stream);
+  return tall ? skinny_dispatch<32, 16>(epilogue, tw, tx, out, ldo, M, N, K, err, stream)
+              : skinny_dispatch<16, 16>(epilogue, tw, tx, out, ldo, M, N, K, err, stream);
 }

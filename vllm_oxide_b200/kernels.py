@@ -223,7 +223,7 @@ def gemm_skinny(x, w, out, epilogue: int, err) -> None:
     assert w.shape[1] == K and out.stride(1) == 1 and out.shape[0] == M
     assert out.shape[1] == (N // 2 if epilogue == EPI_SWIGLU else N)
     assert out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16)
-    map_w = tensor_map(w, 16)
+    map_w = tensor_map(w, int(lib().vob_gemm_skinny_weight_box(ctypes.c_long(N))))
     map_x = tensor_map(x, 8 if M <= 8 else 16)
     _check(lib().vob_gemm_skinny(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, _p(err),
                                  _stream()), "gemm_skinny")

@@ -106,8 +106,8 @@ def test_qk_norm_rope_kv_write(dtype, nh, kvh, hd, norm, bias):
     pos = torch.tensor([0, 1, 2, 299, 150, 7, 64, 65, 31], dtype=torch.int32, device=DEV)
     slots = torch.tensor([5, 95, 17, -1, 40, 41, 0, 63, 64], dtype=torch.int32, device=DEV)
     table = P.rope_table(hd, max_pos, theta)
-    kc = torch.full((pages, bs, kvh, hd), 7.0, device=DEV).to(dtype)
-    vc = torch.full((pages, bs, kvh, hd), 7.0, device=DEV).to(dtype)
+    kc = torch.full((pages, kvh, bs, hd), 7.0, device=DEV).to(dtype)     # [pages, kv heads, slots of a page, hd]
+    vc = torch.full((pages, kvh, bs, hd), 7.0, device=DEV).to(dtype)
     out = qkv.clone()
     err = err_word()
     kernels.qk_norm_rope_kv_write(out, b, pos, slots, wq, wk, table.to(DEV), kc, vc, T, nh, kvh, hd, eps, True, err)
@@ -123,7 +123,8 @@ def test_qk_norm_rope_kv_write(dtype, nh, kvh, hd, norm, bias):
     k = P.apply_rope(k, pos.cpu(), table, dtype)
     got_q = out[:, :nh * hd].reshape(T, nh, hd).cpu()
     assert torch.allclose(got_q.float(), q.float(), **tol(dtype))
-    kflat, vflat = kc.reshape(pages * bs, kvh, hd).cpu(), vc.reshape(pages * bs, kvh, hd).cpu()
+    kflat = kc.permute(0, 2, 1, 3).reshape(pages * bs, kvh, hd).cpu()   # by slot
+    vflat = vc.permute(0, 2, 1, 3).reshape(pages * bs, kvh, hd).cpu()
     written = torch.zeros(pages * bs, dtype=torch.bool)
     for t in range(T):
         s = int(slots[t])
@@ -155,8 +156,8 @@ def paged_setup(dtype, kvh, hd, bs, ctx_lens, g):
     perm = torch.randperm(num_pages, generator=g).tolist()
     P_max = max(pages_per)
     bt = torch.full((B, P_max), -1, dtype=torch.int32)
-    kc = torch.randn(num_pages, bs, kvh, hd, generator=g).to(dtype)   # unused slots hold noise on purpose
-    vc = torch.randn(num_pages, bs, kvh, hd, generator=g).to(dtype)
+    kc = torch.randn(num_pages, kvh, bs, hd, generator=g).to(dtype)   # unused slots hold noise on purpose
+    vc = torch.randn(num_pages, kvh, bs, hd, generator=g).to(dtype)
     ks, vs = [], []
     it = iter(perm)
     for b, c in enumerate(ctx_lens):
@@ -166,8 +167,8 @@ def paged_setup(dtype, kvh, hd, bs, ctx_lens, g):
             page = next(it)
             bt[b, p] = page
             n = min(bs, c - p * bs)
-            kc[page, :n] = k[p * bs:p * bs + n]
-            vc[page, :n] = v[p * bs:p * bs + n]
+            kc[page, :, :n] = k[p * bs:p * bs + n].transpose(0, 1)
+            vc[page, :, :n] = v[p * bs:p * bs + n].transpose(0, 1)
         ks.append(k); vs.append(v)
     return kc, vc, bt, ks, vs
 
@@ -228,7 +229,7 @@ def craft_spike(key_pos):
     """Makes one far key dominate every query's scores: the output must be that key's value."""
     def craft(q, ks, vs, kc, vc, bt, positions):
         hd = q.shape[-1]
-        bs = kc.shape[1]
+        bs = kc.shape[2]
         q[:] = 0
         q[..., 0] = 8.0
         for b in range(len(ks)):
@@ -237,8 +238,8 @@ def craft_spike(key_pos):
             vs[b][key_pos] = 5.0
             for p in range((ks[b].shape[0] + bs - 1) // bs):
                 n = min(bs, ks[b].shape[0] - p * bs)
-                kc[bt[b, p], :n] = ks[b][p * bs:p * bs + n]
-                vc[bt[b, p], :n] = vs[b][p * bs:p * bs + n]
+                kc[bt[b, p], :, :n] = ks[b][p * bs:p * bs + n].transpose(0, 1)
+                vc[bt[b, p], :, :n] = vs[b][p * bs:p * bs + n].transpose(0, 1)
     return craft
 
 
@@ -265,8 +266,8 @@ def test_attention_generic_does_not_depend_on_the_batch():
     kc2, vc2, bt2, ks2, vs2 = paged_setup(torch.float32, 2, 64, 16, [50, 200, 9], g2)
     for p in range(13):
         n = min(16, 200 - p * 16)
-        kc2[bt2[1, p], :n] = ks[0][p * 16:p * 16 + n]
-        vc2[bt2[1, p], :n] = vs[0][p * 16:p * 16 + n]
+        kc2[bt2[1, p], :, :n] = ks[0][p * 16:p * 16 + n].transpose(0, 1)
+        vc2[bt2[1, p], :, :n] = vs[0][p * 16:p * 16 + n].transpose(0, 1)
     qq = torch.cat([torch.randn(1, 4, 64, generator=g2), q, torch.randn(2, 4, 64, generator=g2)])
     token_req = torch.tensor([0, 1, 1, 1, 2, 2], dtype=torch.int32, device=DEV)
     positions = torch.tensor([49, 197, 198, 199, 7, 8], dtype=torch.int32, device=DEV)
@@ -452,7 +453,7 @@ def test_penalties_kernel():
 
 def test_copy_pages():
     from vllm_oxide_b200 import kernels
-    plane = torch.randn(6, 16, 2, 8, device=DEV)
+    plane = torch.randn(6, 2, 16, 8, device=DEV)
     before = plane.clone()
     pairs = torch.tensor([[0, 4], [2, 5]], dtype=torch.int32, device=DEV)
     kernels.copy_pages(plane, pairs, 2)

@@ -71,7 +71,7 @@ def test_attention_part(dtype, window, bias):
     att.load({k: v.to(DEV) for k, v in tensors.items()})
     assert att.cache_spec().window == (window or 0) and att.cache_spec().kv_heads == kvh
     m = manager_with([(0, 21), (1, 50)], windows=(window or 0,))
-    plane = CachePlane(torch.zeros(32, 16, kvh, hd, dtype=dtype, device=DEV), torch.zeros(32, 16, kvh, hd, dtype=dtype, device=DEV), 0, 16)
+    plane = CachePlane(torch.zeros(32, kvh, 16, hd, dtype=dtype, device=DEV), torch.zeros(32, kvh, 16, hd, dtype=dtype, device=DEV), 0, 16)
     xa, xb = torch.randn(21, Hd, generator=g).to(dtype), torch.randn(50, Hd, generator=g).to(dtype)
 
     def plain(x):
@@ -125,4 +125,4 @@ def test_a_model_may_mix_parts_layer_by_layer():
     assert [s.window for s in specs] == [0, 0, 24, 24]
     cache = PagedCache(specs, model.state_specs(), torch.float32, DEV, 16, 10, 4)
     assert [(g.window, g.planes) for g in cache.groups] == [(0, [0, 1]), (24, [2, 3])]
-    assert cache.manager.num_groups == 2 and cache.planes[2].group == 1 and cache.planes[0].k.shape == (10, 16, 3, 48)
+    assert cache.manager.num_groups == 2 and cache.planes[2].group == 1 and cache.planes[0].k.shape == (10, 3, 16, 48)

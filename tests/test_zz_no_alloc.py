@@ -28,8 +28,8 @@ def _inputs(seed, B, nh, kvh, hd, bs, ctx_lens):
     for b in range(B):
         for p in range(pages_per[b]):
             bt[b, p] = next(it)
-    kc = torch.randn(num_pages, bs, kvh, hd, generator=g).bfloat16()
-    vc = torch.randn(num_pages, bs, kvh, hd, generator=g).bfloat16()
+    kc = torch.randn(num_pages, kvh, bs, hd, generator=g).bfloat16()
+    vc = torch.randn(num_pages, kvh, bs, hd, generator=g).bfloat16()
     q = torch.randn(B, nh * hd, generator=g).bfloat16()
     cu_q = torch.arange(B + 1, dtype=torch.int32)
     ctx = torch.tensor(ctx_lens, dtype=torch.int32)

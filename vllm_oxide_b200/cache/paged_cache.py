@@ -3,8 +3,10 @@
 Planes whose mixers have the same needs (the same window) form a cache group: one page pool and
 one block table per request, managed on the host by `KvCacheManager` (C++).  The reference keeps
 one buffer [2, layers, num_blocks, block_size, kv_heads, head_dim] (vllm-oxide,
-crates/vllm-oxide/src/attention/mod.rs:42-85); here every plane has a [2, num_pages, block_size,
-kv_heads, head_dim] buffer, so planes of different widths can share a group.  The pool is sized
+crates/vllm-oxide/src/attention/mod.rs:42-85); here every plane has a [2, num_pages, kv_heads,
+block_size, head_dim] buffer: planes of different widths can share a group, and the keys of one head
+within a page are contiguous in memory (a decoding block reads one head's keys, and HBM serves long
+runs far better than 256-byte pieces).  The pool is sized
 like the reference's (crates/vllm-oxide/src/llm.rs:485-537): free memory times
 `gpu_memory_utilization`, divided by the bytes of one page in every plane, unless a page count
 is given.
@@ -59,7 +61,7 @@ class PagedCache:
                 self.planes.append(None)
                 continue
             gi = windows.index(s.window)
-            buf = torch.zeros((2, self.num_blocks, block_size, s.kv_heads, s.head_dim), dtype=dtype, device=device)
+            buf = torch.zeros((2, self.num_blocks, s.kv_heads, block_size, s.head_dim), dtype=dtype, device=device)
             self.planes.append(CachePlane(buf[0], buf[1], gi, block_size))
         self.num_state_slots = num_state_slots
         self.states: List[Optional[torch.Tensor]] = [

@@ -26,11 +26,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __nv
                         const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
                         long num_pages, float* __restrict__ part_o, float* __restrict__ part_lse, int* err) {
   extern __shared__ __align__(16) char smem[];
+  pdl_launch_dependents();
   const int split = blockIdx.x, num_splits = gridDim.x, kh = blockIdx.y, b = blockIdx.z;
   const int t = cu_q[b];
-  if (cu_q[b + 1] - t != 1) return;                    // not a decoding request
+  const int t_next = cu_q[b + 1], context = context_lens[b];   // the step's index arrays: written before the step
+  pdl_wait();                                                   // the query, and this token's key and value, are not
+  if (t_next - t != 1) return;                         // not a decoding request
   const int G = nh / kvh;
-  const int pos = context_lens[b] - 1;
+  const int pos = context - 1;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int n_keys = pos + 1 - lo;
   // the key range in tiles of 64 from lo; split s takes tiles [s*n/S, (s+1)*n/S): within one tile of each other
@@ -144,9 +147,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __nv
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                                 __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q, int nh,
                                                 int num_splits) {
+  pdl_launch_dependents();
   const int b = blockIdx.y, head = blockIdx.x;
   const int t = cu_q[b];
-  if (cu_q[b + 1] - t != 1) return;
+  const int t_next = cu_q[b + 1];
+  pdl_wait();
+  if (t_next - t != 1) return;
   const size_t base = ((size_t)b * nh + head) * num_splits;
   float M = -INFINITY;
   for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_lse[base + s]);
@@ -168,12 +174,15 @@ using namespace vob;
 
 VOB_API int vob_attention_decode_head_dim() { return HD; }
 
+// Programmatic dependent launch on (default) or off, for every kernel of this library.
+VOB_API void vob_set_pdl(int on) { pdl_enabled() = on != 0; }
+
 // Floats of scratch memory a launch with these sizes needs (0 with one split).
 VOB_API long vob_attention_decode_scratch_floats(int num_requests, int nh, int num_splits) {
   return num_splits > 1 ? (long)num_requests * nh * num_splits * (HD + 1) : 0;
 }
 
-// q rows of q_stride elements (head h at h*HD); out [T, nh*HD]; caches [num_pages, block_size, kvh, HD];
+// q rows of q_stride elements (head h at h*HD); out [T, nh*HD]; caches [num_pages, kvh, block_size, HD];
 // block_tables [B, table_stride]; cu_q [B+1]; context_lens [B]; scratch: see above.
 VOB_API int vob_attention_decode(const void* q, long q_stride, void* out, const void* kcache, const void* vcache,
                                  const int* block_tables, int table_stride, const int* cu_q, const int* context_lens,
@@ -193,14 +202,13 @@ VOB_API int vob_attention_decode(const void* q, long q_stride, void* out, const 
   float* part_o = scratch;
   float* part_lse = scratch ? scratch + (size_t)num_requests * nh * num_splits * HD : nullptr;
   dim3 grid(num_splits, kvh, num_requests);
-  attention_decode_kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(
-      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,
-      block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, part_o, part_lse, err);
-  int rc = launch_status();
+  int rc = launch_kernel(attention_decode_kernel, grid, DEC_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, q_stride,
+                         (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,
+                         table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, part_o, part_lse,
+                         err);
   if (rc || num_splits == 1) return rc;
-  attention_decode_combine_kernel<<<dim3(nh, num_requests), HD < 128 ? 64 : 128, 0, stream>>>(
-      part_o, part_lse, (__nv_bfloat16*)out, cu_q, nh, num_splits);
-  return launch_status();
+  return launch_kernel(attention_decode_combine_kernel, dim3(nh, num_requests), HD < 128 ? 64 : 128, 0, stream,
+                       (const float*)part_o, (const float*)part_lse, (__nv_bfloat16*)out, cu_q, nh, num_splits);
 }
 
 // ------------------------------------------------------------------------------------------------

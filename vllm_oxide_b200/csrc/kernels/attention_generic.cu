@@ -63,6 +63,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, long q_stride, T* __rest
   float* qs = smem;                        // [hd]
   float* accs = smem + hd;                 // [ATT_WARPS][hd]
   __shared__ float ms[ATT_WARPS], ls[ATT_WARPS];
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const int req = token_req[t];
   if (req < 0) return;
@@ -75,7 +77,6 @@ paged_attention_generic_kernel(const T* __restrict__ q, long q_stride, T* __rest
   for (int i = threadIdx.x; i < hd; i += blockDim.x) qs[i] = to_f<T>(qrow[i]);
   __syncthreads();
   const int* table = block_tables + (size_t)req * table_stride;
-  const size_t row_elems = (size_t)kvh * hd;
 
   float m = -INFINITY, l = 0.f;
   float acc[ATT_MAXD];
@@ -89,7 +90,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, long q_stride, T* __rest
     if (valid) {
       const int page = table[key / block_size];
       if (page < 0 || page >= num_pages) atomicOr(err, VOB_ERR_PAGE);
-      else row = ((long)page * block_size + key % block_size) * (long)row_elems + (long)kh * hd;
+      else row = (((long)page * kvh + kh) * block_size + key % block_size) * (long)hd;
     }
     float s = -INFINITY;
     if (row >= 0) s = dot_row<T>(qs, kcache + row, hd) * scale;
@@ -141,7 +142,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, long q_stride, T* __rest
 
 using namespace vob;
 
-// q: rows of q_stride elements, head h at h*hd; out [T, nh*hd]; caches [num_pages, block_size, kvh, hd];
+// q: rows of q_stride elements, head h at h*hd; out [T, nh*hd]; caches [num_pages, kvh, block_size, hd];
 // block_tables [B, table_stride]; token_req [T] (-1: padding); positions [T].
 VOB_API int vob_paged_attention_generic(const void* q, long q_stride, void* out, const void* kcache, const void* vcache,
                                         const int* block_tables, int table_stride, const int* token_req,
@@ -154,15 +155,13 @@ VOB_API int vob_paged_attention_generic(const void* q, long q_stride, void* out,
   dim3 grid(T, nh);
   const size_t smem = (size_t)(1 + ATT_WARPS) * hd * sizeof(float);
   if (dtype == VOB_F32)
-    paged_attention_generic_kernel<float><<<grid, ATT_WARPS * 32, smem, stream>>>(
-        (const float*)q, q_stride, (float*)out, (const float*)kcache, (const float*)vcache, block_tables, table_stride,
-        token_req, positions, skip_single_cu_q, nh, kvh, hd, block_size, window, scale, num_pages, err);
-  else if (dtype == VOB_BF16)
-    paged_attention_generic_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache,
-        (const __nv_bfloat16*)vcache, block_tables, table_stride, token_req, positions, skip_single_cu_q, nh, kvh, hd,
-        block_size, window, scale, num_pages, err);
-  else
-    return VOB_BAD_ARGUMENT;
-  return launch_status();
+    return launch_kernel(paged_attention_generic_kernel<float>, grid, ATT_WARPS * 32, smem, stream, (const float*)q, q_stride,
+                         (float*)out, (const float*)kcache, (const float*)vcache, block_tables, table_stride, token_req,
+                         positions, skip_single_cu_q, nh, kvh, hd, block_size, window, scale, num_pages, err);
+  if (dtype == VOB_BF16)
+    return launch_kernel(paged_attention_generic_kernel<__nv_bfloat16>, grid, ATT_WARPS * 32, smem, stream,
+                         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache,
+                         (const __nv_bfloat16*)vcache, block_tables, table_stride, token_req, positions, skip_single_cu_q,
+                         nh, kvh, hd, block_size, window, scale, num_pages, err);
+  return VOB_BAD_ARGUMENT;
 }

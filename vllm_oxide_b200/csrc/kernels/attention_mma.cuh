@@ -142,8 +142,8 @@ __device__ __forceinline__ void load_kv_tile(char* stage, const __nv_bfloat16* _
     int row = threadIdx.x / CHUNKS;
     int key = tile_start + row;
     int page_idx = key / block_size, in_page = key - page_idx * block_size;
-    const long head_off = (long)kh * HD + col * 8;
-    const long row_elems = (long)kvh * HD;
+    const long head_off = (long)kh * block_size * HD + col * 8;   // caches are [pages, kv_heads, block_size, HD]
+    const long page_elems = (long)kvh * block_size * HD;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
       bool valid = key >= begin && key < end;
@@ -151,7 +151,7 @@ __device__ __forceinline__ void load_kv_tile(char* stage, const __nv_bfloat16* _
       if (valid) {
         const int page = table[page_idx];
         if (page < 0 || page >= num_pages) { atomicOr(err, VOB_ERR_PAGE); valid = false; }
-        else off = ((long)page * block_size + in_page) * row_elems + head_off;
+        else off = (long)page * page_elems + (long)in_page * HD + head_off;
       }
       char* dst = stage + row * ROW_BYTES + col * 16;
       cp_async16(dst, kcache + off, valid);
@@ -168,7 +168,7 @@ __device__ __forceinline__ void load_kv_tile(char* stage, const __nv_bfloat16* _
       if (valid) {
         const int page = table[key / block_size];
         if (page < 0 || page >= num_pages) { atomicOr(err, VOB_ERR_PAGE); valid = false; }
-        else off = (((long)page * block_size + key % block_size) * kvh + kh) * HD + col * 8;
+        else off = (((long)page * kvh + kh) * block_size + key % block_size) * HD + col * 8;
       }
       cp_async16(stage + row * ROW_BYTES + col * 16, kcache + off, valid);
       cp_async16(stage + TILE * ROW_BYTES + row * ROW_BYTES + col * 16, vcache + off, valid);

@@ -26,6 +26,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __n
                          const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
                          long num_pages, int* err) {
   extern __shared__ __align__(16) char smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int kh = blockIdx.y, b = blockIdx.z;
   const int t0 = cu_q[b];
   const int n = cu_q[b + 1] - t0;
@@ -156,8 +158,7 @@ VOB_API int vob_attention_prefill(const void* q, long q_stride, void* out, const
   }
   const long rows = (long)max_q * (nh / kvh);
   dim3 grid((unsigned)((rows + PF_ROWS - 1) / PF_ROWS), kvh, num_requests);
-  attention_prefill_kernel<<<grid, PF_WARPS * 32, smem, stream>>>(
-      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,
-      block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, err);
-  return launch_status();
+  return launch_kernel(attention_prefill_kernel, grid, PF_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, q_stride,
+                       (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,
+                       table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, err);
 }

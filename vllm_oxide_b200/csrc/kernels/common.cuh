@@ -60,6 +60,30 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
   return t;
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------------
+// Kernels of the decode chain are launched so that the next kernel may start while the one before it
+// is still running: it sets up, reads what no earlier kernel writes (weights, tables, the step's index
+// arrays), and only then waits for the earlier kernel to finish (pdl_wait) before it touches
+// activations or the cache.  A kernel launched without the attribute sees both calls as no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+inline bool& pdl_enabled() { static bool on = true; return on; }
+
+template <typename... KArgs, typename... Args>
+inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaGetLastError();
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return static_cast<int>(e);

@@ -15,8 +15,10 @@ namespace vob {
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, T* __restrict__ out,
                                  int H, int V, int* err) {
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
+  pdl_wait();
   if (id < 0 || id >= V) {
     if (threadIdx.x == 0) atomicOr(err, VOB_ERR_TOKEN_ID);
     for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)t * H + i] = from_f<T>(0.f);
@@ -73,8 +75,10 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const f
                                    int* err) {
   extern __shared__ float srow[];  // H floats
   __shared__ float scratch[32];
+  pdl_launch_dependents();
   const int r = blockIdx.x;
   int src = r;
+  pdl_wait();
   if (rows) {
     src = rows[r];
     if (src < 0 || src >= num_src_rows) {
@@ -130,6 +134,8 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const f
 // eight gate values and the eight up values of the same outputs.
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
     const int i = (int)(idx - t * I);
@@ -146,21 +152,24 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 // One warp per (token, head) over the merged q|k|v row.  q heads are normalised and rotated in
 // place; k heads are normalised, rotated and written to the key cache at the token's slot; v
 // heads are copied to the value cache.  cos_sin is [max_pos, hd] float: cos of hd/2 angles, then
-// sin.  A slot of -1 writes nothing.
+// sin.  A slot of -1 writes nothing.  The caches are [pages, kv_heads, block_size, hd]: slot s is row
+// s % block_size of page s / block_size, and the rows of one head within a page are contiguous.
 template <typename T>
 __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __restrict__ bias,
                                              const int* __restrict__ positions, const int* __restrict__ slots,
                                              const float* __restrict__ wq, const float* __restrict__ wk,
                                              const float* __restrict__ cos_sin, T* __restrict__ kcache,
                                              T* __restrict__ vcache, int nh, int kvh, int hd, float eps, int max_pos,
-                                             long num_slots, int write_kv, int* err) {
+                                             long num_slots, int block_size, int write_kv, int* err) {
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y * (blockDim.x >> 5) + warp;
   const int total_heads = nh + 2 * kvh;
-  if (head >= total_heads) return;
   const int pos = positions[t];
   const int slot = slots ? slots[t] : -1;
+  pdl_wait();
+  if (head >= total_heads) return;
   const int width = total_heads * hd;
   T* row = qkv + (size_t)t * width + (size_t)head * hd;
   const T* brow = bias ? bias + (size_t)head * hd : nullptr;
@@ -171,7 +180,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
     return;
   }
   if (!is_q && !is_k) {  // value head: bias, then copy
-    T* dst = vcache + ((size_t)slot * kvh + (head - nh - kvh)) * hd;
+    T* dst = vcache + (((size_t)(slot / block_size) * kvh + (head - nh - kvh)) * block_size + slot % block_size) * hd;
     for (int i = lane; i < hd; i += 32) {
       float v = to_f<T>(row[i]);
       if (brow) v = round_to<T>(v + to_f<T>(brow[i]));
@@ -211,7 +220,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
     }
   }
   const float* cs = cos_sin + (size_t)pos * hd;
-  T* dst = is_q ? row : kcache + ((size_t)slot * kvh + (head - nh)) * hd;
+  T* dst = is_q ? row : kcache + (((size_t)(slot / block_size) * kvh + (head - nh)) * block_size + slot % block_size) * hd;
 #pragma unroll
   for (int j = 0; j < MAXP; ++j) {
     const int i = lane + 32 * j;
@@ -239,12 +248,11 @@ VOB_API int vob_embedding(const void* table, const int* ids, void* out, int T, i
                           cudaStream_t stream) {
   if (T <= 0) return 0;
   if (dtype == VOB_F32)
-    embedding_kernel<float><<<T, 128, 0, stream>>>((const float*)table, ids, (float*)out, H, V, err);
-  else if (dtype == VOB_BF16)
-    embedding_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>((const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, H, V, err);
-  else
-    return VOB_BAD_ARGUMENT;
-  return launch_status();
+    return launch_kernel(embedding_kernel<float>, T, 128, 0, stream, (const float*)table, ids, (float*)out, H, V, err);
+  if (dtype == VOB_BF16)
+    return launch_kernel(embedding_kernel<__nv_bfloat16>, T, 128, 0, stream, (const __nv_bfloat16*)table, ids,
+                         (__nv_bfloat16*)out, H, V, err);
+  return VOB_BAD_ARGUMENT;
 }
 
 template <typename T>
@@ -260,12 +268,10 @@ static int add_rmsnorm_launch(const void* x, void* residual, const float* w, voi
     if (e != cudaSuccess) return (int)e;
   }
   if (vec)
-    add_rmsnorm_kernel<T, NT, true><<<n_out, NT, smem, stream>>>((const T*)x, (T*)residual, w, (T*)y, rows, H, num_src_rows,
-                                                                 eps, has_residual, err);
-  else
-    add_rmsnorm_kernel<T, NT, false><<<n_out, NT, smem, stream>>>((const T*)x, (T*)residual, w, (T*)y, rows, H, num_src_rows,
-                                                                  eps, has_residual, err);
-  return launch_status();
+    return launch_kernel(add_rmsnorm_kernel<T, NT, true>, n_out, NT, smem, stream, (const T*)x, (T*)residual, w, (T*)y, rows, H,
+                         num_src_rows, eps, has_residual, err);
+  return launch_kernel(add_rmsnorm_kernel<T, NT, false>, n_out, NT, smem, stream, (const T*)x, (T*)residual, w, (T*)y, rows, H,
+                       num_src_rows, eps, has_residual, err);
 }
 
 // y[n_out, H]; x and residual [num_src_rows, H]; rows may be null (then n_out == num_src_rows).
@@ -285,34 +291,31 @@ VOB_API int vob_silu_mul(const void* gu, void* out, int T, int I, int interleave
   const size_t total = (size_t)T * I;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (dtype == VOB_F32)
-    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, I, total, interleaved);
-  else if (dtype == VOB_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total, interleaved);
-  else
-    return VOB_BAD_ARGUMENT;
-  return launch_status();
+    return launch_kernel(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, I, total, interleaved);
+  if (dtype == VOB_BF16)
+    return launch_kernel(silu_mul_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+                         I, total, interleaved);
+  return VOB_BAD_ARGUMENT;
 }
 
 VOB_API int vob_qk_norm_rope_kv_write(void* qkv, const void* bias, const int* positions, const int* slots,
                                       const float* wq, const float* wk, const float* cos_sin, void* kcache, void* vcache,
                                       int T, int nh, int kvh, int hd, float eps, int max_pos, long num_slots,
-                                      int write_kv, int dtype, int* err, cudaStream_t stream) {
+                                      int block_size, int write_kv, int dtype, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hd <= 0 || hd % 2 || hd > 512) return VOB_UNSUPPORTED;
+  if (hd <= 0 || hd % 2 || hd > 512 || block_size <= 0) return VOB_UNSUPPORTED;
   if ((wq == nullptr) != (wk == nullptr)) return VOB_BAD_ARGUMENT;
   const int warps = 4;
   dim3 grid(T, (nh + 2 * kvh + warps - 1) / warps);
   if (dtype == VOB_F32)
-    qk_norm_rope_kv_write_kernel<float><<<grid, warps * 32, 0, stream>>>(
-        (float*)qkv, (const float*)bias, positions, slots, wq, wk, cos_sin, (float*)kcache, (float*)vcache, nh, kvh, hd,
-        eps, max_pos, num_slots, write_kv, err);
-  else if (dtype == VOB_BF16)
-    qk_norm_rope_kv_write_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
-        (__nv_bfloat16*)qkv, (const __nv_bfloat16*)bias, positions, slots, wq, wk, cos_sin, (__nv_bfloat16*)kcache,
-        (__nv_bfloat16*)vcache, nh, kvh, hd, eps, max_pos, num_slots, write_kv, err);
-  else
-    return VOB_BAD_ARGUMENT;
-  return launch_status();
+    return launch_kernel(qk_norm_rope_kv_write_kernel<float>, grid, warps * 32, 0, stream, (float*)qkv, (const float*)bias,
+                         positions, slots, wq, wk, cos_sin, (float*)kcache, (float*)vcache, nh, kvh, hd, eps, max_pos,
+                         num_slots, block_size, write_kv, err);
+  if (dtype == VOB_BF16)
+    return launch_kernel(qk_norm_rope_kv_write_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream, (__nv_bfloat16*)qkv,
+                         (const __nv_bfloat16*)bias, positions, slots, wq, wk, cos_sin, (__nv_bfloat16*)kcache,
+                         (__nv_bfloat16*)vcache, nh, kvh, hd, eps, max_pos, num_slots, block_size, write_kv, err);
+  return VOB_BAD_ARGUMENT;
 }
 
 // pairs: [n_pairs][2] = (source page, destination page); one cache plane of page_elems elements per page.
@@ -327,6 +330,9 @@ VOB_API int vob_copy_pages(void* cache, const int* pairs, int n_pairs, long page
     return VOB_BAD_ARGUMENT;
   return launch_status();
 }
+
+// Programmatic dependent launch on (default) or off, for every kernel of this library.
+VOB_API void vob_set_pdl(int on) { pdl_enabled() = on != 0; }
 
 VOB_API const char* vob_error_string(int code) {
   if (code == VOB_BAD_ARGUMENT) return "bad argument to a vllm_oxide_b200 kernel launcher";

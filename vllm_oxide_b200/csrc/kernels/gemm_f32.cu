@@ -15,6 +15,8 @@ gemm_f32_kernel(const float* __restrict__ A, long lda, const float* __restrict__
                 long ldc, const float* __restrict__ bias, int M, int N, int K) {
   __shared__ float As[GK][GM + 4];
   __shared__ float Ws[GK][GN + 4];
+  pdl_launch_dependents();
+  pdl_wait();
   const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
   const int tid = threadIdx.x;
   const int tx = tid % 16, ty = tid / 16;  // micro-tile: rows ty*4.., cols tx*4..
@@ -71,6 +73,5 @@ VOB_API int vob_gemm_f32(const float* A, long lda, const float* W, long ldw, flo
   if (K <= 0) return VOB_BAD_ARGUMENT;
   dim3 grid((N + GN - 1) / GN, (M + GM - 1) / GM);
   if (grid.y > 65535) return VOB_UNSUPPORTED;
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, bias, M, N, K);
-  return launch_status();
+  return launch_kernel(gemm_f32_kernel, grid, 256, 0, stream, A, lda, W, ldw, C, ldc, bias, M, N, K);
 }

@@ -108,25 +108,43 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
 
   const int m_rows = M < MT ? M : MT;
+  pdl_launch_dependents();
   if (warp == SK_CONSUMERS) {
     // ------------------------------------------------ producer (one thread)
     if (lane == 0) {
-      long it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        for (int kc = 0; kc < k_iters; ++kc, ++it) {
-          const int s = (int)(it % S);
-          if (it >= S) {
-            ok = mbar_wait(&empty[s], (unsigned)(((it / S) - 1) & 1), abort_flag, err);
-            if (!ok) break;
-          }
-          mbar_expect_tx(&full[s], (unsigned)STAGE_BYTES);
-          char* st = stages + s * STAGE_BYTES;
+      const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      const long total = (long)my_tiles * k_iters;
+      // The weights do not depend on the kernel before this one: the first stages of W are on their way
+      // before that kernel has finished.  The tokens do, so their copies follow the wait.
+      const int ahead = total < S ? (int)total : S;
+      for (int it0 = 0; it0 < ahead; ++it0) {
+        const int tile = blockIdx.x + (it0 / k_iters) * gridDim.x, kc = it0 % k_iters;
+        mbar_expect_tx(&full[it0], (unsigned)STAGE_BYTES);
 #pragma unroll
-          for (int c = 0; c < SK_SLICES; ++c) {
-            tma_load_2d(st + c * W_SLICE, &tmW, kc * SK_KC + c * TMA_BOX_COLS, tile * R, &full[s]);
-            tma_load_2d(st + SK_SLICES * W_SLICE + c * X_SLICE, &tmX, kc * SK_KC + c * TMA_BOX_COLS, 0, &full[s]);
-          }
+        for (int c = 0; c < SK_SLICES; ++c)
+          tma_load_2d(stages + it0 * STAGE_BYTES + c * W_SLICE, &tmW, kc * SK_KC + c * TMA_BOX_COLS, tile * R, &full[it0]);
+      }
+      pdl_wait();
+      for (int it0 = 0; it0 < ahead; ++it0) {
+        const int kc = it0 % k_iters;
+#pragma unroll
+        for (int c = 0; c < SK_SLICES; ++c)
+          tma_load_2d(stages + it0 * STAGE_BYTES + SK_SLICES * W_SLICE + c * X_SLICE, &tmX, kc * SK_KC + c * TMA_BOX_COLS, 0,
+                      &full[it0]);
+      }
+      long it = ahead;
+      bool ok = true;
+      for (; it < total; ++it) {
+        const int tile = blockIdx.x + (int)(it / k_iters) * gridDim.x, kc = (int)(it % k_iters);
+        const int s = (int)(it % S);
+        ok = mbar_wait(&empty[s], (unsigned)(((it / S) - 1) & 1), abort_flag, err);
+        if (!ok) break;
+        mbar_expect_tx(&full[s], (unsigned)STAGE_BYTES);
+        char* st = stages + s * STAGE_BYTES;
+#pragma unroll
+        for (int c = 0; c < SK_SLICES; ++c) {
+          tma_load_2d(st + c * W_SLICE, &tmW, kc * SK_KC + c * TMA_BOX_COLS, tile * R, &full[s]);
+          tma_load_2d(st + SK_SLICES * W_SLICE + c * X_SLICE, &tmX, kc * SK_KC + c * TMA_BOX_COLS, 0, &full[s]);
         }
       }
       // every copy this block issued must have landed before the block may exit
@@ -139,6 +157,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
   } else {
     // ------------------------------------------------ consumers
+    pdl_wait();   // they write `out`, which the kernel before this one may still read
     const int g = lane >> 2, tq = lane & 3;
     const int mi = lane >> 3, r8 = lane & 7;
     const int a_row = (mi & 1) * 8 + r8, a_chunk = mi >> 1;                       // W rows, ldmatrix x4
@@ -242,8 +261,8 @@ static int skinny_launch(const CUtensorMap* tmW, const CUtensorMap* tmX, void* o
   }
   const int num_tiles = (N + R - 1) / R;
   const int grid = num_tiles < 2 * 148 ? num_tiles : 2 * 148;
-  gemm_skinny_kernel<R, MT, EPI><<<grid, SK_THREADS, smem, stream>>>(*tmW, *tmX, out, ldo, M, N, K, num_tiles, err);
-  return launch_status();
+  return launch_kernel(gemm_skinny_kernel<R, MT, EPI>, grid, SK_THREADS, smem, stream, *tmW, *tmX, out, ldo, M, N, K,
+                       num_tiles, err);
 }
 
 template <int R, int MT>

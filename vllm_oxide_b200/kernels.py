@@ -125,10 +125,11 @@ def silu_mul(gate_up, out, num_tokens: int, interleaved: bool = False) -> None:
 def qk_norm_rope_kv_write(qkv, bias, positions, slots, wq, wk, cos_sin, kcache, vcache, num_tokens, nh, kvh, hd,
                           eps, write_kv: bool, err) -> None:
     _cuda(qkv, positions, slots, cos_sin, kcache, vcache)
-    num_slots = kcache.shape[0] * kcache.shape[1] if kcache is not None else 0
+    num_slots = kcache.shape[0] * kcache.shape[2] if kcache is not None else 0
+    block_size = kcache.shape[2] if kcache is not None else 1
     _check(lib().vob_qk_norm_rope_kv_write(_p(qkv), _p(bias), _p(positions), _p(slots), _p(wq), _p(wk), _p(cos_sin),
                                            _p(kcache), _p(vcache), num_tokens, nh, kvh, hd, ctypes.c_float(eps),
-                                           cos_sin.shape[0], ctypes.c_long(num_slots), int(write_kv),
+                                           cos_sin.shape[0], ctypes.c_long(num_slots), block_size, int(write_kv),
                                            _code(qkv.dtype), _p(err), _stream()), "qk_norm_rope_kv_write")
 
 
@@ -139,7 +140,7 @@ def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, toke
     _cuda(q, out, kcache, vcache, block_tables, token_req, positions)
     _check(lib().vob_paged_attention_generic(_p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache),
                                              _p(block_tables), block_tables.shape[-1], _p(token_req), _p(positions),
-                                             _p(skip_single_cu_q), num_tokens, nh, kvh, hd, kcache.shape[1], window,
+                                             _p(skip_single_cu_q), num_tokens, nh, kvh, hd, kcache.shape[2], window,
                                              ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), _code(q.dtype),
                                              _p(err), _stream()), "paged_attention_generic")
 
@@ -155,7 +156,7 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, conte
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
     _check(attention_lib(hd).vob_attention_decode(
         _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables), block_tables.shape[-1],
-        _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[1], window, ctypes.c_float(scale),
+        _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[2], window, ctypes.c_float(scale),
         ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(err), _stream()), "attention_decode")
 
 
@@ -166,7 +167,7 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
     _check(attention_lib(hd).vob_attention_prefill(
         _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables), block_tables.shape[-1],
-        _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, kcache.shape[1], window, ctypes.c_float(scale),
+        _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, kcache.shape[2], window, ctypes.c_float(scale),
         ctypes.c_long(kcache.shape[0]), _p(err), _stream()), "attention_prefill")
 
 

@@ -55,7 +55,7 @@ class StateSpec:
 
 @dataclass
 class CachePlane:
-    """One layer's keys and values: [num_pages, block_size, kv_heads, head_dim] each."""
+    """One layer's keys and values: [num_pages, kv_heads, block_size, head_dim] each."""
     k: torch.Tensor
     v: torch.Tensor
     group: int

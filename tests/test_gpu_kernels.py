@@ -277,14 +277,14 @@ def test_attention_generic_does_not_depend_on_the_batch():
     assert torch.equal(out[1:4].cpu(), a_got)
 
 
-def decode_attention(num_splits):
+def decode_attention(num_splits, use_tma=True):
     def fn(q, out, kc, vc, bt, cu_q, ctx, T, nh, kvh, hd, window, err, **_):
         from vllm_oxide_b200 import kernels
         B = ctx.shape[0]
         n = kernels.attention_decode_scratch_floats(hd, B, nh, num_splits)
         scratch = torch.full((max(n, 1),), float("nan"), device=DEV)
         kernels.attention_decode(q.reshape(T, nh * hd), nh * hd, out, kc, vc, bt, cu_q, ctx, B, nh, kvh, hd, window,
-                                 1.0 / math.sqrt(hd), num_splits, scratch if n else None, err)
+                                 1.0 / math.sqrt(hd), num_splits, scratch if n else None, err, use_tma=use_tma)
     return fn
 
 
@@ -297,13 +297,18 @@ DECODE_CASES = [  # nh, kvh, hd, block_size, window, ctx_lens, splits
     (16, 1, 64, 64, 0, [513, 77], 5),
     (8, 2, 256, 64, 100, [400, 99, 101], 3),
     (5, 5, 80, 48, 0, [200], 7),
+    (8, 8, 64, 48, 30, [200, 31, 47, 48, 49], 2),
+    (12, 3, 192, 32, 0, [333, 1, 65], 3),
 ]
 
 
+@pytest.mark.parametrize("use_tma", [True, False])
 @pytest.mark.parametrize("case", DECODE_CASES)
-def test_attention_decode(case):
+def test_attention_decode(case, use_tma):
+    """Head sizes that are a multiple of 64 have two kernels (TMA and cp.async copies); both are checked."""
     nh, kvh, hd, bs, window, ctx_lens, splits = case
-    got, want = run_attention(decode_attention(splits), torch.bfloat16, nh, kvh, hd, bs, window, [1] * len(ctx_lens), ctx_lens)
+    got, want = run_attention(decode_attention(splits, use_tma), torch.bfloat16, nh, kvh, hd, bs, window,
+                              [1] * len(ctx_lens), ctx_lens)
     assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
 
 
@@ -460,8 +465,8 @@ def test_copy_pages():
     assert torch.equal(plane[4], before[0]) and torch.equal(plane[5], before[2]) and torch.equal(plane[:4], before[:4])
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 16, 16), (8, 4096, 4096), (3, 331, 80), (16, 24576 // 8, 512), (9, 100, 272),
-                                   (5, 517, 96), (16, 48, 12288), (2, 151936 // 16, 1024), (4, 40, 200), (11, 70, 8)])
+@pytest.mark.parametrize("M,N,K", [(1, 16, 64), (8, 4096, 4096), (3, 331, 128), (16, 24576 // 8, 512), (9, 100, 320),
+                                   (5, 517, 192), (16, 48, 12288), (2, 151936 // 16, 1024), (4, 40, 704), (11, 70, 64)])
 def test_gemm_skinny(M, N, K):
     from vllm_oxide_b200 import kernels
     g = torch.Generator().manual_seed(M * 1000 + N)
@@ -485,7 +490,7 @@ def test_gemm_skinny(M, N, K):
     assert torch.equal(out2, out) and err.item() == 0
 
 
-@pytest.mark.parametrize("M,I,K", [(1, 8, 16), (8, 12288 // 4, 1024), (7, 104, 80), (16, 200, 96), (12, 64, 4096)])
+@pytest.mark.parametrize("M,I,K", [(1, 8, 64), (8, 12288 // 4, 1024), (7, 104, 128), (16, 200, 192), (12, 64, 4096)])
 def test_gemm_skinny_swiglu(M, I, K):
     from vllm_oxide_b200 import kernels
     g = torch.Generator().manual_seed(M + I)
@@ -508,7 +513,9 @@ def test_gemm_skinny_refuses_what_it_cannot_take():
     x = torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV)
     assert not kernels.gemm_skinny_supported(x, w)
-    assert not kernels.gemm_skinny_supported(x[:4, 4:44], w[:, 4:44])      # rows that start off a 16-byte boundary
+    assert not kernels.gemm_skinny_supported(x[:4, :48], w[:, :48])        # K is not a multiple of 64
+    x2 = torch.zeros(4, 136, dtype=torch.bfloat16, device=DEV)
+    assert not kernels.gemm_skinny_supported(x2[:, 4:132], torch.zeros(8, 128, dtype=torch.bfloat16, device=DEV))   # misaligned rows
     assert not kernels.gemm_skinny_supported(x[:4].float(), w.float())
     with pytest.raises(kernels.KernelError, match="not supported"):
         kernels.gemm_skinny(x, w, torch.zeros(17, 8, dtype=torch.bfloat16, device=DEV), kernels.EPI_BF16, err_word())

@@ -35,13 +35,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __nv
   const int G = nh / kvh;
   const int pos = context - 1;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int n_keys = pos + 1 - lo;
-  // the key range in tiles of 64 from lo; split s takes tiles [s*n/S, (s+1)*n/S): within one tile of each other
-  const int all_tiles = (n_keys + DEC_TILE - 1) / DEC_TILE;
+  // the key range in tiles of 64 from lo rounded down to a multiple of 16 (the copies work in runs of 16
+  // keys); split s takes tiles [s*n/S, (s+1)*n/S): within one tile of each other
+  const int lo16 = lo & ~15;
+  const int all_tiles = (pos + 1 - lo16 + DEC_TILE - 1) / DEC_TILE;
   const int tile_begin = (int)((long)split * all_tiles / num_splits);
   const int tile_end = (int)((long)(split + 1) * all_tiles / num_splits);
-  const int start = lo + tile_begin * DEC_TILE;
-  const int end = min(pos + 1, lo + tile_end * DEC_TILE);
+  const int start = lo16 + tile_begin * DEC_TILE;
+  const int end = min(pos + 1, lo16 + tile_end * DEC_TILE);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int* table = block_tables + (size_t)b * table_stride;
@@ -64,18 +65,25 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __nv
   st.clear();
   const float sc = scale * LOG2E;
   const int n_tiles = start < end ? (end - start + DEC_TILE - 1) / DEC_TILE : 0;
+  int pages[DEC_TILE / RUN_KEYS];
 #pragma unroll
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < n_tiles)
-      load_kv_tile<DEC_TILE, DEC_WARPS * 32>(smem + s * DEC_STAGE_BYTES, kcache, vcache, table, block_size, kvh, kh, start + s * DEC_TILE, start, end,
-                       num_pages, err);
+    if (s < n_tiles) {
+      tile_pages<DEC_TILE>(pages, table, block_size, start + s * DEC_TILE, lo, end);
+      load_kv_tile<DEC_TILE, DEC_WARPS * 32>(smem + s * DEC_STAGE_BYTES, kcache, vcache, pages, block_size, kvh, kh,
+                                             start + s * DEC_TILE, lo, end, num_pages, err);
+    }
     cp_async_commit();
   }
+  if (DEC_STAGES - 1 < n_tiles) tile_pages<DEC_TILE>(pages, table, block_size, start + (DEC_STAGES - 1) * DEC_TILE, lo, end);
   for (int it = 0; it < n_tiles; ++it) {
     const int nxt = it + DEC_STAGES - 1;
-    if (nxt < n_tiles)
-      load_kv_tile<DEC_TILE, DEC_WARPS * 32>(smem + (nxt % DEC_STAGES) * DEC_STAGE_BYTES, kcache, vcache, table, block_size, kvh, kh,
-                       start + nxt * DEC_TILE, start, end, num_pages, err);
+    if (nxt < n_tiles) {
+      load_kv_tile<DEC_TILE, DEC_WARPS * 32>(smem + (nxt % DEC_STAGES) * DEC_STAGE_BYTES, kcache, vcache, pages, block_size,
+                                             kvh, kh, start + nxt * DEC_TILE, lo, end, num_pages, err);
+      // the pages of the tile after that: looked up now, used in the next round
+      if (nxt + 1 < n_tiles) tile_pages<DEC_TILE>(pages, table, block_size, start + (nxt + 1) * DEC_TILE, lo, end);
+    }
     cp_async_commit();
     cp_async_wait<DEC_STAGES - 1>();
     __syncthreads();
@@ -87,10 +95,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __nv
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         const int key = k0 + i * 8 + tq * 2;
-        s[i][0] = key < end ? s[i][0] * sc : -INFINITY;
-        s[i][1] = key + 1 < end ? s[i][1] * sc : -INFINITY;
-        s[i][2] = key < end ? s[i][2] * sc : -INFINITY;
-        s[i][3] = key + 1 < end ? s[i][3] * sc : -INFINITY;
+        const bool ok0 = key >= lo && key < end, ok1 = key + 1 >= lo && key + 1 < end;
+        s[i][0] = ok0 ? s[i][0] * sc : -INFINITY;
+        s[i][1] = ok1 ? s[i][1] * sc : -INFINITY;
+        s[i][2] = ok0 ? s[i][2] * sc : -INFINITY;
+        s[i][3] = ok1 ? s[i][3] * sc : -INFINITY;
       }
       softmax_pv_16keys(st, s, stage + DEC_TILE * ROW_BYTES + warp * 16 * ROW_BYTES, lane);
     }
@@ -127,7 +136,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __nv
     float L = 0.f, O = 0.f;
 #pragma unroll
     for (int w = 0; w < DEC_WARPS; ++w) {
-      const float f = wm[w * 16 + r] == -INFINITY ? 0.f : exp2f(wm[w * 16 + r] - M);
+      const float f = wm[w * 16 + r] == -INFINITY ? 0.f : fast_exp2(wm[w * 16 + r] - M);
       L += wl[w * 16 + r] * f;
       O += wo[((size_t)w * 16 + r) * HD + d] * f;
     }
@@ -142,6 +151,207 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __nv
     }
   }
 }
+
+#if VOB_HD % 64 == 0
+// ---- the same kernel with the keys and values brought in by TMA ------------------------------------------
+// cp.async moves about 16 bytes per clock and SM on this GPU, the copy engine about twice that, so head sizes
+// that are a multiple of 64 (one or more 128-byte swizzled column slices) take this kernel.  A fifth warp is the
+// producer: one thread looks the pages up (one tile ahead), and issues one copy of K and one of V per tile when
+// pages hold a multiple of 64 keys (a tile then lies in one page), else one per run of 16 keys; a copy brings all
+// column slices at once.  An mbarrier per stage counts the bytes in, a second one the four consumer warps out.
+// Every wait is bounded.  tmK / tmV describe a cache plane as a matrix [pages * kv_heads * block_size, HD] in
+// column slices, with boxes of `box_keys` (64 or 16) rows.
+constexpr int DT_SLICES = HD / 64;
+constexpr int DT_TILE_BYTES = DT_SLICES * DEC_TILE * 128;       // one of K or V
+constexpr int DT_STAGE_BYTES = 2 * DT_TILE_BYTES;
+constexpr int DT_STAGES = HD <= 128 ? 3 : 2;
+constexpr int DT_THREADS = (DEC_WARPS + 1) * 32;
+
+__global__ void __launch_bounds__(DT_THREADS)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                            const __nv_bfloat16* __restrict__ q, long q_stride, __nv_bfloat16* __restrict__ out,
+                            const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
+                            const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
+                            long num_pages, float* __restrict__ part_o, float* __restrict__ part_lse, int box_keys, int* err) {
+  extern __shared__ __align__(1024) char smem_raw[];
+  char* smem = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int MERGE_BYTES = (2 * DEC_WARPS * 16 + DEC_WARPS * 16 * HD) * 4;
+  constexpr int DATA_BYTES = DT_STAGES * DT_STAGE_BYTES > MERGE_BYTES ? DT_STAGES * DT_STAGE_BYTES : MERGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + DATA_BYTES);
+  uint64_t* empty = full + DT_STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + DT_STAGES);
+  pdl_launch_dependents();
+  const int split = blockIdx.x, num_splits = gridDim.x, kh = blockIdx.y, b = blockIdx.z;
+  const int t = cu_q[b];
+  const int t_next = cu_q[b + 1], context = context_lens[b];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < DT_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], DEC_WARPS); }
+    *abort_flag = 0;
+    tma_prefetch_map(&tmK);
+    tma_prefetch_map(&tmV);
+  }
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  __syncthreads();
+  pdl_wait();
+  if (t_next - t != 1) return;                         // not a decoding request (uniform for the block)
+  const int G = nh / kvh;
+  const int pos = context - 1;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo16 = lo & ~(box_keys - 1);               // tiles start on a box boundary
+  const int all_tiles = (pos + 1 - lo16 + DEC_TILE - 1) / DEC_TILE;
+  const int tile_begin = (int)((long)split * all_tiles / num_splits);
+  const int tile_end = (int)((long)(split + 1) * all_tiles / num_splits);
+  const int start = lo16 + tile_begin * DEC_TILE;
+  const int end = min(pos + 1, lo16 + tile_end * DEC_TILE);
+  const int n_tiles = start < end ? (end - start + DEC_TILE - 1) / DEC_TILE : 0;
+  const int* table = block_tables + (size_t)b * table_stride;
+  WarpSoftmax st;
+  st.clear();
+
+  if (warp == DEC_WARPS) {
+    // ------------------------------------------------ producer (one thread)
+    if (lane == 0 && n_tiles > 0) {
+      int pages[DEC_TILE / RUN_KEYS];
+      tile_pages<DEC_TILE>(pages, table, block_size, start, lo, end);
+      bool ok = true;
+      int it = 0;
+      for (; it < n_tiles; ++it) {
+        const int s = it % DT_STAGES;
+        if (it >= DT_STAGES) {
+          ok = mbar_wait(&empty[s], (unsigned)(((it / DT_STAGES) - 1) & 1), abort_flag, err);
+          if (!ok) break;
+        }
+        mbar_expect_tx(&full[s], (unsigned)DT_STAGE_BYTES);
+        char* kt = smem + s * DT_STAGE_BYTES;
+        const int tile_start = start + it * DEC_TILE;
+        if (box_keys == DEC_TILE) {
+          // the tile lies in one page: one copy of K, one of V (the page of its first run serves all of it)
+          const int page = pages[0] != PAGE_NONE ? pages[0] : (pages[1] != PAGE_NONE ? pages[1] : (pages[2] != PAGE_NONE ? pages[2] : pages[3]));
+          const bool page_ok = page >= 0 && page < num_pages;
+          if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
+          const int row = page_ok ? (page * kvh + kh) * block_size + tile_start % block_size : 0;
+          tma_load_3d(kt, &tmK, 0, row, 0, &full[s]);
+          tma_load_3d(kt + DT_TILE_BYTES, &tmV, 0, row, 0, &full[s]);
+        } else {
+#pragma unroll
+          for (int run = 0; run < DEC_TILE / RUN_KEYS; ++run) {
+            const int page = pages[run];
+            const bool page_ok = page >= 0 && page < num_pages;
+            if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
+            // a run nobody will read is filled from row 0 of the plane: finite values that the mask zeroes
+            const int key0 = tile_start + run * RUN_KEYS;
+            const int row = page_ok ? (page * kvh + kh) * block_size + key0 % block_size : 0;
+            // a 16-row box covers rows run*16.. of every slice: slices are DEC_TILE rows apart in shared memory,
+            // but a box writes its slices box_rows apart, so each slice gets a copy of its own
+#pragma unroll
+            for (int c = 0; c < DT_SLICES; ++c) {
+              tma_load_3d(kt + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmK, 0, row, c, &full[s]);
+              tma_load_3d(kt + DT_TILE_BYTES + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, row, c, &full[s]);
+            }
+          }
+        }
+        if (it + 1 < n_tiles) tile_pages<DEC_TILE>(pages, table, block_size, tile_start + DEC_TILE, lo, end);
+      }
+      const int first = it > DT_STAGES ? it - DT_STAGES : 0;     // copies in flight must land before the block exits
+      for (int j = first; j < it; ++j) {
+        bool done = false;
+        for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % DT_STAGES], (unsigned)((j / DT_STAGES) & 1));
+        if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+      }
+    }
+  } else {
+    // ------------------------------------------------ consumers: warp w takes keys 16w..16w+15 of every tile
+    const int g = lane >> 2, tq = lane & 3;
+    uint32_t qf[KSTEPS][4];
+    {
+      const __nv_bfloat16* qrow0 = q + (size_t)t * q_stride + (size_t)(kh * G + g) * HD;
+      const __nv_bfloat16* qrow1 = qrow0 + (size_t)8 * HD;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int d = ks * 16 + tq * 2;
+        qf[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + d) : 0u;
+        qf[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + d) : 0u;
+        qf[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + d + 8) : 0u;
+        qf[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + d + 8) : 0u;
+      }
+    }
+    const float sc = scale * LOG2E;
+    for (int it = 0; it < n_tiles; ++it) {
+      const int s = it % DT_STAGES;
+      bool ok = mbar_wait(&full[s], (unsigned)((it / DT_STAGES) & 1), abort_flag, err);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const char* kt = smem + s * DT_STAGE_BYTES;
+      const int k0 = start + it * DEC_TILE + warp * 16;
+      if (k0 < end && k0 + 16 > lo) {
+        float sv[2][4];
+        qk_16keys_swizzled<DEC_TILE>(qf, kt, warp * 16, lane, sv);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int key = k0 + i * 8 + tq * 2;
+          const bool ok0 = key >= lo && key < end, ok1 = key + 1 >= lo && key + 1 < end;
+          sv[i][0] = ok0 ? sv[i][0] * sc : -INFINITY;
+          sv[i][1] = ok1 ? sv[i][1] * sc : -INFINITY;
+          sv[i][2] = ok0 ? sv[i][2] * sc : -INFINITY;
+          sv[i][3] = ok1 ? sv[i][3] * sc : -INFINITY;
+        }
+        softmax_pv_16keys_swizzled<DEC_TILE>(st, sv, kt + DT_TILE_BYTES, warp * 16, lane);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+  }
+  __syncthreads();        // every stage has been read (or given up): the merge may reuse the memory
+  if (*abort_flag) return;
+  float* wm = reinterpret_cast<float*>(smem);                 // [DEC_WARPS][16]
+  float* wl = wm + DEC_WARPS * 16;
+  float* wo = wl + DEC_WARPS * 16;                            // [DEC_WARPS][16][HD]
+  if (warp < DEC_WARPS) {
+    const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 1);
+      st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 2);
+    }
+    if (tq == 0) {
+      wm[warp * 16 + g] = st.m[0]; wm[warp * 16 + g + 8] = st.m[1];
+      wl[warp * 16 + g] = st.l[0]; wl[warp * 16 + g + 8] = st.l[1];
+    }
+#pragma unroll
+    for (int j = 0; j < DTILES; ++j) {
+      float* r0 = wo + ((size_t)warp * 16 + g) * HD + j * 8 + tq * 2;
+      float* r1 = wo + ((size_t)warp * 16 + g + 8) * HD + j * 8 + tq * 2;
+      r0[0] = st.o[j][0]; r0[1] = st.o[j][1];
+      r1[0] = st.o[j][2]; r1[1] = st.o[j][3];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += DT_THREADS) {
+    const int r = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, wm[w * 16 + r]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float f = wm[w * 16 + r] == -INFINITY ? 0.f : fast_exp2(wm[w * 16 + r] - M);
+      L += wl[w * 16 + r] * f;
+      O += wo[((size_t)w * 16 + r) * HD + d] * f;
+    }
+    const float val = L > 0.f ? O / L : 0.f;
+    const int head = kh * G + r;
+    if (num_splits == 1) {
+      out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(val);
+    } else {
+      const size_t p = ((size_t)b * nh + head) * num_splits + split;
+      part_o[p * HD + d] = val;
+      if (d == 0) part_lse[p] = L > 0.f ? M + log2f(L) : -INFINITY;
+    }
+  }
+}
+#endif  // VOB_HD % 64 == 0
 
 // Merges the splits of every (decoding request, head): weights 2^(lse - max lse).
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
@@ -182,12 +392,11 @@ VOB_API long vob_attention_decode_scratch_floats(int num_requests, int nh, int n
   return num_splits > 1 ? (long)num_requests * nh * num_splits * (HD + 1) : 0;
 }
 
-// q rows of q_stride elements (head h at h*HD); out [T, nh*HD]; caches [num_pages, kvh, block_size, HD];
-// block_tables [B, table_stride]; cu_q [B+1]; context_lens [B]; scratch: see above.
-VOB_API int vob_attention_decode(const void* q, long q_stride, void* out, const void* kcache, const void* vcache,
-                                 const int* block_tables, int table_stride, const int* cu_q, const int* context_lens,
-                                 int num_requests, int nh, int kvh, int block_size, int window, float scale,
-                                 long num_pages, int num_splits, float* scratch, int* err, cudaStream_t stream) {
+static int attention_decode_launch(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
+                                   const void* kcache, const void* vcache, const int* block_tables, int table_stride,
+                                   const int* cu_q, const int* context_lens, int num_requests, int nh, int kvh,
+                                   int block_size, int window, float scale, long num_pages, int num_splits, float* scratch,
+                                   int* err, cudaStream_t stream) {
   if (num_requests <= 0) return 0;
   if (kvh <= 0 || nh % kvh || nh / kvh > 16 || block_size <= 0 || num_splits < 1 || num_splits > 65535) return VOB_UNSUPPORTED;
   if (num_splits > 1 && !scratch) return VOB_BAD_ARGUMENT;
@@ -202,7 +411,25 @@ VOB_API int vob_attention_decode(const void* q, long q_stride, void* out, const 
   float* part_o = scratch;
   float* part_lse = scratch ? scratch + (size_t)num_requests * nh * num_splits * HD : nullptr;
   dim3 grid(num_splits, kvh, num_requests);
-  int rc = launch_kernel(attention_decode_kernel, grid, DEC_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, q_stride,
+  int rc;
+#if VOB_HD % 64 == 0
+  if (map_k && map_v && block_size % 16 == 0) {
+    static bool tma_configured = false;
+    constexpr int MERGE = (2 * DEC_WARPS * 16 + DEC_WARPS * 16 * HD) * 4;
+    constexpr int DATA = DT_STAGES * DT_STAGE_BYTES > MERGE ? DT_STAGES * DT_STAGE_BYTES : MERGE;
+    const int tma_smem = 1024 + DATA + 2 * DT_STAGES * 8 + 16;
+    if (!tma_configured) {
+      cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tma_smem);
+      if (e != cudaSuccess) return (int)e;
+      tma_configured = true;
+    }
+    rc = launch_kernel(attention_decode_tma_kernel, grid, DT_THREADS, tma_smem, stream, *(const CUtensorMap*)map_k,
+                       *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, block_tables,
+                       table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, part_o, part_lse,
+                       block_size % DEC_TILE == 0 ? DEC_TILE : RUN_KEYS, err);
+  } else
+#endif
+  rc = launch_kernel(attention_decode_kernel, grid, DEC_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, q_stride,
                          (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,
                          table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, part_o, part_lse,
                          err);
@@ -210,6 +437,34 @@ VOB_API int vob_attention_decode(const void* q, long q_stride, void* out, const 
   return launch_kernel(attention_decode_combine_kernel, dim3(nh, num_requests), HD < 128 ? 64 : 128, 0, stream,
                        (const float*)part_o, (const float*)part_lse, (__nv_bfloat16*)out, cu_q, nh, num_splits);
 }
+
+// q rows of q_stride elements (head h at h*HD); out [T, nh*HD]; caches [num_pages, kvh, block_size, HD];
+// block_tables [B, table_stride]; cu_q [B+1]; context_lens [B]; scratch: vob_attention_decode_scratch_floats.
+VOB_API int vob_attention_decode(const void* q, long q_stride, void* out, const void* kcache, const void* vcache,
+                                 const int* block_tables, int table_stride, const int* cu_q, const int* context_lens,
+                                 int num_requests, int nh, int kvh, int block_size, int window, float scale,
+                                 long num_pages, int num_splits, float* scratch, int* err, cudaStream_t stream) {
+  return attention_decode_launch(nullptr, nullptr, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
+                                 context_lens, num_requests, nh, kvh, block_size, window, scale, num_pages, num_splits,
+                                 scratch, err, stream);
+}
+
+// The same with the caches also given as tensor maps (vob_tensor_map_bf16_sliced over [pages*kvh*block_size, HD] with
+// boxes of vob_attention_decode_box_keys(block_size) rows and vob_attention_decode_box_slices(block_size) slices): head
+// sizes that are a multiple of 64 then bring keys and values in by TMA.  Null maps fall back to cp.async.
+VOB_API int vob_attention_decode_tma(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
+                                     const void* kcache, const void* vcache, const int* block_tables, int table_stride,
+                                     const int* cu_q, const int* context_lens, int num_requests, int nh, int kvh,
+                                     int block_size, int window, float scale, long num_pages, int num_splits,
+                                     float* scratch, int* err, cudaStream_t stream) {
+  return attention_decode_launch(map_k, map_v, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
+                                 context_lens, num_requests, nh, kvh, block_size, window, scale, num_pages, num_splits,
+                                 scratch, err, stream);
+}
+
+VOB_API int vob_attention_decode_has_tma() { return VOB_HD % 64 == 0 ? 1 : 0; }
+VOB_API int vob_attention_decode_box_keys(int block_size) { return block_size % DEC_TILE == 0 ? DEC_TILE : RUN_KEYS; }
+VOB_API int vob_attention_decode_box_slices(int block_size) { return block_size % DEC_TILE == 0 ? HD / 64 : 1; }
 
 // ------------------------------------------------------------------------------------------------
 // The same computation for callers that cannot allocate: see attention_decode_noalloc.h.

@@ -5,7 +5,7 @@
 // The head size is a compile-time constant: the file that includes this header is compiled once
 // per head size with -DVOB_HD=<multiple of 16, at most 256>.
 #pragma once
-#include "common.cuh"
+#include "tensor_map.cuh"
 
 #ifndef VOB_HD
 #define VOB_HD 128
@@ -44,6 +44,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 2^x by the hardware approximation (2 ulp; -inf gives 0): the softmax needs no more on the bfloat16 path.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -93,16 +100,18 @@ __device__ __forceinline__ void softmax_pv_16keys(WarpSoftmax& st, float (&s)[2]
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     mnew[h] = fmaxf(st.m[h], mx[h]);
-    corr[h] = (st.m[h] == -INFINITY) ? 0.f : exp2f(st.m[h] - mnew[h]);
+    corr[h] = (st.m[h] == -INFINITY) ? 0.f : fast_exp2(st.m[h] - mnew[h]);
     st.m[h] = mnew[h];
   }
   float p[2][4];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    p[i][0] = (mnew[0] == -INFINITY) ? 0.f : exp2f(s[i][0] - mnew[0]);
-    p[i][1] = (mnew[0] == -INFINITY) ? 0.f : exp2f(s[i][1] - mnew[0]);
-    p[i][2] = (mnew[1] == -INFINITY) ? 0.f : exp2f(s[i][2] - mnew[1]);
-    p[i][3] = (mnew[1] == -INFINITY) ? 0.f : exp2f(s[i][3] - mnew[1]);
+    // a row that has seen no key yet (maximum -inf) gets a finite stand-in, so that -inf - -inf never occurs
+    const float m0 = mnew[0] == -INFINITY ? 0.f : mnew[0], m1 = mnew[1] == -INFINITY ? 0.f : mnew[1];
+    p[i][0] = fast_exp2(s[i][0] - m0);
+    p[i][1] = fast_exp2(s[i][1] - m0);
+    p[i][2] = fast_exp2(s[i][2] - m1);
+    p[i][3] = fast_exp2(s[i][3] - m1);
   }
   st.l[0] = st.l[0] * corr[0] + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
   st.l[1] = st.l[1] * corr[1] + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
@@ -124,55 +133,120 @@ __device__ __forceinline__ void softmax_pv_16keys(WarpSoftmax& st, float (&s)[2]
   }
 }
 
-// Copies TILE cache rows (keys tile_start .. tile_start+TILE-1 of key/value head kh) into shared memory:
-// K rows first, V rows after them, each row found through the block table, so any page size works.
-// Rows of keys outside [begin, end) are zero-filled without a look at the block table (a window group has
-// given the pages below its window back).  A thread copies one 16-byte column of every (THREADS/CHUNKS)-th
-// row; the page of a row follows from the previous row's by stepping, without a division per row.
+// The cache rows of a tile are copied in runs of 16 keys.  The caches are [pages, kv_heads, block_size, HD],
+// pages hold a multiple of 16 keys and tiles start at multiples of 16, so a run lies in one page and is ONE
+// contiguous piece of memory for a head.  Looking the pages up is a global load with a long latency, so it is
+// done one tile ahead of the copies that need it (tile_pages), into registers.
+constexpr int RUN_KEYS = 16;
+constexpr int PAGE_NONE = -2;      // no key of the run is wanted: nothing is looked up, zeros are written
+
+template <int TILE>
+__device__ __forceinline__ void tile_pages(int (&pages)[TILE / RUN_KEYS], const int* __restrict__ table, int block_size,
+                                           int tile_start, int begin, int end) {
+#pragma unroll
+  for (int run = 0; run < TILE / RUN_KEYS; ++run) {
+    const int key0 = tile_start + run * RUN_KEYS;
+    pages[run] = (key0 < end && key0 + RUN_KEYS > begin) ? table[key0 / block_size] : PAGE_NONE;
+  }
+}
+
+// Copies TILE cache rows (keys tile_start .. tile_start+TILE-1 of key/value head kh) into shared memory: K rows
+// first, V rows after them; `pages` comes from tile_pages for the same tile.  Keys outside [begin, end) are
+// zero-filled (a window group has given the pages below its window back).
 template <int TILE, int THREADS>
 __device__ __forceinline__ void load_kv_tile(char* stage, const __nv_bfloat16* __restrict__ kcache,
-                                             const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ table,
+                                             const __nv_bfloat16* __restrict__ vcache, const int (&pages)[TILE / RUN_KEYS],
                                              int block_size, int kvh, int kh, int tile_start, int begin, int end,
                                              long num_pages, int* err) {
   constexpr int CHUNKS = HD / 8;                       // 16-byte chunks per row
-  if constexpr (THREADS % CHUNKS == 0 && (TILE * CHUNKS) % THREADS == 0) {
-    constexpr int ROW_STEP = THREADS / CHUNKS;         // rows between two copies of a thread
-    constexpr int ITERS = TILE / ROW_STEP;
-    const int col = threadIdx.x % CHUNKS;
-    int row = threadIdx.x / CHUNKS;
-    int key = tile_start + row;
-    int page_idx = key / block_size, in_page = key - page_idx * block_size;
-    const long head_off = (long)kh * block_size * HD + col * 8;   // caches are [pages, kv_heads, block_size, HD]
-    const long page_elems = (long)kvh * block_size * HD;
+  constexpr int RUN_CHUNKS = RUN_KEYS * CHUNKS;
+  const long head_off = (long)kh * block_size * HD;
+  const long page_elems = (long)kvh * block_size * HD;
 #pragma unroll
-    for (int i = 0; i < ITERS; ++i) {
-      bool valid = key >= begin && key < end;
-      long off = 0;
-      if (valid) {
-        const int page = table[page_idx];
-        if (page < 0 || page >= num_pages) { atomicOr(err, VOB_ERR_PAGE); valid = false; }
-        else off = (long)page * page_elems + (long)in_page * HD + head_off;
-      }
-      char* dst = stage + row * ROW_BYTES + col * 16;
-      cp_async16(dst, kcache + off, valid);
-      cp_async16(dst + TILE * ROW_BYTES, vcache + off, valid);
-      row += ROW_STEP; key += ROW_STEP; in_page += ROW_STEP;
-      while (in_page >= block_size) { in_page -= block_size; ++page_idx; }
+  for (int run = 0; run < TILE / RUN_KEYS; ++run) {
+    const int key0 = tile_start + run * RUN_KEYS;
+    const int page = pages[run];
+    const bool page_ok = page >= 0 && page < num_pages;
+    if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
+    const long base = page_ok ? (long)page * page_elems + head_off + (long)(key0 % block_size) * HD : 0;
+    const __nv_bfloat16* ksrc = kcache + base;
+    const __nv_bfloat16* vsrc = vcache + base;
+    char* kdst = stage + run * RUN_KEYS * ROW_BYTES;
+#pragma unroll
+    for (int c = threadIdx.x; c < RUN_CHUNKS; c += THREADS) {
+      const int row = c / CHUNKS, col = c - row * CHUNKS;
+      const int key = key0 + row;
+      const bool valid = page_ok && key >= begin && key < end;
+      char* dst = kdst + row * ROW_BYTES + col * 16;
+      cp_async16(dst, ksrc + (valid ? c * 8 : 0), valid);
+      cp_async16(dst + TILE * ROW_BYTES, vsrc + (valid ? c * 8 : 0), valid);
     }
-  } else {
-    for (int c = threadIdx.x; c < TILE * CHUNKS; c += THREADS) {
-      const int row = c / CHUNKS, col = c % CHUNKS;
-      const int key = tile_start + row;
-      bool valid = key >= begin && key < end;
-      long off = 0;
-      if (valid) {
-        const int page = table[key / block_size];
-        if (page < 0 || page >= num_pages) { atomicOr(err, VOB_ERR_PAGE); valid = false; }
-        else off = (((long)page * kvh + kh) * block_size + key % block_size) * HD + col * 8;
-      }
-      cp_async16(stage + row * ROW_BYTES + col * 16, kcache + off, valid);
-      cp_async16(stage + TILE * ROW_BYTES + row * ROW_BYTES + col * 16, vcache + off, valid);
-    }
+  }
+}
+
+// ---- the same two steps over tiles that TMA wrote: 64-column slices of [rows, 128 bytes], 128-byte swizzled
+// (slice s of a tile of ROWS keys starts at s * ROWS * 128 bytes; the tile's base is 1024-byte aligned).
+template <int ROWS>
+__device__ __forceinline__ void qk_16keys_swizzled(const uint32_t (&q)[KSTEPS][4], const char* ktile, int row0, int lane,
+                                                   float (&s)[2][4]) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+  const int mi = lane >> 3, r = lane & 7;
+  const int row = row0 + (mi >> 1) * 8 + r;
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    uint32_t b[4];
+    ldmatrix_x4(b, ktile + (ks >> 2) * ROWS * 128 + swizzled_offset(row, (ks & 3) * 2 + (mi & 1)));
+    mma_bf16(s[0], q[ks], b[0], b[1]);
+    mma_bf16(s[1], q[ks], b[2], b[3]);
+  }
+}
+
+template <int ROWS>
+__device__ __forceinline__ void softmax_pv_16keys_swizzled(WarpSoftmax& st, float (&s)[2][4], const char* vtile, int row0,
+                                                           int lane) {
+  float mx[2];
+  mx[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+  mx[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+  }
+  float corr[2], mnew[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    mnew[h] = fmaxf(st.m[h], mx[h]);
+    corr[h] = (st.m[h] == -INFINITY) ? 0.f : fast_exp2(st.m[h] - mnew[h]);
+    st.m[h] = mnew[h];
+  }
+  float p[2][4];
+  const float m0 = mnew[0] == -INFINITY ? 0.f : mnew[0], m1 = mnew[1] == -INFINITY ? 0.f : mnew[1];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    p[i][0] = fast_exp2(s[i][0] - m0);
+    p[i][1] = fast_exp2(s[i][1] - m0);
+    p[i][2] = fast_exp2(s[i][2] - m1);
+    p[i][3] = fast_exp2(s[i][3] - m1);
+  }
+  st.l[0] = st.l[0] * corr[0] + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
+  st.l[1] = st.l[1] * corr[1] + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
+  uint32_t a[4];
+  a[0] = pack_bf16(p[0][0], p[0][1]);
+  a[1] = pack_bf16(p[0][2], p[0][3]);
+  a[2] = pack_bf16(p[1][0], p[1][1]);
+  a[3] = pack_bf16(p[1][2], p[1][3]);
+  const int mi = lane >> 3, r = lane & 7;
+  const int row = row0 + (mi & 1) * 8 + r;
+#pragma unroll
+  for (int j = 0; j < DTILES; j += 2) {
+    st.o[j][0] *= corr[0]; st.o[j][1] *= corr[0]; st.o[j][2] *= corr[1]; st.o[j][3] *= corr[1];
+    st.o[j + 1][0] *= corr[0]; st.o[j + 1][1] *= corr[0]; st.o[j + 1][2] *= corr[1]; st.o[j + 1][3] *= corr[1];
+    const int d0 = j * 8 + (mi >> 1) * 8;      // first of the eight value columns this lane's row address names
+    uint32_t b[4];
+    ldmatrix_x4_trans(b, vtile + (d0 >> 6) * ROWS * 128 + swizzled_offset(row, (d0 & 63) >> 3));
+    mma_bf16(st.o[j], a, b[0], b[1]);
+    mma_bf16(st.o[j + 1], a, b[2], b[3]);
   }
 }
 

@@ -81,18 +81,24 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __n
   const float sc = scale * LOG2E;
   const int start = key_lo / PF_TILE * PF_TILE;
   const int n_tiles = (key_end - start + PF_TILE - 1) / PF_TILE;
+  int pages[PF_TILE / RUN_KEYS];
 #pragma unroll
   for (int s = 0; s < PF_STAGES - 1; ++s) {
-    if (s < n_tiles)
-      load_kv_tile<PF_TILE, PF_WARPS * 32>(smem + s * PF_STAGE_BYTES, kcache, vcache, table, block_size, kvh, kh,
+    if (s < n_tiles) {
+      tile_pages<PF_TILE>(pages, table, block_size, start + s * PF_TILE, key_lo, key_end);
+      load_kv_tile<PF_TILE, PF_WARPS * 32>(smem + s * PF_STAGE_BYTES, kcache, vcache, pages, block_size, kvh, kh,
                                            start + s * PF_TILE, key_lo, key_end, num_pages, err);
+    }
     cp_async_commit();
   }
+  if (PF_STAGES - 1 < n_tiles) tile_pages<PF_TILE>(pages, table, block_size, start + (PF_STAGES - 1) * PF_TILE, key_lo, key_end);
   for (int it = 0; it < n_tiles; ++it) {
     const int nxt = it + PF_STAGES - 1;
-    if (nxt < n_tiles)
-      load_kv_tile<PF_TILE, PF_WARPS * 32>(smem + (nxt % PF_STAGES) * PF_STAGE_BYTES, kcache, vcache, table, block_size,
-                                           kvh, kh, start + nxt * PF_TILE, key_lo, key_end, num_pages, err);
+    if (nxt < n_tiles) {
+      load_kv_tile<PF_TILE, PF_WARPS * 32>(smem + (nxt % PF_STAGES) * PF_STAGE_BYTES, kcache, vcache, pages, block_size, kvh,
+                                           kh, start + nxt * PF_TILE, key_lo, key_end, num_pages, err);
+      if (nxt + 1 < n_tiles) tile_pages<PF_TILE>(pages, table, block_size, start + (nxt + 1) * PF_TILE, key_lo, key_end);
+    }
     cp_async_commit();
     cp_async_wait<PF_STAGES - 1>();
     __syncthreads();

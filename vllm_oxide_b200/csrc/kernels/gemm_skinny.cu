@@ -3,8 +3,8 @@
 //
 //   * persistent blocks (two per SM) walk tiles of 32 rows of W (16 when W has too few rows to give
 //     every SM a tile); a producer thread streams each tile, 256 columns per stage, with TMA
-//     (cp.async.bulk.tensor through tensor maps: four [rows x 64] boxes of W and four of the tokens per
-//     stage, 128-byte swizzled, completion counted on an mbarrier) into a ring of 4-8 stages, running
+//     (cp.async.bulk.tensor through tensor maps: ONE copy of W and one of the tokens per stage, each four
+//     column slices of [rows x 64], 128-byte swizzled, completion counted on an mbarrier) into a ring of 4-8 stages, running
 //     ahead across tile boundaries, so the copies never stop while the other warps finish a tile; rows
 //     and columns beyond the matrices arrive as zeros.  The copy engine moves about 30 bytes per clock
 //     and SM, tokens included, so the taller tile matters: it halves the tokens' share of the copies;
@@ -20,7 +20,6 @@
 // abort flag; the block then waits (bounded again) for the copies it still has in flight and returns.
 #include "tensor_map.cuh"
 
-#define VOB_ERR_TIMEOUT 32
 
 namespace vob {
 
@@ -28,37 +27,9 @@ constexpr int SK_KC = 256;                 // columns per stage
 constexpr int SK_SLICES = SK_KC / TMA_BOX_COLS;   // boxes of 64 columns per stage
 constexpr int SK_CONSUMERS = 4;
 constexpr int SK_THREADS = (SK_CONSUMERS + 1) * 32;
-constexpr unsigned SK_SPIN_LIMIT = 1u << 22;
 
 enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
 
-__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
-  unsigned ok;
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// False when the wait ran out (or another thread of the block gave up before).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int* err) {
-  for (unsigned i = 0; i < SK_SPIN_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-  }
-  *abort_flag = 1;
-  atomicOr(err, VOB_ERR_TIMEOUT);
-  return false;
-}
 __device__ __forceinline__ void sk_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
@@ -120,18 +91,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       for (int it0 = 0; it0 < ahead; ++it0) {
         const int tile = blockIdx.x + (it0 / k_iters) * gridDim.x, kc = it0 % k_iters;
         mbar_expect_tx(&full[it0], (unsigned)STAGE_BYTES);
-#pragma unroll
-        for (int c = 0; c < SK_SLICES; ++c)
-          tma_load_2d(stages + it0 * STAGE_BYTES + c * W_SLICE, &tmW, kc * SK_KC + c * TMA_BOX_COLS, tile * R, &full[it0]);
+        tma_load_3d(stages + it0 * STAGE_BYTES, &tmW, 0, tile * R, kc * SK_SLICES, &full[it0]);
       }
       pdl_wait();
-      for (int it0 = 0; it0 < ahead; ++it0) {
-        const int kc = it0 % k_iters;
-#pragma unroll
-        for (int c = 0; c < SK_SLICES; ++c)
-          tma_load_2d(stages + it0 * STAGE_BYTES + SK_SLICES * W_SLICE + c * X_SLICE, &tmX, kc * SK_KC + c * TMA_BOX_COLS, 0,
-                      &full[it0]);
-      }
+      for (int it0 = 0; it0 < ahead; ++it0)
+        tma_load_3d(stages + it0 * STAGE_BYTES + SK_SLICES * W_SLICE, &tmX, 0, 0, (it0 % k_iters) * SK_SLICES, &full[it0]);
       long it = ahead;
       bool ok = true;
       for (; it < total; ++it) {
@@ -141,17 +105,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (!ok) break;
         mbar_expect_tx(&full[s], (unsigned)STAGE_BYTES);
         char* st = stages + s * STAGE_BYTES;
-#pragma unroll
-        for (int c = 0; c < SK_SLICES; ++c) {
-          tma_load_2d(st + c * W_SLICE, &tmW, kc * SK_KC + c * TMA_BOX_COLS, tile * R, &full[s]);
-          tma_load_2d(st + SK_SLICES * W_SLICE + c * X_SLICE, &tmX, kc * SK_KC + c * TMA_BOX_COLS, 0, &full[s]);
-        }
+        tma_load_3d(st, &tmW, 0, tile * R, kc * SK_SLICES, &full[s]);
+        tma_load_3d(st + SK_SLICES * W_SLICE, &tmX, 0, 0, kc * SK_SLICES, &full[s]);
       }
       // every copy this block issued must have landed before the block may exit
       const long first = it > S ? it - S : 0;
       for (long j = first; j < it; ++j) {
         bool done = false;
-        for (unsigned i = 0; i < SK_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % S], (unsigned)((j / S) & 1));
+        for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % S], (unsigned)((j / S) & 1));
         if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
       }
     }
@@ -285,13 +246,14 @@ VOB_API int vob_gemm_skinny_weight_box(long N) { return (N + 31) / 32 >= 148 ? 3
 VOB_API int vob_gemm_skinny_token_box(int M) { return M <= 8 ? 8 : 16; }
 
 // map_w: tensor map of W [N, K] with box rows vob_gemm_skinny_weight_box(N); map_x: tensor map of x [M, K] with box
-// rows vob_gemm_skinny_token_box(M) (both from vob_tensor_map_bf16_2d, host memory).
+// rows vob_gemm_skinny_token_box(M) (both from vob_tensor_map_bf16_sliced with 4 slices per box, host memory; K must be
+// a multiple of 64).
 // epilogue: 0 bfloat16 out [M,N]; 1 float out [M,N] (rounded to bfloat16 first); 2 SiLU(gate)*up over rows that
 // alternate in groups of eight between gate and up, out [M,N/2] bfloat16.  Needs M <= 16.
 VOB_API int vob_gemm_skinny(const void* map_w, const void* map_x, void* out, long ldo, int M, int N, int K, int epilogue,
                             int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 16 || K <= 0 || !map_w || !map_x) return VOB_UNSUPPORTED;
+  if (M > 16 || K <= 0 || K % 64 || !map_w || !map_x) return VOB_UNSUPPORTED;
   if (epilogue == EPI_SWIGLU && N % 16) return VOB_BAD_ARGUMENT;
   const CUtensorMap* tw = (const CUtensorMap*)map_w;
   const CUtensorMap* tx = (const CUtensorMap*)map_x;

@@ -37,3 +37,22 @@ VOB_API int vob_tensor_map_bf16_2d(void* out_map, const void* base, long rows, l
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : VOB_BAD_ARGUMENT;
 }
+
+// The same matrix as (64 columns, rows, cols/64 slices) with box (64, box_rows, box_slices): one copy brings
+// box_slices column slices of box_rows rows each.  Needs cols to be a multiple of 64.
+VOB_API int vob_tensor_map_bf16_sliced(void* out_map, const void* base, long rows, long cols, long row_stride, int box_rows,
+                                       int box_slices) {
+  if (!out_map || !base || rows <= 0 || cols <= 0 || box_rows <= 0 || box_rows > 256 || box_slices <= 0 || box_slices > 256)
+    return VOB_BAD_ARGUMENT;
+  if (cols % TMA_BOX_COLS || ((uintptr_t)base) % 16 || (row_stride * 2) % 16 || ((uintptr_t)out_map) % 64) return VOB_UNSUPPORTED;
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return VOB_UNSUPPORTED;
+  const cuuint64_t dims[3] = {(cuuint64_t)TMA_BOX_COLS, (cuuint64_t)rows, (cuuint64_t)(cols / TMA_BOX_COLS)};
+  const cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)TMA_BOX_COLS * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)TMA_BOX_COLS, (cuuint32_t)box_rows, (cuuint32_t)box_slices};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  CUresult r = fn((CUtensorMap*)out_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : VOB_BAD_ARGUMENT;
+}

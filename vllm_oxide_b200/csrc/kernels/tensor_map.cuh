@@ -1,17 +1,51 @@
 // Tensor maps (TMA descriptors) for row-major bfloat16 matrices, and the device-side copy that uses them.
 //
-// A map describes a matrix [rows, cols] with a row stride and a box [box_rows, 64 columns] that one
-// cp.async.bulk.tensor instruction copies into shared memory in the 128-byte swizzled layout: row r of
-// the box occupies 128 bytes, and its 16-byte chunk c sits at chunk position c ^ (r % 8).  Elements of
-// the box outside the matrix arrive as zeros, so ragged edges need no special case.  The innermost
-// coordinate of every copy in this package is a multiple of 64 columns (128 bytes), as the copy engine
-// requires 16-byte alignment there.
+// A matrix [rows, cols] (cols a multiple of 64) is described as a three-dimensional tensor
+// (64 columns, rows, cols/64 column slices), and a box (64, box_rows, box_slices) is what ONE
+// cp.async.bulk.tensor instruction copies into shared memory: slice after slice, each slice box_rows rows
+// of 128 bytes in the 128-byte swizzled layout (the 16-byte chunk c of row r sits at chunk position
+// c ^ (r % 8)).  One instruction per tile matters: issuing a copy costs the issuing thread a few hundred
+// cycles whatever its size, so many small boxes starve the pipeline.  Rows and slices of the box outside
+// the matrix arrive as zeros, so ragged edges need no special case.  The innermost coordinate of every copy
+// is 0, which satisfies the copy engine's 16-byte alignment rule.
 #pragma once
 #include <cuda.h>
 
 #include "common.cuh"
 
 namespace vob {
+
+#define VOB_ERR_TIMEOUT 32
+
+constexpr unsigned MBAR_SPIN_LIMIT = 1u << 22;   // tries before a wait on an mbarrier gives up
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// False when the wait ran out (or another thread of the block gave up before).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int* err) {
+  for (unsigned i = 0; i < MBAR_SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicOr(err, VOB_ERR_TIMEOUT);
+  return false;
+}
 
 constexpr int TMA_BOX_COLS = 64;   // 128 bytes of bfloat16: the widest box the 128-byte swizzle allows
 
@@ -20,6 +54,12 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
   const unsigned mbar = (unsigned)__cvta_generic_to_shared(bar);
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
                ::"r"(dst), "l"(map), "r"(col), "r"(row), "r"(mbar) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  const unsigned mbar = (unsigned)__cvta_generic_to_shared(bar);
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(mbar) : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(map) : "memory");

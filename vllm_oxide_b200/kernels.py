@@ -150,11 +150,23 @@ def attention_decode_scratch_floats(head_dim: int, num_requests: int, nh: int, n
 
 
 def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, nh, kvh, hd,
-                     window: int, scale: float, num_splits: int, scratch, err) -> None:
+                     window: int, scale: float, num_splits: int, scratch, err, use_tma: bool = True) -> None:
     """Requests that bring exactly one token; the others are skipped."""
     _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, scratch)
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
-    _check(attention_lib(hd).vob_attention_decode(
+    L = attention_lib(hd)
+    if use_tma and L.vob_attention_decode_has_tma() and kcache.is_contiguous() and vcache.is_contiguous():
+        # head sizes that are a multiple of 64: keys and values come in by TMA (about twice cp.async's rate)
+        bs = kcache.shape[2]
+        keys, slices = L.vob_attention_decode_box_keys(bs), L.vob_attention_decode_box_slices(bs)
+        map_k, map_v = tensor_map(kcache.view(-1, hd), keys, slices), tensor_map(vcache.view(-1, hd), keys, slices)
+        _check(L.vob_attention_decode_tma(
+            map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
+            block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[2], window,
+            ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(err), _stream()),
+            "attention_decode_tma")
+        return
+    _check(L.vob_attention_decode(
         _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables), block_tables.shape[-1],
         _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[2], window, ctypes.c_float(scale),
         ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(err), _stream()), "attention_decode")
@@ -187,15 +199,16 @@ EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
 _tensor_maps = {}
 
 
-def tensor_map(t: torch.Tensor, box_rows: int):
-    """A TMA descriptor (host memory, cached) of a row-major bfloat16 matrix with box [box_rows, 64 columns]."""
-    key = (t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows)
+def tensor_map(t: torch.Tensor, box_rows: int, box_slices: int):
+    """A TMA descriptor (host memory, cached) of a row-major bfloat16 matrix whose width is a multiple of 64: one copy
+    brings `box_slices` column slices (64 columns each) of `box_rows` rows."""
+    key = (t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows, box_slices)
     hit = _tensor_maps.get(key)
     if hit is None:
         raw = (ctypes.c_char * 256)()
         addr = (ctypes.addressof(raw) + 63) & ~63
-        code = lib().vob_tensor_map_bf16_2d(ctypes.c_void_p(addr), _p(t), ctypes.c_long(t.shape[0]), ctypes.c_long(t.shape[1]),
-                                            ctypes.c_long(t.stride(0)), box_rows)
+        code = lib().vob_tensor_map_bf16_sliced(ctypes.c_void_p(addr), _p(t), ctypes.c_long(t.shape[0]),
+                                                ctypes.c_long(t.shape[1]), ctypes.c_long(t.stride(0)), box_rows, box_slices)
         if code != 0:
             raise KernelError(f"tensor map for a [{t.shape[0]}, {t.shape[1]}] matrix: {lib().vob_error_string(code).decode()}")
         if len(_tensor_maps) > 4096:
@@ -205,9 +218,10 @@ def tensor_map(t: torch.Tensor, box_rows: int):
 
 
 def gemm_skinny_supported(x, w) -> bool:
-    """Whether the weight-streaming kernel takes x[M,K] @ w[N,K]^T: bfloat16, M <= 16, rows that start on
-    16-byte boundaries (K need not be a multiple of anything else: the copy engine fills ragged edges with zeros)."""
+    """Whether the weight-streaming kernel takes x[M,K] @ w[N,K]^T: bfloat16, M <= 16, K a multiple of 64 (the
+    column slices of a TMA box), rows that start on 16-byte boundaries."""
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= 16
+            and x.shape[1] % 64 == 0
             and x.stride(1) == 1 and w.stride(1) == 1 and (x.stride(0) * 2) % 16 == 0 and (w.stride(0) * 2) % 16 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
@@ -218,14 +232,14 @@ def gemm_skinny(x, w, out, epilogue: int, err) -> None:
     eight between gate and up; out bfloat16 [M,N/2] = SiLU(gate) * up)."""
     _cuda(x, w, out)
     if not gemm_skinny_supported(x, w):
-        raise KernelError("gemm_skinny: this product is not supported (bfloat16, at most 16 rows, 16-byte aligned rows)")
+        raise KernelError("gemm_skinny: this product is not supported (bfloat16, at most 16 rows, K a multiple of 64, 16-byte aligned rows)")
     M, K = x.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.stride(1) == 1 and out.shape[0] == M
     assert out.shape[1] == (N // 2 if epilogue == EPI_SWIGLU else N)
     assert out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16)
-    map_w = tensor_map(w, int(lib().vob_gemm_skinny_weight_box(ctypes.c_long(N))))
-    map_x = tensor_map(x, 8 if M <= 8 else 16)
+    map_w = tensor_map(w, int(lib().vob_gemm_skinny_weight_box(ctypes.c_long(N))), 4)
+    map_x = tensor_map(x, 8 if M <= 8 else 16, 4)
     _check(lib().vob_gemm_skinny(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, _p(err),
                                  _stream()), "gemm_skinny")
 

@@ -320,12 +320,12 @@ def test_attention_decode_reads_the_right_far_key(key_pos, window, expect_hit):
     assert (got.mean() > 4.9) == expect_hit
 
 
-def prefill_attention(q, out, kc, vc, bt, cu_q, ctx, T, nh, kvh, hd, window, err, **_):
+def prefill_attention(q, out, kc, vc, bt, cu_q, ctx, T, nh, kvh, hd, window, err, use_tma=True, **_):
     from vllm_oxide_b200 import kernels
     B = ctx.shape[0]
     max_q = int((cu_q[1:] - cu_q[:-1]).max())
     kernels.attention_prefill(q.reshape(T, nh * hd), nh * hd, out, kc, vc, bt, cu_q, ctx, B, max_q, nh, kvh, hd, window,
-                              1.0 / math.sqrt(hd), err)
+                              1.0 / math.sqrt(hd), err, use_tma=use_tma)
 
 
 PREFILL_CASES = [  # nh, kvh, hd, block_size, window, q_lens, ctx_lens
@@ -337,13 +337,20 @@ PREFILL_CASES = [  # nh, kvh, hd, block_size, window, q_lens, ctx_lens
     (16, 1, 64, 64, 0, [65, 3], [513, 77]),
     (8, 2, 256, 64, 100, [150, 20], [400, 99]),
     (5, 5, 80, 48, 7, [50], [50]),
+    (8, 8, 64, 48, 30, [200, 31, 2], [200, 31, 48]),
+    (12, 3, 192, 32, 0, [133, 65], [333, 65]),
+    (16, 4, 128, 128, 70, [300, 129], [700, 129]),
 ]
 
 
+@pytest.mark.parametrize("use_tma", [True, False])
 @pytest.mark.parametrize("case", PREFILL_CASES)
-def test_attention_prefill(case):
+def test_attention_prefill(case, use_tma):
+    """Head sizes that are a multiple of 64 have two kernels (TMA and cp.async copies); both are checked."""
+    import functools
     nh, kvh, hd, bs, window, q_lens, ctx_lens = case
-    got, want = run_attention(prefill_attention, torch.bfloat16, nh, kvh, hd, bs, window, q_lens, ctx_lens)
+    got, want = run_attention(functools.partial(prefill_attention, use_tma=use_tma), torch.bfloat16, nh, kvh, hd, bs,
+                              window, q_lens, ctx_lens)
     assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
 
 

@@ -173,11 +173,21 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, conte
 
 
 def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, max_q, nh, kvh,
-                      hd, window: int, scale: float, err) -> None:
+                      hd, window: int, scale: float, err, use_tma: bool = True) -> None:
     """Requests that bring more than one token; the others are skipped."""
     _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens)
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
-    _check(attention_lib(hd).vob_attention_prefill(
+    L = attention_lib(hd)
+    if use_tma and L.vob_attention_decode_has_tma() and kcache.is_contiguous() and vcache.is_contiguous():
+        bs = kcache.shape[2]
+        keys, slices = L.vob_attention_decode_box_keys(bs), L.vob_attention_decode_box_slices(bs)
+        map_k, map_v = tensor_map(kcache.view(-1, hd), keys, slices), tensor_map(vcache.view(-1, hd), keys, slices)
+        _check(L.vob_attention_prefill_tma(
+            map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
+            block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, bs, window,
+            ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), _p(err), _stream()), "attention_prefill_tma")
+        return
+    _check(L.vob_attention_prefill(
         _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables), block_tables.shape[-1],
         _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, kcache.shape[2], window, ctypes.c_float(scale),
         ctypes.c_long(kcache.shape[0]), _p(err), _stream()), "attention_prefill")

@@ -34,7 +34,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __n
   if (n <= 1) return;                                   // nothing, or a decoding request
   const int G = nh / kvh;
   const int total_rows = n * G;
-  const int row0 = blockIdx.x * PF_ROWS;
+  const int row0 = (int)(gridDim.x - 1 - blockIdx.x) * PF_ROWS;   // longest blocks first
   if (row0 >= total_rows) return;
   const int ctx = context_lens[b];
   const int first_pos = ctx - n;                        // position of the portion's first token
@@ -190,7 +190,8 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   if (n <= 1) return;                                   // nothing, or a decoding request
   const int G = nh / kvh;
   const int total_rows = n * G;
-  const int row0 = blockIdx.x * PT_ROWS;
+  // later row blocks see more keys: they go first, so that the short ones fill the end of the grid
+  const int row0 = (int)(gridDim.x - 1 - blockIdx.x) * PT_ROWS;
   if (row0 >= total_rows) return;
   const int ctx = context_lens[b];
   const int first_pos = ctx - n;

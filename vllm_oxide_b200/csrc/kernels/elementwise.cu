@@ -68,6 +68,17 @@ template <> __device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16
   *reinterpret_cast<uint4*>(p) = r;
 }
 
+template <typename T> __device__ __forceinline__ float2 load2(const T* p);
+template <> __device__ __forceinline__ float2 load2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <> __device__ __forceinline__ float2 load2<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+template <typename T> __device__ __forceinline__ void store2(T* p, float2 v);
+template <> __device__ __forceinline__ void store2<float>(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+template <> __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16* p, float2 v) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y);
+}
+
 // VEC: 16-byte accesses (the row width must be a multiple of 16 bytes); otherwise one element at a time.
 template <typename T, int NT, bool VEC>
 __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const float* __restrict__ w, T* __restrict__ y,
@@ -210,10 +221,10 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
   }
   if (!is_q && !is_k) {  // value head: bias, then copy
     T* dst = vcache + (((size_t)(slot / block_size) * kvh + (head - nh - kvh)) * block_size + slot % block_size) * hd;
-    for (int i = lane; i < hd; i += 32) {
-      float v = to_f<T>(row[i]);
-      if (brow) v = round_to<T>(v + to_f<T>(brow[i]));
-      dst[i] = from_f<T>(v);
+    for (int i = 2 * lane; i < hd; i += 64) {
+      float2 v = load2<T>(row + i);
+      if (brow) { const float2 bv = load2<T>(brow + i); v.x = round_to<T>(v.x + bv.x); v.y = round_to<T>(v.y + bv.y); }
+      store2<T>(dst + i, v);
     }
     return;
   }
@@ -221,42 +232,48 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
     if (lane == 0) atomicOr(err, VOB_ERR_POSITION);
     return;
   }
+  // a lane owns pairs (i, i + hd/2) for i = 2*lane, 2*lane+1 (+64, +128, ...): two neighbouring elements per access
   const int half = hd >> 1;
   const float* w = is_q ? wq : wk;
-  constexpr int MAXP = 8;  // pairs per lane: hd <= 512
-  float x1[MAXP], x2[MAXP];
+  constexpr int MAXV = 4;  // hd <= 512
+  float2 x1[MAXV], x2[MAXV];
   float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < MAXP; ++j) {
-    const int i = lane + 32 * j;
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = 2 * lane + 64 * j;
     if (i < half) {
-      float a = to_f<T>(row[i]), b = to_f<T>(row[i + half]);
-      if (brow) { a = round_to<T>(a + to_f<T>(brow[i])); b = round_to<T>(b + to_f<T>(brow[i + half])); }
+      float2 a = load2<T>(row + i), b = load2<T>(row + i + half);
+      if (brow) {
+        const float2 ba = load2<T>(brow + i), bb = load2<T>(brow + i + half);
+        a.x = round_to<T>(a.x + ba.x); a.y = round_to<T>(a.y + ba.y);
+        b.x = round_to<T>(b.x + bb.x); b.y = round_to<T>(b.y + bb.y);
+      }
       x1[j] = a; x2[j] = b;
-      ss += a * a + b * b;
+      ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
     }
   }
   if (w) {
     ss = warp_sum(ss);
     const float denom = sqrtf(ss / (float)hd + eps);
 #pragma unroll
-    for (int j = 0; j < MAXP; ++j) {
-      const int i = lane + 32 * j;
+    for (int j = 0; j < MAXV; ++j) {
+      const int i = 2 * lane + 64 * j;
       if (i < half) {
-        x1[j] = round_to<T>(round_to<T>(x1[j] / denom) * w[i]);
-        x2[j] = round_to<T>(round_to<T>(x2[j] / denom) * w[i + half]);
+        const float2 wa = *reinterpret_cast<const float2*>(w + i), wb = *reinterpret_cast<const float2*>(w + i + half);
+        x1[j].x = round_to<T>(round_to<T>(x1[j].x / denom) * wa.x); x1[j].y = round_to<T>(round_to<T>(x1[j].y / denom) * wa.y);
+        x2[j].x = round_to<T>(round_to<T>(x2[j].x / denom) * wb.x); x2[j].y = round_to<T>(round_to<T>(x2[j].y / denom) * wb.y);
       }
     }
   }
   const float* cs = cos_sin + (size_t)pos * hd;
   T* dst = is_q ? row : kcache + (((size_t)(slot / block_size) * kvh + (head - nh)) * block_size + slot % block_size) * hd;
 #pragma unroll
-  for (int j = 0; j < MAXP; ++j) {
-    const int i = lane + 32 * j;
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = 2 * lane + 64 * j;
     if (i < half) {
-      const float c = cs[i], s = cs[i + half];
-      dst[i] = from_f<T>(x1[j] * c - x2[j] * s);
-      dst[i + half] = from_f<T>(x2[j] * c + x1[j] * s);
+      const float2 c = *reinterpret_cast<const float2*>(cs + i), sn = *reinterpret_cast<const float2*>(cs + i + half);
+      store2<T>(dst + i, make_float2(x1[j].x * c.x - x2[j].x * sn.x, x1[j].y * c.y - x2[j].y * sn.y));
+      store2<T>(dst + i + half, make_float2(x2[j].x * c.x + x1[j].x * sn.x, x2[j].y * c.y + x1[j].y * sn.y));
     }
   }
 }

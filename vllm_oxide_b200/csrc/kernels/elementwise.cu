@@ -80,11 +80,13 @@ template <> __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16*
 }
 
 // VEC: 16-byte accesses (the row width must be a multiple of 16 bytes); otherwise one element at a time.
-template <typename T, int NT, bool VEC>
+// REG: the row's sums stay in registers between the two passes (rows of at most 4 * NT 16-byte pieces); else they
+// are parked in shared memory.  The order of additions is the same in all three and depends on H only.
+template <typename T, int NT, bool VEC, bool REG>
 __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const float* __restrict__ w, T* __restrict__ y,
                                    const int* __restrict__ rows, int H, int num_src_rows, float eps, int has_residual,
                                    int* err) {
-  extern __shared__ float srow[];  // H floats
+  extern __shared__ float srow[];  // H floats (unused with REG)
   __shared__ float scratch[32];
   pdl_launch_dependents();
   const int r = blockIdx.x;
@@ -101,6 +103,45 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const f
   T* rr = residual + (size_t)src * H;
   T* yr = y + (size_t)r * H;
   float ss = 0.f;
+  if (VEC && REG) {
+    constexpr int N = Vec16<T>::N, IT = 4;
+    float v[IT][N];
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+      const int i = (threadIdx.x + it * NT) * N;
+      if (i < H) {
+        load16<T>(xr + i, v[it]);
+        if (has_residual) {
+          float q[N];
+          load16<T>(rr + i, q);
+#pragma unroll
+          for (int j = 0; j < N; ++j) v[it][j] += q[j];
+        }
+      }
+    }
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+      const int i = (threadIdx.x + it * NT) * N;
+      if (i < H) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) ss += v[it][j] * v[it][j];
+        if (!rows) store16<T>(rr + i, v[it]);
+      }
+    }
+    const float total = block_sum<NT>(ss, scratch);
+    const float denom = sqrtf(total / (float)H + eps);
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+      const int i = (threadIdx.x + it * NT) * N;
+      if (i < H) {
+        float o[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) o[j] = round_to<T>(v[it][j] / denom) * w[i + j];
+        store16<T>(yr + i, o);
+      }
+    }
+    return;
+  }
   if (VEC) {
     constexpr int N = Vec16<T>::N;
     for (int i = threadIdx.x * N; i < H; i += NT * N) {
@@ -305,19 +346,23 @@ template <typename T>
 static int add_rmsnorm_launch(const void* x, void* residual, const float* w, void* y, const int* rows, int n_out, int H,
                               int num_src_rows, float eps, int has_residual, int* err, cudaStream_t stream) {
   constexpr int NT = 256;
-  const size_t smem = (size_t)H * sizeof(float);
-  if (smem > 200 * 1024) return VOB_UNSUPPORTED;
   const bool vec = ((size_t)H * sizeof(T)) % 16 == 0 && ((uintptr_t)x | (uintptr_t)residual | (uintptr_t)y) % 16 == 0;
+  const bool reg = vec && H <= 4 * NT * Vec16<T>::N;
+  const size_t smem = reg ? 0 : (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) return VOB_UNSUPPORTED;
   if (smem > 48 * 1024) {
-    cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                        : cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                        : cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
+  if (reg)
+    return launch_kernel(add_rmsnorm_kernel<T, NT, true, true>, n_out, NT, smem, stream, (const T*)x, (T*)residual, w, (T*)y, rows,
+                         H, num_src_rows, eps, has_residual, err);
   if (vec)
-    return launch_kernel(add_rmsnorm_kernel<T, NT, true>, n_out, NT, smem, stream, (const T*)x, (T*)residual, w, (T*)y, rows, H,
-                         num_src_rows, eps, has_residual, err);
-  return launch_kernel(add_rmsnorm_kernel<T, NT, false>, n_out, NT, smem, stream, (const T*)x, (T*)residual, w, (T*)y, rows, H,
-                       num_src_rows, eps, has_residual, err);
+    return launch_kernel(add_rmsnorm_kernel<T, NT, true, false>, n_out, NT, smem, stream, (const T*)x, (T*)residual, w, (T*)y, rows,
+                         H, num_src_rows, eps, has_residual, err);
+  return launch_kernel(add_rmsnorm_kernel<T, NT, false, false>, n_out, NT, smem, stream, (const T*)x, (T*)residual, w, (T*)y, rows,
+                       H, num_src_rows, eps, has_residual, err);
 }
 
 // y[n_out, H]; x and residual [num_src_rows, H]; rows may be null (then n_out == num_src_rows).

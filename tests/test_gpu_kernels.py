@@ -526,3 +526,39 @@ def test_gemm_skinny_refuses_what_it_cannot_take():
     assert not kernels.gemm_skinny_supported(x[:4].float(), w.float())
     with pytest.raises(kernels.KernelError, match="not supported"):
         kernels.gemm_skinny(x, w, torch.zeros(17, 8, dtype=torch.bfloat16, device=DEV), kernels.EPI_BF16, err_word())
+
+
+@pytest.mark.parametrize("M,N,K", [(17, 128, 64), (32, 256, 128), (33, 331, 80), (64, 4096, 4096), (100, 517, 200),
+                                   (128, 1000, 1024), (8, 128, 64), (64, 24576 // 8, 512), (48, 130, 12288)])
+def test_gemm_tc5(M, N, K):
+    """The tcgen05 product (accumulator in tensor memory) against a float64 product."""
+    from vllm_oxide_b200 import kernels
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().to(DEV)
+    assert kernels.gemm_tc5_supported(x, w)
+    err = err_word()
+    ref = x.double() @ w.double().t()
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tc5(x, w, out, kernels.EPI_BF16, err)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    assert torch.allclose(out.double(), ref, rtol=1e-2, atol=1e-2)
+    outf = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.gemm_tc5(x, w, outf, kernels.EPI_F32, err)
+    assert torch.equal(outf, out.float()) and err.item() == 0
+
+
+@pytest.mark.parametrize("M,I,K", [(17, 8, 64), (64, 12288 // 4, 1024), (40, 104, 128), (128, 200, 192)])
+def test_gemm_tc5_swiglu(M, I, K):
+    from vllm_oxide_b200 import kernels
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    wg = (2 * torch.randn(I, K, generator=g) / math.sqrt(K)).bfloat16()
+    wu = (torch.randn(I, K, generator=g) / math.sqrt(K)).bfloat16()
+    want = P.swiglu(x, wg, wu, torch.eye(I).bfloat16(), torch.bfloat16)
+    wgu = torch.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], dim=1).reshape(2 * I, K)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = err_word()
+    kernels.gemm_tc5(x.to(DEV), wgu.to(DEV), out, kernels.EPI_SWIGLU, err)
+    assert torch.allclose(out.cpu().float(), want.float(), rtol=2e-2, atol=2e-2) and err.item() == 0

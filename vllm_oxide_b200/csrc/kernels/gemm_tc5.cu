@@ -1,0 +1,265 @@
+// out[M,N] = x[M,K] * W[N,K]^T in bfloat16 for steps of 17 to 128 tokens (decoding at larger batch sizes,
+// short portions), on the fifth-generation tensor cores: tcgen05.mma with the accumulator in tensor memory.
+//
+// Such a product still costs the time to read W once, so the weights are the 128-row operand ("swap-AB"):
+// a tile is 128 rows of W against all tokens of the step (padded to 32, 64 or 128), D[128 x tokens] in float
+// lives in TMEM, and every byte of W is read exactly once.  One block per SM walks the tiles:
+//   warp 0      producer: per 64 columns of K one TMA copy of the W tile [128 x 64] and one of the tokens
+//               [tokens x 64] (128-byte swizzle) into a ring of stages;
+//   warp 1      allocates TMEM (two accumulators) and issues the MMAs: four tcgen05.mma (K = 16 each) per
+//               stage from shared-memory descriptors; tcgen05.commit hands a stage back to the producer and,
+//               after the last one of a tile, the accumulator to the epilogue;
+//   warps 2-5   epilogue: tcgen05.ld brings the accumulator to registers (a thread owns one row of W, that is
+//               one output feature, for all tokens), rounds, and stores; the next tile's MMAs run meanwhile
+//               into the other accumulator.
+// Epilogues as in the weight-streaming kernel for smaller steps: bfloat16, float logits, SiLU(gate)*up over
+// interleaved gate/up rows.  Every wait on an mbarrier is bounded; on a timeout the block sets an error bit,
+// stops issuing work, and still frees its TMEM before it returns.
+#include "tensor_map.cuh"
+
+namespace vob {
+
+constexpr int T5_ROWS = 128;      // rows of W per tile (the MMA's M)
+constexpr int T5_KC = 64;         // columns of K per stage: one 128-byte swizzle atom
+constexpr int T5_THREADS = 192;
+constexpr int T5_EPI_WARPS = 4;
+
+enum { T5_EPI_BF16 = 0, T5_EPI_F32 = 1, T5_EPI_SWIGLU = 2 };
+
+// Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzled layout (rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart): start address, leading offset (unused here), stride between row groups,
+// descriptor version 1, layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t t5_smem_desc(const void* p) {
+  const uint64_t addr = (uint64_t)((smem_addr(p) & 0x3FFFF) >> 4);
+  return addr | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor of kind::f16: float accumulator, bfloat16 A and B, both K-major, N and M of the tile.
+__device__ __forceinline__ uint32_t t5_instr_desc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void t5_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void t5_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void t5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void t5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+// 32 lanes x 32 columns of 32-bit: thread i of the warp gets its lane's 32 consecutive columns.
+__device__ __forceinline__ void t5_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                 "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                 "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                 "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ float t5_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+template <int NT> struct T5Stages { static constexpr int N = (192 * 1024) / ((T5_ROWS + NT) * 128); };
+
+// tmW: W [N, K] as 2-D map with box [128 rows, 64 columns]; tmX: x [M, K] with box [NT rows, 64 columns].
+template <int NT, int EPI>
+__global__ void __launch_bounds__(T5_THREADS, 1)
+gemm_tc5_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, void* __restrict__ out,
+                long ldo, int M, int N, int K, int num_tiles, int* err) {
+  constexpr int S = T5Stages<NT>::N > 8 ? 8 : T5Stages<NT>::N;
+  constexpr int A_BYTES = T5_ROWS * 128, B_BYTES = NT * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = 2 * NT < 32 ? 32 : 2 * NT;      // two accumulators; a power of two
+  extern __shared__ __align__(1024) char smem_raw[];
+  char* stages = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(stages + S * STAGE_BYTES);
+  uint64_t* empty = full + S;
+  uint64_t* acc_full = empty + S;       // [2] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2;   // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_iters = (K + T5_KC - 1) / T5_KC;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], T5_EPI_WARPS); }
+    *abort_flag = 0;
+    tma_prefetch_map(&tmW);
+    tma_prefetch_map(&tmX);
+  }
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  if (warp == 1) {   // one warp allocates the tensor memory for the block and publishes its address
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  t5_fence_before();
+  __syncthreads();
+  t5_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (warp == 0) {
+    // ------------------------------------------------ producer (one thread)
+    if (lane == 0) {
+      const long total = (long)my_tiles * k_iters;
+      // W does not depend on the kernel before this one: its first stages are on their way before that kernel ends
+      const int ahead = total < S ? (int)total : S;
+      for (int it0 = 0; it0 < ahead; ++it0) {
+        const int tile = blockIdx.x + (it0 / k_iters) * gridDim.x, kb = it0 % k_iters;
+        mbar_expect_tx(&full[it0], (unsigned)STAGE_BYTES);
+        tma_load_2d(stages + it0 * STAGE_BYTES, &tmW, kb * T5_KC, tile * T5_ROWS, &full[it0]);
+      }
+      pdl_wait();
+      for (int it0 = 0; it0 < ahead; ++it0)
+        tma_load_2d(stages + it0 * STAGE_BYTES + A_BYTES, &tmX, (it0 % k_iters) * T5_KC, 0, &full[it0]);
+      long it = ahead;
+      for (; it < total; ++it) {
+        const int tile = blockIdx.x + (int)(it / k_iters) * gridDim.x, kb = (int)(it % k_iters);
+        const int s = (int)(it % S);
+        if (!mbar_wait(&empty[s], (unsigned)(((it / S) - 1) & 1), abort_flag, err)) break;
+        mbar_expect_tx(&full[s], (unsigned)STAGE_BYTES);
+        tma_load_2d(stages + s * STAGE_BYTES, &tmW, kb * T5_KC, tile * T5_ROWS, &full[s]);
+        tma_load_2d(stages + s * STAGE_BYTES + A_BYTES, &tmX, kb * T5_KC, 0, &full[s]);
+      }
+      const long first = it > S ? it - S : 0;       // copies in flight must land before the block exits
+      for (long j = first; j < it; ++j) {
+        bool done = false;
+        for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % S], (unsigned)((j / S) & 1));
+        if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer (one thread)
+    if (lane == 0) {
+      const uint32_t idesc = t5_instr_desc(T5_ROWS, NT);
+      long it = 0;
+      bool ok = true;
+      for (int lt = 0; lt < my_tiles && ok; ++lt) {
+        const int a = lt & 1;
+        if (lt >= 2) {   // the epilogue must have drained this accumulator (two tiles ago)
+          ok = mbar_wait(&acc_empty[a], (unsigned)(((lt >> 1) - 1) & 1), abort_flag, err);
+          if (!ok) break;
+          t5_fence_after();
+        }
+        const uint32_t d_tmem = tmem_base + (uint32_t)(a * NT);
+        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+          const int s = (int)(it % S);
+          ok = mbar_wait(&full[s], (unsigned)((it / S) & 1), abort_flag, err);
+          if (!ok) break;
+          t5_fence_after();
+          const char* st = stages + s * STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < T5_KC / 16; ++k)      // 16 columns = 32 bytes further into the swizzle atom
+            t5_mma(d_tmem, t5_smem_desc(st + k * 32), t5_smem_desc(st + A_BYTES + k * 32), idesc, (kb | k) ? 1u : 0u);
+          t5_commit(&empty[s]);                      // the stage is free once these MMAs have read it
+        }
+        if (ok) t5_commit(&acc_full[a]);             // the accumulator is complete once they have all finished
+      }
+    }
+  } else {
+    // ------------------------------------------------ epilogue: warp w reads TMEM lanes 32*(w%4) .. +31
+    pdl_wait();   // `out` may still be read by the kernel before this one
+    const int q = warp & 3;
+    const int m_rows = M < NT ? M : NT;
+    for (int lt = 0; lt < my_tiles; ++lt) {
+      const int tile = blockIdx.x + lt * gridDim.x;
+      const int a = lt & 1;
+      bool ok = mbar_wait(&acc_full[a], (unsigned)((lt >> 1) & 1), abort_flag, err);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      t5_fence_after();
+      const long n = (long)tile * T5_ROWS + q * 32 + lane;        // this thread's row of W: one output feature
+#pragma unroll
+      for (int c0 = 0; c0 < NT; c0 += 32) {
+        float v[32];
+        t5_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * NT + c0), v);
+        if (EPI == T5_EPI_SWIGLU) {
+          // rows alternate in groups of eight between gate and up: lane l (l & 8 == 0) holds a gate row, lane l + 8 its up row
+          const long n_out = (long)tile * (T5_ROWS / 2) + q * 16 + (lane >> 4) * 8 + (lane & 7);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float up = __shfl_down_sync(0xffffffffu, v[j], 8);
+            const int tok = c0 + j;
+            if ((lane & 8) == 0 && tok < m_rows && n_out < N / 2) {
+              const float g = t5_round(v[j]);
+              const float act = t5_round(g / (1.f + expf(-g)));
+              reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n_out] = __float2bfloat16_rn(act * t5_round(up));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tok = c0 + j;
+            if (tok < m_rows && n < N) {
+              if (EPI == T5_EPI_F32) reinterpret_cast<float*>(out)[(long)tok * ldo + n] = t5_round(v[j]);
+              else reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        }
+      }
+      t5_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[a]);
+    }
+  }
+  // every path ends here: the tensor memory goes back before the block exits
+  t5_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    t5_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+template <int NT, int EPI>
+static int tc5_launch(const CUtensorMap* tmW, const CUtensorMap* tmX, void* out, long ldo, int M, int N, int K, int* err,
+                      cudaStream_t stream) {
+  constexpr int S = T5Stages<NT>::N > 8 ? 8 : T5Stages<NT>::N;
+  const int smem = 1024 + S * (T5_ROWS + NT) * 128 + (2 * S + 4) * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int num_tiles = (N + T5_ROWS - 1) / T5_ROWS;
+  const int grid = num_tiles < 148 ? num_tiles : 148;
+  return launch_kernel(gemm_tc5_kernel<NT, EPI>, grid, T5_THREADS, smem, stream, *tmW, *tmX, out, ldo, M, N, K, num_tiles, err);
+}
+
+template <int NT>
+static int tc5_dispatch(int epilogue, const CUtensorMap* tw, const CUtensorMap* tx, void* out, long ldo, int M, int N, int K,
+                        int* err, cudaStream_t stream) {
+  if (epilogue == T5_EPI_BF16) return tc5_launch<NT, T5_EPI_BF16>(tw, tx, out, ldo, M, N, K, err, stream);
+  if (epilogue == T5_EPI_F32) return tc5_launch<NT, T5_EPI_F32>(tw, tx, out, ldo, M, N, K, err, stream);
+  if (epilogue == T5_EPI_SWIGLU) return tc5_launch<NT, T5_EPI_SWIGLU>(tw, tx, out, ldo, M, N, K, err, stream);
+  return VOB_BAD_ARGUMENT;
+}
+
+}  // namespace vob
+
+using namespace vob;
+
+// Rows of the token box for a step of M tokens (32, 64 or 128).
+VOB_API int vob_gemm_tc5_token_box(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
+
+// map_w: vob_tensor_map_bf16_2d of W [N, K] with box rows 128; map_x: of x [M, K] with box rows
+// vob_gemm_tc5_token_box(M).  epilogue: 0 bfloat16 out [M,N]; 1 float out [M,N] (rounded to bfloat16 first);
+// 2 SiLU(gate)*up over rows that alternate in groups of eight between gate and up, out [M,N/2].  Needs M <= 128.
+VOB_API int vob_gemm_tc5(const void* map_w, const void* map_x, void* out, long ldo, int M, int N, int K, int epilogue,
+                         int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 128 || K <= 0 || K % 8 || !map_w || !map_x) return VOB_UNSUPPORTED;
+  if (epilogue == T5_EPI_SWIGLU && N % 16) return VOB_BAD_ARGUMENT;
+  const CUtensorMap* tw = (const CUtensorMap*)map_w;
+  const CUtensorMap* tx = (const CUtensorMap*)map_x;
+  if (M <= 32) return tc5_dispatch<32>(epilogue, tw, tx, out, ldo, M, N, K, err, stream);
+  if (M <= 64) return tc5_dispatch<64>(epilogue, tw, tx, out, ldo, M, N, K, err, stream);
+  return tc5_dispatch<128>(epilogue, tw, tx, out, ldo, M, N, K, err, stream);
+}

@@ -227,6 +227,48 @@ def tensor_map(t: torch.Tensor, box_rows: int, box_slices: int):
     return hit[1]
 
 
+def tensor_map_2d(t: torch.Tensor, box_rows: int):
+    """A TMA descriptor (host memory, cached) of a row-major bfloat16 matrix with box [box_rows, 64 columns]."""
+    key = (t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows, "2d")
+    hit = _tensor_maps.get(key)
+    if hit is None:
+        raw = (ctypes.c_char * 256)()
+        addr = (ctypes.addressof(raw) + 63) & ~63
+        code = lib().vob_tensor_map_bf16_2d(ctypes.c_void_p(addr), _p(t), ctypes.c_long(t.shape[0]), ctypes.c_long(t.shape[1]),
+                                            ctypes.c_long(t.stride(0)), box_rows)
+        if code != 0:
+            raise KernelError(f"tensor map for a [{t.shape[0]}, {t.shape[1]}] matrix: {lib().vob_error_string(code).decode()}")
+        if len(_tensor_maps) > 4096:
+            _tensor_maps.clear()
+        hit = _tensor_maps[key] = (raw, ctypes.c_void_p(addr))
+    return hit[1]
+
+
+def gemm_tc5_supported(x, w) -> bool:
+    """Whether the tcgen05 product takes x[M,K] @ w[N,K]^T: bfloat16, at most 128 rows of x, K a multiple of 8,
+    rows that start on 16-byte boundaries."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and 0 < x.shape[0] <= 128
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and (x.stride(0) * 2) % 16 == 0
+            and (w.stride(0) * 2) % 16 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc5(x, w, out, epilogue: int, err) -> None:
+    """out = x @ w^T on the tcgen05 tensor cores for at most 128 rows of x; epilogues as gemm_skinny."""
+    _cuda(x, w, out)
+    if not gemm_tc5_supported(x, w):
+        raise KernelError("gemm_tc5: this product is not supported (bfloat16, at most 128 rows, K a multiple of 8, "
+                          "16-byte aligned rows)")
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.stride(1) == 1 and out.shape[0] == M
+    assert out.shape[1] == (N // 2 if epilogue == EPI_SWIGLU else N)
+    assert out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16)
+    map_w = tensor_map_2d(w, 128)
+    map_x = tensor_map_2d(x, int(lib().vob_gemm_tc5_token_box(M)))
+    _check(lib().vob_gemm_tc5(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, _p(err), _stream()),
+           "gemm_tc5")
+
+
 def gemm_skinny_supported(x, w) -> bool:
     """Whether the weight-streaming kernel takes x[M,K] @ w[N,K]^T: bfloat16, M <= 16, K a multiple of 64 (the
     column slices of a TMA box), rows that start on 16-byte boundaries."""

@@ -547,6 +547,15 @@ def test_gemm_tc5(M, N, K):
     outf = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
     kernels.gemm_tc5(x, w, outf, kernels.EPI_F32, err)
     assert torch.equal(outf, out.float()) and err.item() == 0
+    # with and without a split along K, twice in a row (the counters must come back to zero)
+    for ksplit in (1, 2, 3):
+        k_iters = -(-K // 64)
+        if (ksplit - 1) * -(-k_iters // ksplit) >= k_iters:
+            continue                      # a K range would be empty
+        for _ in range(2):
+            o2 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+            kernels.gemm_tc5(x, w, o2, kernels.EPI_BF16, err, ksplit=ksplit)
+            assert torch.allclose(o2.double(), ref, rtol=1e-2, atol=1e-2) and err.item() == 0
 
 
 @pytest.mark.parametrize("M,I,K", [(17, 8, 64), (64, 12288 // 4, 1024), (40, 104, 128), (128, 200, 192)])
@@ -562,3 +571,7 @@ def test_gemm_tc5_swiglu(M, I, K):
     err = err_word()
     kernels.gemm_tc5(x.to(DEV), wgu.to(DEV), out, kernels.EPI_SWIGLU, err)
     assert torch.allclose(out.cpu().float(), want.float(), rtol=2e-2, atol=2e-2) and err.item() == 0
+    if K >= 128:
+        out.fill_(float("nan"))
+        kernels.gemm_tc5(x.to(DEV), wgu.to(DEV), out, kernels.EPI_SWIGLU, err, ksplit=2)
+        assert torch.allclose(out.cpu().float(), want.float(), rtol=2e-2, atol=2e-2) and err.item() == 0

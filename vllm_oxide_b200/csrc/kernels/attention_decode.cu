@@ -172,7 +172,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                             const __nv_bfloat16* __restrict__ q, long q_stride, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                             const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
-                            long num_pages, float* __restrict__ part_o, float* __restrict__ part_lse, int box_keys, int* err) {
+                            long num_pages, float* __restrict__ part_o, float* __restrict__ part_lse,
+                            int box_keys, int* err) {
   extern __shared__ __align__(1024) char smem_raw[];
   char* smem = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int MERGE_BYTES = (2 * DEC_WARPS * 16 + DEC_WARPS * 16 * HD) * 4;
@@ -194,8 +195,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   __syncthreads();
-  pdl_wait();
-  if (t_next - t != 1) return;                         // not a decoding request (uniform for the block)
+  // The step's index arrays, the block tables and the keys and values before this step's token were written
+  // before this step's kernels began; the kernels of this step write this token's query, key and value only.
+  // So the producer waits for the kernels before this one only when it comes to the tile that holds the new key,
+  // and the consumers wait before they read the query: the older tiles stream in while those kernels still run.
+  if (t_next - t != 1) { pdl_wait(); return; }         // not a decoding request (uniform for the block)
   const int G = nh / kvh;
   const int pos = context - 1;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -211,58 +215,65 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   st.clear();
 
   if (warp == DEC_WARPS) {
-    // ------------------------------------------------ producer (one thread)
-    if (lane == 0 && n_tiles > 0) {
-      int pages[DEC_TILE / RUN_KEYS];
-      tile_pages<DEC_TILE>(pages, table, block_size, start, lo, end);
-      bool ok = true;
+    // ------------------------------------------------ producer: lane 0 issues, all lanes look pages up
+    {
+      WarpPages wp;
+      bool ok = true, waited = false;
       int it = 0;
       for (; it < n_tiles; ++it) {
         const int s = it % DT_STAGES;
-        if (it >= DT_STAGES) {
-          ok = mbar_wait(&empty[s], (unsigned)(((it / DT_STAGES) - 1) & 1), abort_flag, err);
-          if (!ok) break;
-        }
-        mbar_expect_tx(&full[s], (unsigned)DT_STAGE_BYTES);
-        char* kt = smem + s * DT_STAGE_BYTES;
-        const int tile_start = start + it * DEC_TILE;
-        if (box_keys == DEC_TILE) {
-          // the tile lies in one page: one copy of K, one of V (the page of its first run serves all of it)
-          const int page = pages[0] != PAGE_NONE ? pages[0] : (pages[1] != PAGE_NONE ? pages[1] : (pages[2] != PAGE_NONE ? pages[2] : pages[3]));
-          const bool page_ok = page >= 0 && page < num_pages;
-          if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
-          const int row = page_ok ? (page * kvh + kh) * block_size + tile_start % block_size : 0;
-          tma_load_3d(kt, &tmK, 0, row, 0, &full[s]);
-          tma_load_3d(kt + DT_TILE_BYTES, &tmV, 0, row, 0, &full[s]);
-        } else {
+        wp.advance(table, block_size, start, it, lane, lo, end);
+        int pg[4];
 #pragma unroll
-          for (int run = 0; run < DEC_TILE / RUN_KEYS; ++run) {
-            const int page = pages[run];
-            const bool page_ok = page >= 0 && page < num_pages;
-            if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
-            // a run nobody will read is filled from row 0 of the plane: finite values that the mask zeroes
-            const int key0 = tile_start + run * RUN_KEYS;
-            const int row = page_ok ? (page * kvh + kh) * block_size + key0 % block_size : 0;
-            // a 16-row box covers rows run*16.. of every slice: slices are DEC_TILE rows apart in shared memory,
-            // but a box writes its slices box_rows apart, so each slice gets a copy of its own
+        for (int run = 0; run < 4; ++run) pg[run] = wp.page(it, run);
+        if (lane == 0) {
+          if (it >= DT_STAGES) ok = mbar_wait(&empty[s], (unsigned)(((it / DT_STAGES) - 1) & 1), abort_flag, err);
+          if (ok) {
+            const int tile_start = start + it * DEC_TILE;
+            if (!waited && tile_start + DEC_TILE > pos) { pdl_wait(); waited = true; }
+            mbar_expect_tx(&full[s], (unsigned)DT_STAGE_BYTES);
+            char* kt = smem + s * DT_STAGE_BYTES;
+            if (box_keys == DEC_TILE) {
+              // the tile lies in one page: one copy of K, one of V (any run that is wanted names the page)
+              const int page = pg[0] != PAGE_NONE ? pg[0] : (pg[1] != PAGE_NONE ? pg[1] : (pg[2] != PAGE_NONE ? pg[2] : pg[3]));
+              const bool page_ok = page >= 0 && page < num_pages;
+              if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
+              const int row = page_ok ? (page * kvh + kh) * block_size + tile_start % block_size : 0;
+              tma_load_3d(kt, &tmK, 0, row, 0, &full[s]);
+              tma_load_3d(kt + DT_TILE_BYTES, &tmV, 0, row, 0, &full[s]);
+            } else {
 #pragma unroll
-            for (int c = 0; c < DT_SLICES; ++c) {
-              tma_load_3d(kt + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmK, 0, row, c, &full[s]);
-              tma_load_3d(kt + DT_TILE_BYTES + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, row, c, &full[s]);
+              for (int run = 0; run < 4; ++run) {
+                const bool page_ok = pg[run] >= 0 && pg[run] < num_pages;
+                if (!page_ok && pg[run] != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
+                // a run nobody will read is filled from row 0 of the plane: finite values that the mask zeroes
+                const int key0 = tile_start + run * RUN_KEYS;
+                const int row = page_ok ? (pg[run] * kvh + kh) * block_size + key0 % block_size : 0;
+                // a 16-row box writes its slices 16 rows apart, the tile keeps them DEC_TILE rows apart: a copy per slice
+#pragma unroll
+                for (int c = 0; c < DT_SLICES; ++c) {
+                  tma_load_3d(kt + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmK, 0, row, c, &full[s]);
+                  tma_load_3d(kt + DT_TILE_BYTES + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, row, c, &full[s]);
+                }
+              }
             }
           }
         }
-        if (it + 1 < n_tiles) tile_pages<DEC_TILE>(pages, table, block_size, tile_start + DEC_TILE, lo, end);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
       }
-      const int first = it > DT_STAGES ? it - DT_STAGES : 0;     // copies in flight must land before the block exits
-      for (int j = first; j < it; ++j) {
-        bool done = false;
-        for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % DT_STAGES], (unsigned)((j / DT_STAGES) & 1));
-        if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+      if (lane == 0) {
+        const int first = it > DT_STAGES ? it - DT_STAGES : 0;     // copies in flight must land before the block exits
+        for (int j = first; j < it; ++j) {
+          bool done = false;
+          for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % DT_STAGES], (unsigned)((j / DT_STAGES) & 1));
+          if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+        }
       }
     }
   } else {
     // ------------------------------------------------ consumers: warp w takes keys 16w..16w+15 of every tile
+    pdl_wait();
     const int g = lane >> 2, tq = lane & 3;
     uint32_t qf[KSTEPS][4];
     {
@@ -303,6 +314,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
       if (lane == 0) mbar_arrive(&empty[s]);
     }
   }
+  pdl_wait();             // (a no-op for threads that have waited) nothing is written before the kernels before are done
   __syncthreads();        // every stage has been read (or given up): the merge may reuse the memory
   if (*abort_flag) return;
   float* wm = reinterpret_cast<float*>(smem);                 // [DEC_WARPS][16]
@@ -417,7 +429,7 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
     static bool tma_configured = false;
     constexpr int MERGE = (2 * DEC_WARPS * 16 + DEC_WARPS * 16 * HD) * 4;
     constexpr int DATA = DT_STAGES * DT_STAGE_BYTES > MERGE ? DT_STAGES * DT_STAGE_BYTES : MERGE;
-    const int tma_smem = 1024 + DATA + 2 * DT_STAGES * 8 + 16;
+    const int tma_smem = 1024 + DATA + 2 * DT_STAGES * 8 + 32;
     if (!tma_configured) {
       cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tma_smem);
       if (e != cudaSuccess) return (int)e;
@@ -427,7 +439,10 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
                        *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, block_tables,
                        table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, part_o, part_lse,
                        block_size % DEC_TILE == 0 ? DEC_TILE : RUN_KEYS, err);
-  } else
+    if (rc || num_splits == 1) return rc;
+    return launch_kernel(attention_decode_combine_kernel, dim3(nh, num_requests), HD < 128 ? 64 : 128, 0, stream,
+                         (const float*)part_o, (const float*)part_lse, (__nv_bfloat16*)out, cu_q, nh, num_splits);
+  }
 #endif
   rc = launch_kernel(attention_decode_kernel, grid, DEC_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, q_stride,
                          (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,

@@ -250,4 +250,27 @@ __device__ __forceinline__ void softmax_pv_16keys_swizzled(WarpSoftmax& st, floa
   }
 }
 
+// Page ids for a TMA producer warp.  A look-up is a global load with a long latency, and a producer that needs
+// one per tile cannot run ahead of it; so the warp's 32 lanes fetch the pages of 32 runs of 16 keys (8 tiles) at
+// once, one chunk ahead of their use, and hand them to the issuing lane by shuffle.
+struct WarpPages {
+  int cur = PAGE_NONE, next = PAGE_NONE;   // this lane's run in the current and in the next chunk
+  __device__ __forceinline__ int fetch(const int* __restrict__ table, int block_size, int first_key, int chunk, int lane,
+                                       int begin, int end) const {
+    const int key0 = first_key + (chunk * 32 + lane) * RUN_KEYS;
+    return (key0 < end && key0 + RUN_KEYS > begin) ? table[key0 / block_size] : PAGE_NONE;
+  }
+  // call with all lanes at tile `it` (tiles of 64 keys = 4 runs) before `page()`
+  __device__ __forceinline__ void advance(const int* __restrict__ table, int block_size, int first_key, int it, int lane,
+                                          int begin, int end) {
+    if ((it & 7) == 0) {
+      const int chunk = it >> 3;
+      cur = it == 0 ? fetch(table, block_size, first_key, 0, lane, begin, end) : next;
+      next = fetch(table, block_size, first_key, chunk + 1, lane, begin, end);
+    }
+  }
+  // page of run `run` (0..3) of tile `it`, the same value in every lane
+  __device__ __forceinline__ int page(int it, int run) const { return __shfl_sync(0xffffffffu, cur, ((it & 7) << 2) + run); }
+};
+
 }  // namespace vob

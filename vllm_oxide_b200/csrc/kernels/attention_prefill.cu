@@ -204,46 +204,59 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   const int n_tiles = (key_end - start + PT_TILE - 1) / PT_TILE;
 
   if (warp == PT_WARPS) {
-    // ------------------------------------------------ producer (one thread)
-    if (lane == 0) {
-      int pages[PT_TILE / RUN_KEYS];
-      tile_pages<PT_TILE>(pages, table, block_size, start, key_lo, key_end);
+    // ------------------------------------------------ producer: lane 0 issues, all lanes look pages up
+    {
+      WarpPages wp;
+      bool ok = true;
       int it = 0;
       for (; it < n_tiles; ++it) {
         const int s = it % PT_STAGES;
-        if (it >= PT_STAGES && !mbar_wait(&empty[s], (unsigned)(((it / PT_STAGES) - 1) & 1), abort_flag, err)) break;
-        mbar_expect_tx(&full[s], (unsigned)PT_STAGE_BYTES);
-        char* kt = smem + s * PT_STAGE_BYTES;
-        const int tile_start = start + it * PT_TILE;
-        if (box_keys == PT_TILE) {
-          const int page = pages[0] != PAGE_NONE ? pages[0] : (pages[1] != PAGE_NONE ? pages[1] : (pages[2] != PAGE_NONE ? pages[2] : pages[3]));
-          const bool page_ok = page >= 0 && page < num_pages;
-          if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
-          const int row = page_ok ? (page * kvh + kh) * block_size + tile_start % block_size : 0;
-          tma_load_3d(kt, &tmK, 0, row, 0, &full[s]);
-          tma_load_3d(kt + PT_TILE_BYTES, &tmV, 0, row, 0, &full[s]);
-        } else {
+        wp.advance(table, block_size, start, it, lane, key_lo, key_end);
+        int pg[4];
 #pragma unroll
-          for (int run = 0; run < PT_TILE / RUN_KEYS; ++run) {
-            const int page = pages[run];
-            const bool page_ok = page >= 0 && page < num_pages;
-            if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
-            const int key0 = tile_start + run * RUN_KEYS;
-            const int row = page_ok ? (page * kvh + kh) * block_size + key0 % block_size : 0;
+        for (int run = 0; run < 4; ++run) pg[run] = wp.page(it, run);
+        if (lane == 0) {
+          if (it >= PT_STAGES) ok = mbar_wait(&empty[s], (unsigned)(((it / PT_STAGES) - 1) & 1), abort_flag, err);
+          if (ok) {
+            const int tile_start = start + it * PT_TILE;
+            mbar_expect_tx(&full[s], (unsigned)PT_STAGE_BYTES);
+            char* kt = smem + s * PT_STAGE_BYTES;
+            if (box_keys == PT_TILE) {
+              // the tile lies in one page: one copy of K, one of V (any run that is wanted names the page)
+              const int page = pg[0] != PAGE_NONE ? pg[0] : (pg[1] != PAGE_NONE ? pg[1] : (pg[2] != PAGE_NONE ? pg[2] : pg[3]));
+              const bool page_ok = page >= 0 && page < num_pages;
+              if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
+              const int row = page_ok ? (page * kvh + kh) * block_size + tile_start % block_size : 0;
+              tma_load_3d(kt, &tmK, 0, row, 0, &full[s]);
+              tma_load_3d(kt + PT_TILE_BYTES, &tmV, 0, row, 0, &full[s]);
+            } else {
 #pragma unroll
-            for (int c = 0; c < PT_SLICES; ++c) {
-              tma_load_3d(kt + c * PT_TILE * 128 + run * RUN_KEYS * 128, &tmK, 0, row, c, &full[s]);
-              tma_load_3d(kt + PT_TILE_BYTES + c * PT_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, row, c, &full[s]);
+              for (int run = 0; run < 4; ++run) {
+                const bool page_ok = pg[run] >= 0 && pg[run] < num_pages;
+                if (!page_ok && pg[run] != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
+                // a run nobody will read is filled from row 0 of the plane: finite values that the mask zeroes
+                const int key0 = tile_start + run * RUN_KEYS;
+                const int row = page_ok ? (pg[run] * kvh + kh) * block_size + key0 % block_size : 0;
+                // a 16-row box writes its slices 16 rows apart, the tile keeps them PT_TILE rows apart: a copy per slice
+#pragma unroll
+                for (int c = 0; c < PT_SLICES; ++c) {
+                  tma_load_3d(kt + c * PT_TILE * 128 + run * RUN_KEYS * 128, &tmK, 0, row, c, &full[s]);
+                  tma_load_3d(kt + PT_TILE_BYTES + c * PT_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, row, c, &full[s]);
+                }
+              }
             }
           }
         }
-        if (it + 1 < n_tiles) tile_pages<PT_TILE>(pages, table, block_size, tile_start + PT_TILE, key_lo, key_end);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
       }
-      const int first = it > PT_STAGES ? it - PT_STAGES : 0;     // copies in flight must land before the block exits
-      for (int j = first; j < it; ++j) {
-        bool done = false;
-        for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % PT_STAGES], (unsigned)((j / PT_STAGES) & 1));
-        if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+      if (lane == 0) {
+        const int first = it > PT_STAGES ? it - PT_STAGES : 0;     // copies in flight must land before the block exits
+        for (int j = first; j < it; ++j) {
+          bool done = false;
+          for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % PT_STAGES], (unsigned)((j / PT_STAGES) & 1));
+          if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+        }
       }
     }
     return;

@@ -252,8 +252,37 @@ def gemm_tc5_supported(x, w) -> bool:
             and (w.stride(0) * 2) % 16 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc5(x, w, out, epilogue: int, err) -> None:
-    """out = x @ w^T on the tcgen05 tensor cores for at most 128 rows of x; epilogues as gemm_skinny."""
+_tc5_scratch = {}
+
+
+def _tc5_buffers(device, floats: int, counters: int):
+    """Scratch of the split-K product: partial tiles (grown on demand) and counters (zero; the kernel keeps them so)."""
+    part, cnt = _tc5_scratch.get(device, (None, None))
+    if part is None or part.numel() < floats:
+        part = torch.empty(max(floats, 1), dtype=torch.float32, device=device)
+    if cnt is None or cnt.numel() < counters:
+        cnt = torch.zeros(max(counters, 1), dtype=torch.int32, device=device)
+    _tc5_scratch[device] = (part, cnt)
+    return part, cnt
+
+
+def gemm_tc5_scratch(x, w):
+    """(ksplit, floats of partial tiles, counters) the tcgen05 product wants for x @ w^T."""
+    L = lib()
+    L.vob_gemm_tc5_scratch_floats.restype = ctypes.c_long
+    L.vob_gemm_tc5_counters.restype = ctypes.c_long
+    N, K = w.shape
+    ksplit = int(L.vob_gemm_tc5_ksplit(ctypes.c_long(N), ctypes.c_long(K)))
+    if ksplit <= 1:
+        return 1, 0, 0
+    return (ksplit, int(L.vob_gemm_tc5_scratch_floats(x.shape[0], ctypes.c_long(N), ksplit)),
+            int(L.vob_gemm_tc5_counters(ctypes.c_long(N))))
+
+
+def gemm_tc5(x, w, out, epilogue: int, err, ksplit: Optional[int] = None, scratch=None) -> None:
+    """out = x @ w^T on the tcgen05 tensor cores for at most 128 rows of x; epilogues as gemm_skinny.  The product
+    is split along K where that fills the GPU better (`ksplit` None: chosen by the library); `scratch` is a pair
+    (float partials, zeroed int counters) for a caller that keeps buffers of its own (CUDA graphs)."""
     _cuda(x, w, out)
     if not gemm_tc5_supported(x, w):
         raise KernelError("gemm_tc5: this product is not supported (bfloat16, at most 128 rows, K a multiple of 8, "
@@ -263,10 +292,21 @@ def gemm_tc5(x, w, out, epilogue: int, err) -> None:
     assert w.shape[1] == K and out.stride(1) == 1 and out.shape[0] == M
     assert out.shape[1] == (N // 2 if epilogue == EPI_SWIGLU else N)
     assert out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16)
+    L = lib()
+    L.vob_gemm_tc5_scratch_floats.restype = ctypes.c_long
+    L.vob_gemm_tc5_counters.restype = ctypes.c_long
+    if ksplit is None:
+        ksplit = int(L.vob_gemm_tc5_ksplit(ctypes.c_long(N), ctypes.c_long(K)))
+    part = cnt = None
+    if ksplit > 1:
+        floats = int(L.vob_gemm_tc5_scratch_floats(M, ctypes.c_long(N), ksplit))
+        counters = int(L.vob_gemm_tc5_counters(ctypes.c_long(N)))
+        part, cnt = scratch if scratch is not None else _tc5_buffers(x.device, floats, counters)
+        assert part.numel() >= floats and cnt.numel() >= counters
     map_w = tensor_map_2d(w, 128)
-    map_x = tensor_map_2d(x, int(lib().vob_gemm_tc5_token_box(M)))
-    _check(lib().vob_gemm_tc5(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, _p(err), _stream()),
-           "gemm_tc5")
+    map_x = tensor_map_2d(x, int(L.vob_gemm_tc5_token_box(M)))
+    _check(L.vob_gemm_tc5(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, ksplit, _p(part), _p(cnt),
+                          _p(err), _stream()), "gemm_tc5")
 
 
 def gemm_skinny_supported(x, w) -> bool:

@@ -16,7 +16,7 @@ import torch
 
 from .. import kernels
 from ..parts.base import CachePlane, CacheSpec, StateSpec, build_part
-from ..parts.linear import linear
+from ..parts.linear import linear, tc5_product
 from ..weights.loader import TensorSpec
 from .plan import ModelPlan
 
@@ -114,6 +114,8 @@ class CausalLM:
         out = ctx.ws.get_rows("logits_f32", R, V, torch.float32)
         if kernels.gemm_skinny_supported(normed, self.lm_head):
             kernels.gemm_skinny(normed, self.lm_head, out, kernels.EPI_F32, ctx.err)   # rounds to bfloat16, stores float
+        elif tc5_product(normed, self.lm_head, out, kernels.EPI_F32, ctx):
+            pass
         else:
             out.copy_(linear(normed, self.lm_head, ctx.ws.get_rows("logits", R, V, self.dtype), ctx))
         return out

@@ -91,12 +91,13 @@ class Workspace:
             self._buffers[key] = buf
         return buf[:rows]
 
-    def get_flat(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
-        """Scratch memory of a kernel: a flat buffer that grows on demand."""
+    def get_flat(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """Scratch memory of a kernel: a flat buffer that grows on demand (`zero`: filled with zeros when made)."""
         key = (name, 0, dtype)
         buf = self._buffers.get(key)
         if buf is None or buf.numel() < numel:
-            buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            make = torch.zeros if zero else torch.empty
+            buf = make(max(numel, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf[:numel]
 

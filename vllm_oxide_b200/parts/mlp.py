@@ -9,7 +9,7 @@ import torch
 from .. import kernels
 from ..weights.loader import TensorSpec
 from .base import FeedForward, register_part
-from .linear import linear
+from .linear import linear, tc5_product
 
 
 class SwiGLU(FeedForward):
@@ -46,6 +46,8 @@ class SwiGLU(FeedForward):
         if self.interleaved and kernels.gemm_skinny_supported(x, self.wgu):
             # decode-sized steps: the activation is the epilogue of the gate|up product
             kernels.gemm_skinny(x, self.wgu, act, kernels.EPI_SWIGLU, ctx.err)
+        elif self.interleaved and tc5_product(x, self.wgu, act, kernels.EPI_SWIGLU, ctx):
+            pass
         else:
             gu = linear(x, self.wgu, ctx.ws.get("gate_up", T, 2 * self.I, x.dtype), ctx)
             kernels.silu_mul(gu, act, T, self.interleaved)

@@ -320,12 +320,18 @@ def test_attention_decode_reads_the_right_far_key(key_pos, window, expect_hit):
     assert (got.mean() > 4.9) == expect_hit
 
 
-def prefill_attention(q, out, kc, vc, bt, cu_q, ctx, T, nh, kvh, hd, window, err, use_tma=True, **_):
+# the kernels behind attention_prefill: tcgen05 with one or two query tiles a block (head sizes 64 and 128),
+# mma.sync with TMA copies (head sizes that are a multiple of 64), mma.sync with cp.async (every head size)
+PREFILL_KERNELS = {"tc5x2": dict(query_tiles=2), "tc5x1": dict(query_tiles=1), "tma": dict(use_tc5=False),
+                   "cp.async": dict(use_tc5=False, use_tma=False)}
+
+
+def prefill_attention(q, out, kc, vc, bt, cu_q, ctx, T, nh, kvh, hd, window, err, kernel="tc5x2", **_):
     from vllm_oxide_b200 import kernels
     B = ctx.shape[0]
     max_q = int((cu_q[1:] - cu_q[:-1]).max())
     kernels.attention_prefill(q.reshape(T, nh * hd), nh * hd, out, kc, vc, bt, cu_q, ctx, B, max_q, nh, kvh, hd, window,
-                              1.0 / math.sqrt(hd), err, use_tma=use_tma)
+                              1.0 / math.sqrt(hd), err, **PREFILL_KERNELS[kernel])
 
 
 PREFILL_CASES = [  # nh, kvh, hd, block_size, window, q_lens, ctx_lens
@@ -340,25 +346,30 @@ PREFILL_CASES = [  # nh, kvh, hd, block_size, window, q_lens, ctx_lens
     (8, 8, 64, 48, 30, [200, 31, 2], [200, 31, 48]),
     (12, 3, 192, 32, 0, [133, 65], [333, 65]),
     (16, 4, 128, 128, 70, [300, 129], [700, 129]),
+    (6, 2, 128, 64, 0, [700], [700]),            # three heads a group: query tiles that end inside a token
+    (14, 2, 64, 32, 0, [2, 257, 40], [2, 300, 1000]),
 ]
 
 
-@pytest.mark.parametrize("use_tma", [True, False])
+@pytest.mark.parametrize("kernel", list(PREFILL_KERNELS))
 @pytest.mark.parametrize("case", PREFILL_CASES)
-def test_attention_prefill(case, use_tma):
-    """Head sizes that are a multiple of 64 have two kernels (TMA and cp.async copies); both are checked."""
+def test_attention_prefill(case, kernel):
+    """Every kernel that a head size has is checked (a head size without one falls through to the next)."""
     import functools
     nh, kvh, hd, bs, window, q_lens, ctx_lens = case
-    got, want = run_attention(functools.partial(prefill_attention, use_tma=use_tma), torch.bfloat16, nh, kvh, hd, bs,
+    got, want = run_attention(functools.partial(prefill_attention, kernel=kernel), torch.bfloat16, nh, kvh, hd, bs,
                               window, q_lens, ctx_lens)
     assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
 
 
 @pytest.mark.parametrize("key_pos,window,expect_hit", [(3, 0, True), (63, 0, True), (64, 0, True), (791, 0, True),
                                                        (792 - 63, 64, True), (792 - 64, 64, False)])
-def test_attention_prefill_reads_the_right_far_key(key_pos, window, expect_hit):
+@pytest.mark.parametrize("kernel", ["tc5x2", "tc5x1", "tma"])
+def test_attention_prefill_reads_the_right_far_key(key_pos, window, expect_hit, kernel):
     """Eight queries at positions 792..799: the first one decides whether the key is inside its window."""
-    got, want = run_attention(prefill_attention, torch.bfloat16, 8, 2, 64, 16, window, [8], [800], craft=craft_spike(key_pos))
+    import functools
+    got, want = run_attention(functools.partial(prefill_attention, kernel=kernel), torch.bfloat16, 8, 2, 64, 16, window, [8],
+                              [800], craft=craft_spike(key_pos))
     assert torch.allclose(got, want, atol=3e-2)
     assert (got[0].mean() > 4.9) == expect_hit
 

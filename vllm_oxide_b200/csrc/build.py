@@ -89,7 +89,7 @@ def host_sources():
 
 
 # Sources compiled once per head size (-DVOB_HD=<n>) into a library of their own.
-PER_HEAD_DIM = ("attention_decode.cu", "attention_prefill.cu")
+PER_HEAD_DIM = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc5.cu")
 DEFAULT_HEAD_DIMS = (64, 128)
 
 

@@ -1,0 +1,423 @@
+// Causal attention of prompt portions over the paged cache on the fifth-generation tensor cores, for head sizes
+// 64 and 128: S = Q K^T and O = P V are tcgen05.mma products with S and O in tensor memory.
+//
+// A block takes NQ tiles of 128 query rows (a row is a (token, head of the group) pair, so the heads that share a
+// key/value head share every key and value brought in) and walks the keys in steps of 64:
+//   warps 0 .. 4NQ-1   softmax: warp w of a tile owns rows 32(w%4) .. +31 of it, a thread owns ONE row: it reads the
+//                      row's 64 scores from tensor memory (tcgen05.ld), masks, takes the maximum and the sum without
+//                      any exchange between threads, writes P in bfloat16 to shared memory (128-byte swizzled, the A
+//                      operand of the second product), and at the end divides the row of O by its sum and stores it;
+//   warp 4NQ           producer: looks the pages up a chunk ahead and brings K and V tiles in by TMA into a ring of
+//                      stages (the K tile is the K-major B operand of the first product as it lands, the V tile the
+//                      MN-major B operand of the second one: no transposition anywhere);
+//   warp 4NQ+1         allocates tensor memory and issues the products from one thread: the scores of step j+1 go
+//                      into a second S buffer while the softmax of step j runs; tcgen05.commit tells the softmax warps
+//                      that S is complete, that O has been updated, and the producer that a stage is free.
+// O stays in tensor memory over all steps.  The running maximum that the exponentials refer to is moved only when a
+// row's new maximum exceeds it by more than 8 (in base-2 units: P stays below 256, exact enough in bfloat16 since
+// its error is relative); only then the row's O is read, scaled and written back, which is rare after the first
+// steps.  Sums, maxima and the scaling are in float.  Every wait on an mbarrier is bounded; a block that gives up
+// sets an error bit, stops issuing work, waits for what is in flight, and frees its tensor memory.
+#include "attention_mma.cuh"
+#include "tcgen05.cuh"
+
+namespace vob {
+
+#if VOB_HD == 64 || VOB_HD == 128
+
+constexpr int F5_ROWS = 128;                               // rows of a query tile (the MMA's M)
+constexpr int F5_TILE = 64;                                // keys per step
+constexpr int F5_SLICES = HD / 64;                         // 64-column slices of a head
+constexpr int F5_Q_BYTES = F5_SLICES * F5_ROWS * 128;      // a query tile: [slice][128 rows][128 bytes]
+constexpr int F5_P_BYTES = F5_ROWS * 128;                  // P of one step: [128 rows][64 keys]
+constexpr int F5_KV_BYTES = F5_SLICES * F5_TILE * 128;     // one of K or V: [slice][64 keys][128 bytes]
+constexpr int F5_STAGE_BYTES = 2 * F5_KV_BYTES;
+constexpr float F5_MAX_SLACK = 8.f;                        // how far a row's maximum may run ahead of its reference
+
+template <int NQ> struct F5 {
+  static constexpr int THREADS = (4 * NQ + 2) * 32;
+  static constexpr int STAGES = NQ == 1 ? 4 : 3;
+  static constexpr int TILE_COLS = 2 * F5_TILE + HD;       // tensor-memory columns of a query tile: S, S, O
+  static constexpr int TMEM_COLS = NQ * TILE_COLS <= 256 ? 256 : 512;
+  static constexpr int DATA_BYTES = NQ * (F5_Q_BYTES + F5_P_BYTES) + STAGES * F5_STAGE_BYTES;
+  static constexpr int NUM_BARRIERS = 2 * STAGES + 4 * NQ + 1;
+  static constexpr int SMEM_BYTES = 1024 + DATA_BYTES + NUM_BARRIERS * 8 + 16;
+};
+
+template <int NQ>
+__global__ void __launch_bounds__(F5<NQ>::THREADS, 1)
+attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                             const __nv_bfloat16* __restrict__ q, long q_stride, __nv_bfloat16* __restrict__ out,
+                             const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
+                             const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
+                             long num_pages, int box_keys, int* err) {
+  using C = F5<NQ>;
+  constexpr int ST = C::STAGES;
+  extern __shared__ __align__(1024) char smem_raw[];
+  char* smem = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  char* q_s = smem;                                         // [NQ] query tiles
+  char* p_s = q_s + NQ * F5_Q_BYTES;                        // [NQ] P tiles
+  char* kv_s = p_s + NQ * F5_P_BYTES;                       // [ST] stages: K tile, V tile
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + C::DATA_BYTES);
+  uint64_t* kv_empty = kv_full + ST;
+  uint64_t* s_full = kv_empty + ST;                         // [NQ][2] scores of a step are complete
+  uint64_t* p_full = s_full + 2 * NQ;                       // [NQ] P is written (and S read, O rescaled)
+  uint64_t* o_done = p_full + NQ;                           // [NQ] O holds the step's contribution
+  uint64_t* drained = o_done + NQ;                          // every product issued has completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  pdl_launch_dependents();
+  // blockIdx.x = row block * kv heads + kv head: the blocks of all heads that see the most keys start first
+  const int kh = blockIdx.x % kvh, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = cu_q[b];
+  const int n = cu_q[b + 1] - t0;
+  const int G = nh / kvh;
+  const int total_rows = n * G;
+  // later row blocks see more keys: they go first, so that the short ones fill the end of the grid
+  const int row0 = (int)(gridDim.x / kvh - 1 - blockIdx.x / kvh) * NQ * F5_ROWS;
+  if (n <= 1 || row0 >= total_rows) { pdl_wait(); return; }       // a decoding request, or nothing left (uniform)
+  const int ctx = context_lens[b];
+  const int first_pos = ctx - n;
+  const int* table = block_tables + (size_t)b * table_stride;
+  const int last_row = min(row0 + NQ * F5_ROWS, total_rows) - 1;
+  const int blk_pos_lo = first_pos + row0 / G, blk_pos_hi = first_pos + last_row / G;
+  const int key_lo = window > 0 ? max(0, blk_pos_lo - window + 1) : 0;
+  const int key_end = blk_pos_hi + 1;
+  const int start = key_lo / F5_TILE * F5_TILE;
+  const int n_tiles = (key_end - start + F5_TILE - 1) / F5_TILE;
+  // the steps that each query tile takes part in: [jlo, jhi)
+  int jlo[NQ], jhi[NQ];
+#pragma unroll
+  for (int qt = 0; qt < NQ; ++qt) {
+    const int r_first = row0 + qt * F5_ROWS;
+    if (r_first >= total_rows) { jlo[qt] = jhi[qt] = 0; continue; }
+    const int r_last = min(r_first + F5_ROWS, total_rows) - 1;
+    const int pos_lo = first_pos + r_first / G, pos_hi = first_pos + r_last / G;
+    const int klo = window > 0 ? max(0, pos_lo - window + 1) : 0;
+    jlo[qt] = (klo - start) / F5_TILE;
+    jhi[qt] = (pos_hi - start) / F5_TILE + 1;
+  }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int i = 0; i < 2 * NQ; ++i) mbar_init(&s_full[i], 1);
+    for (int i = 0; i < NQ; ++i) { mbar_init(&p_full[i], 4); mbar_init(&o_done[i], 1); }
+    mbar_init(drained, 1);
+    *abort_flag = 0;
+    tma_prefetch_map(&tmK);
+    tma_prefetch_map(&tmV);
+  }
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  if (warp == 4 * NQ + 1) t5_alloc(tmem_slot, C::TMEM_COLS);
+  pdl_wait();                                   // the kernels before this one wrote q and this portion's keys and values
+  if (warp < 4 * NQ) {
+    // the query tile of this warp group into shared memory, rows of 128 bytes per slice, 128-byte swizzled
+    const int qt = warp >> 2, tid = threadIdx.x & 127;
+    char* dst = q_s + qt * F5_Q_BYTES;
+    constexpr int CHUNKS = HD / 8;
+    for (int idx = tid; idx < F5_ROWS * CHUNKS; idx += 128) {
+      const int r = idx / CHUNKS, chunk = idx % CHUNKS;
+      const int row = row0 + qt * F5_ROWS + r;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row < total_rows)
+        v = *reinterpret_cast<const uint4*>(q + (size_t)(t0 + row / G) * q_stride + (size_t)(kh * G + row % G) * HD + chunk * 8);
+      *reinterpret_cast<uint4*>(dst + (chunk >> 3) * (F5_ROWS * 128) + swizzled_offset(r, chunk & 7)) = v;
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  t5_fence_before();
+  __syncthreads();
+  t5_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4 * NQ) {
+    // ------------------------------------------------ producer: lane 0 issues, all lanes look pages up
+    WarpPages wp;
+    bool ok = true;
+    int it = 0;
+    for (; it < n_tiles; ++it) {
+      const int s = it % ST;
+      wp.advance(table, block_size, start, it, lane, key_lo, key_end);
+      int pg[4];
+#pragma unroll
+      for (int run = 0; run < 4; ++run) pg[run] = wp.page(it, run);
+      if (lane == 0) {
+        if (it >= ST) ok = mbar_wait(&kv_empty[s], (unsigned)(((it / ST) - 1) & 1), abort_flag, err);
+        if (ok) {
+          const int tile_start = start + it * F5_TILE;
+          mbar_expect_tx(&kv_full[s], (unsigned)F5_STAGE_BYTES);
+          char* kt = kv_s + s * F5_STAGE_BYTES;
+          if (box_keys == F5_TILE) {
+            // the tile lies in one page: one copy of K, one of V (any run that is wanted names the page)
+            const int page = pg[0] != PAGE_NONE ? pg[0] : (pg[1] != PAGE_NONE ? pg[1] : (pg[2] != PAGE_NONE ? pg[2] : pg[3]));
+            const bool page_ok = page >= 0 && page < num_pages;
+            if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
+            const int row = page_ok ? (page * kvh + kh) * block_size + tile_start % block_size : 0;
+            tma_load_3d(kt, &tmK, 0, row, 0, &kv_full[s]);
+            tma_load_3d(kt + F5_KV_BYTES, &tmV, 0, row, 0, &kv_full[s]);
+          } else {
+#pragma unroll
+            for (int run = 0; run < 4; ++run) {
+              const bool page_ok = pg[run] >= 0 && pg[run] < num_pages;
+              if (!page_ok && pg[run] != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
+              // a run nobody will read is filled from row 0 of the plane: finite values that the mask zeroes
+              const int key0 = tile_start + run * RUN_KEYS;
+              const int row = page_ok ? (pg[run] * kvh + kh) * block_size + key0 % block_size : 0;
+#pragma unroll
+              for (int c = 0; c < F5_SLICES; ++c) {
+                tma_load_3d(kt + c * F5_TILE * 128 + run * RUN_KEYS * 128, &tmK, 0, row, c, &kv_full[s]);
+                tma_load_3d(kt + F5_KV_BYTES + c * F5_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, row, c, &kv_full[s]);
+              }
+            }
+          }
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+    }
+    if (lane == 0) {
+      const int first = it > ST ? it - ST : 0;     // copies in flight must land before the block exits
+      for (int j = first; j < it; ++j) {
+        bool done = false;
+        for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&kv_full[j % ST], (unsigned)((j / ST) & 1));
+        if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+      }
+    }
+  } else if (warp == 4 * NQ + 1) {
+    // ------------------------------------------------ the products (one thread)
+    if (lane == 0) {
+      const uint32_t idesc_qk = t5_instr_desc(F5_ROWS, F5_TILE);
+      const uint32_t idesc_pv = t5_instr_desc_b_mn(F5_ROWS, HD);
+      bool ok = true;
+      // S[qt][buffer] = Q[qt] K_j^T for every query tile that takes part in step j
+      auto scores = [&](int j) {
+        const char* kt = kv_s + (j % ST) * F5_STAGE_BYTES;
+#pragma unroll
+        for (int qt = 0; qt < NQ; ++qt) {
+          if (j < jlo[qt] || j >= jhi[qt]) continue;
+          const int i = j - jlo[qt];
+          const uint32_t d = tmem_base + qt * C::TILE_COLS + (i & 1) * F5_TILE;
+#pragma unroll
+          for (int ks = 0; ks < HD / 16; ++ks)
+            t5_mma(d, t5_smem_desc(q_s + qt * F5_Q_BYTES + (ks >> 2) * (F5_ROWS * 128) + (ks & 3) * 32),
+                   t5_smem_desc(kt + (ks >> 2) * (F5_TILE * 128) + (ks & 3) * 32), idesc_qk, ks > 0);
+          t5_commit(&s_full[qt * 2 + (i & 1)]);
+        }
+      };
+      ok = mbar_wait(&kv_full[0], 0u, abort_flag, err);
+      if (ok) { t5_fence_after(); scores(0); }
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) {
+          ok = mbar_wait(&kv_full[(j + 1) % ST], (unsigned)(((j + 1) / ST) & 1), abort_flag, err);
+          if (!ok) break;
+          t5_fence_after();
+          scores(j + 1);
+        }
+        const char* vt = kv_s + (j % ST) * F5_STAGE_BYTES + F5_KV_BYTES;
+#pragma unroll
+        for (int qt = 0; qt < NQ; ++qt) {
+          if (j < jlo[qt] || j >= jhi[qt]) continue;
+          const int i = j - jlo[qt];
+          ok = mbar_wait(&p_full[qt], (unsigned)(i & 1), abort_flag, err);
+          if (!ok) break;
+          t5_fence_after();
+          const uint32_t d = tmem_base + qt * C::TILE_COLS + 2 * F5_TILE;
+#pragma unroll
+          for (int ks = 0; ks < F5_TILE / 16; ++ks)
+            t5_mma(d, t5_smem_desc(p_s + qt * F5_P_BYTES + ks * 32),
+                   t5_smem_desc_mn(vt + ks * 16 * 128, F5_TILE * 128, 1024), idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
+          t5_commit(&o_done[qt]);
+        }
+        if (!ok) break;
+        t5_commit(&kv_empty[j % ST]);
+      }
+      // nothing may still read shared or tensor memory when the block ends
+      t5_commit(drained);
+      bool done = false;
+      for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(drained, 0u);
+      if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+    }
+  } else {
+    // ------------------------------------------------ softmax: a thread owns a row
+    const int qt = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;                   // row of the tile = lane of tensor memory
+    const int row = row0 + qt * F5_ROWS + r;
+    const bool valid = row < total_rows;
+    const int tok = valid ? row / G : 0, head = kh * G + (valid ? row % G : 0);
+    const int rpos = first_pos + tok;
+    const int r_first = row0 + qt * F5_ROWS, r_last = min(r_first + F5_ROWS, total_rows) - 1;
+    const int t_pos_lo = first_pos + r_first / G, t_pos_hi = first_pos + r_last / G;
+    const bool all_rows = r_first + F5_ROWS <= total_rows;
+    const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + qt * C::TILE_COLS;
+    char* p_row = p_s + qt * F5_P_BYTES;
+    const float sc = scale * LOG2E;
+    float m_ref = -INFINITY, l = 0.f;
+    const int my_lo = jlo[qt], my_hi = jhi[qt];
+    bool ok = true;
+    for (int j = my_lo; j < my_hi; ++j) {
+      const int i = j - my_lo;
+      ok = mbar_wait(&s_full[qt * 2 + (i & 1)], (unsigned)((i >> 1) & 1), abort_flag, err);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      t5_fence_after();
+      uint32_t raw[2][32];
+      t5_ld32_issue(lane_base + (i & 1) * F5_TILE, raw[0]);
+      t5_ld32_issue(lane_base + (i & 1) * F5_TILE + 32, raw[1]);
+      t5_wait_ld();
+      float s[64];
+      const int k0 = start + j * F5_TILE;
+      // mask only where the step touches the diagonal, the window's edge or missing rows
+      const bool need_mask = !all_rows || k0 + F5_TILE - 1 > t_pos_lo || (window > 0 && k0 < t_pos_hi - window + 1);
+      float mx = -INFINITY;                                // of the raw scores: the scale is positive
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int key = k0 + c;
+          bool okk = valid && key <= rpos;
+          if (window > 0) okk = okk && key > rpos - window;
+          s[c] = okk ? __uint_as_float(raw[c >> 5][c & 31]) : -INFINITY;
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) s[c] = __uint_as_float(raw[c >> 5][c & 31]);
+      }
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) mx = fmaxf(mx, fmaxf(s[c], s[c + 1]));
+      mx *= sc;
+      // the reference maximum moves only when the row's maximum has run ahead of it
+      const bool grow = mx > m_ref + F5_MAX_SLACK;
+      float factor = 1.f;
+      if (grow) {
+        factor = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - mx);
+        m_ref = mx;
+        l *= factor;
+      }
+      const float neg_mu = m_ref == -INFINITY ? 0.f : -m_ref;     // a row that has seen no key yet: a finite stand-in
+      float sum0 = 0.f, sum1 = 0.f;
+      uint32_t packed[32];
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) {
+        const float p0 = fast_exp2(fmaf(s[c], sc, neg_mu)), p1 = fast_exp2(fmaf(s[c + 1], sc, neg_mu));
+        sum0 += p0;
+        sum1 += p1;
+        packed[c >> 1] = pack_bf16(p0, p1);
+      }
+      const float sum = sum0 + sum1;
+      l += sum;
+      if (i > 0) {
+        // the product of the step before has left P and updated O
+        ok = mbar_wait(&o_done[qt], (unsigned)((i - 1) & 1), abort_flag, err);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        t5_fence_after();
+        if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            uint32_t o[32];
+            t5_ld32_issue(lane_base + 2 * F5_TILE + c0, o);
+            t5_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+            t5_st32(lane_base + 2 * F5_TILE + c0, o);
+          }
+          t5_wait_st();
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(p_row + swizzled_offset(r, c)) =
+            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      t5_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[qt]);
+    }
+    if (ok && my_hi > my_lo) {
+      ok = mbar_wait(&o_done[qt], (unsigned)((my_hi - my_lo - 1) & 1), abort_flag, err);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        t5_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* orow = out + (size_t)(t0 + tok) * nh * HD + (size_t)head * HD;
+#pragma unroll
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t o[32];
+          t5_ld32_issue(lane_base + 2 * F5_TILE + c0, o);
+          t5_wait_ld();
+          if (valid) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+              v.y = pack_bf16(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+              v.z = pack_bf16(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+              v.w = pack_bf16(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c0 + c) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+  t5_fence_before();
+  __syncthreads();
+  if (warp == 4 * NQ + 1) t5_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+#endif  // VOB_HD == 64 || VOB_HD == 128
+
+}  // namespace vob
+
+using namespace vob;
+
+VOB_API int vob_attention_prefill_has_tc5() {
+#if VOB_HD == 64 || VOB_HD == 128
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// As vob_attention_prefill_tma (same tensor maps: 64-column slices, boxes of vob_attention_decode_box_keys rows), for
+// head sizes 64 and 128.  `query_tiles` is 1 or 2: how many tiles of 128 query rows a block takes.
+VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
+                                      const int* block_tables, int table_stride, const int* cu_q, const int* context_lens,
+                                      int num_requests, int max_q, int nh, int kvh, int block_size, int window, float scale,
+                                      long num_pages, int query_tiles, int* err, cudaStream_t stream) {
+#if VOB_HD == 64 || VOB_HD == 128
+  if (num_requests <= 0 || max_q <= 1) return 0;
+  if (!map_k || !map_v) return VOB_BAD_ARGUMENT;
+  if (kvh <= 0 || nh % kvh || block_size <= 0 || block_size % 16 || kvh > 65535 || num_requests > 65535 ||
+      (query_tiles != 1 && query_tiles != 2) || !(scale > 0.f))   // the kernel takes maxima before it scales
+    return VOB_UNSUPPORTED;
+  const long rows = (long)max_q * (nh / kvh);
+  const int box_keys = block_size % F5_TILE == 0 ? F5_TILE : RUN_KEYS;
+  static bool configured[2] = {false, false};
+  if (query_tiles == 1) {
+    if (!configured[0]) {
+      cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, F5<1>::SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      configured[0] = true;
+    }
+    dim3 grid((unsigned)((rows + F5_ROWS - 1) / F5_ROWS) * kvh, 1, num_requests);
+    return launch_kernel(attention_prefill_tc5_kernel<1>, grid, F5<1>::THREADS, F5<1>::SMEM_BYTES, stream,
+                         *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride,
+                         (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size, window,
+                         scale, num_pages, box_keys, err);
+  }
+  if (!configured[1]) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, F5<2>::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured[1] = true;
+  }
+  dim3 grid((unsigned)((rows + 2 * F5_ROWS - 1) / (2 * F5_ROWS)) * kvh, 1, num_requests);
+  return launch_kernel(attention_prefill_tc5_kernel<2>, grid, F5<2>::THREADS, F5<2>::SMEM_BYTES, stream,
+                       *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride,
+                       (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size, window,
+                       scale, num_pages, box_keys, err);
+#else
+  return VOB_UNSUPPORTED;
+#endif
+}

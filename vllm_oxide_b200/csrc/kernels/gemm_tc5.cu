@@ -19,7 +19,7 @@
 // Epilogues as in the weight-streaming kernel for smaller steps: bfloat16, float logits, SiLU(gate)*up over
 // interleaved gate/up rows.  Every wait on an mbarrier is bounded; on a timeout the block sets an error bit,
 // stops issuing work, and still frees its TMEM before it returns.
-#include "tensor_map.cuh"
+#include "tcgen05.cuh"
 
 namespace vob {
 
@@ -30,41 +30,6 @@ constexpr int T5_EPI_WARPS = 4;
 
 enum { T5_EPI_BF16 = 0, T5_EPI_F32 = 1, T5_EPI_SWIGLU = 2 };
 
-// Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzled layout (rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart): start address, leading offset (unused here), stride between row groups,
-// descriptor version 1, layout type 2 (128-byte swizzle).
-__device__ __forceinline__ uint64_t t5_smem_desc(const void* p) {
-  const uint64_t addr = (uint64_t)((smem_addr(p) & 0x3FFFF) >> 4);
-  return addr | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// Instruction descriptor of kind::f16: float accumulator, bfloat16 A and B, both K-major, N and M of the tile.
-__device__ __forceinline__ uint32_t t5_instr_desc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void t5_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
-__device__ __forceinline__ void t5_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
-}
-__device__ __forceinline__ void t5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void t5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-// 32 lanes x 32 columns of 32-bit: thread i of the warp gets its lane's 32 consecutive columns.
-__device__ __forceinline__ void t5_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                 "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-                 "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-                 "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-               : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 __device__ __forceinline__ float t5_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 template <int NT> struct T5Stages { static constexpr int N = (192 * 1024) / ((T5_ROWS + NT) * 128); };

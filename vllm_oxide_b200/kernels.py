@@ -173,8 +173,10 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, conte
 
 
 def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, max_q, nh, kvh,
-                      hd, window: int, scale: float, err, use_tma: bool = True) -> None:
-    """Requests that bring more than one token; the others are skipped."""
+                      hd, window: int, scale: float, err, use_tma: bool = True, use_tc5: bool = True,
+                      query_tiles: int = 2) -> None:
+    """Requests that bring more than one token; the others are skipped.  Head sizes 64 and 128 run on the tcgen05
+    tensor cores (`use_tc5`), other multiples of 64 on mma.sync with TMA copies (`use_tma`), the rest with cp.async."""
     _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens)
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
     L = attention_lib(hd)
@@ -182,6 +184,12 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
         bs = kcache.shape[2]
         keys, slices = L.vob_attention_decode_box_keys(bs), L.vob_attention_decode_box_slices(bs)
         map_k, map_v = tensor_map(kcache.view(-1, hd), keys, slices), tensor_map(vcache.view(-1, hd), keys, slices)
+        if use_tc5 and L.vob_attention_prefill_has_tc5() and q_stride % 8 == 0:
+            _check(L.vob_attention_prefill_tc5(
+                map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(block_tables), block_tables.shape[-1], _p(cu_q),
+                _p(context_lens), num_requests, max_q, nh, kvh, bs, window, ctypes.c_float(scale),
+                ctypes.c_long(kcache.shape[0]), query_tiles, _p(err), _stream()), "attention_prefill_tc5")
+            return
         _check(L.vob_attention_prefill_tma(
             map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
             block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, max_q, nh, kvh, bs, window,

@@ -80,10 +80,10 @@ template <> __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16*
 }
 
 // VEC: 16-byte accesses (the row width must be a multiple of 16 bytes); otherwise one element at a time.
-// REG: the row's sums stay in registers between the two passes (rows of at most 4 * NT 16-byte pieces); else they
-// are parked in shared memory.  The order of additions is the same in all three and depends on H only.
-template <typename T, int NT, bool VEC, bool REG>
-__global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const float* __restrict__ w, T* __restrict__ y,
+// REG > 0: the row's sums stay in registers between the two passes (rows of at most REG * NT 16-byte pieces); else
+// they are parked in shared memory.  The order of additions is the same in all three and depends on H only.
+template <typename T, int NT, bool VEC, int REG>
+__global__ void __launch_bounds__(NT) add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const float* __restrict__ w, T* __restrict__ y,
                                    const int* __restrict__ rows, int H, int num_src_rows, float eps, int has_residual,
                                    int* err) {
   extern __shared__ float srow[];  // H floats (unused with REG)
@@ -104,7 +104,7 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const f
   T* yr = y + (size_t)r * H;
   float ss = 0.f;
   if (VEC && REG) {
-    constexpr int N = Vec16<T>::N, IT = 4;
+    constexpr int N = Vec16<T>::N, IT = REG > 0 ? REG : 1;
     float v[IT][N];
 #pragma unroll
     for (int it = 0; it < IT; ++it) {
@@ -134,9 +134,11 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const f
     for (int it = 0; it < IT; ++it) {
       const int i = (threadIdx.x + it * NT) * N;
       if (i < H) {
-        float o[N];
+        float o[N], wv[N];
 #pragma unroll
-        for (int j = 0; j < N; ++j) o[j] = round_to<T>(v[it][j] / denom) * w[i + j];
+        for (int j = 0; j < N; j += 4) *reinterpret_cast<float4*>(wv + j) = *reinterpret_cast<const float4*>(w + i + j);
+#pragma unroll
+        for (int j = 0; j < N; ++j) o[j] = round_to<T>(v[it][j] / denom) * wv[j];
         store16<T>(yr + i, o);
       }
     }
@@ -205,7 +207,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
         load16<T>(gp, reinterpret_cast<float(&)[Vec16<T>::N]>(g));
         load16<T>(up, reinterpret_cast<float(&)[Vec16<T>::N]>(u));
 #pragma unroll
-        for (int j = 0; j < N; ++j) o[j] = round_to<T>(g[j] / (1.f + expf(-g[j]))) * u[j];
+        for (int j = 0; j < N; ++j) o[j] = round_to<T>(__fdividef(g[j], 1.f + __expf(-g[j]))) * u[j];   // 2 ulp of float: far below bfloat16's step
         store16<T>(out + gidx * N, reinterpret_cast<float(&)[Vec16<T>::N]>(o));
       } else {
 #pragma unroll
@@ -230,12 +232,15 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 }
 
 // ---------------------------------------------------------------- bias + head norm + rotation + cache write
-// One warp per (token, head) over the merged q|k|v row.  q heads are normalised and rotated in
+// A warp takes HPW consecutive heads of one token's merged q|k|v row.  q heads are normalised and rotated in
 // place; k heads are normalised, rotated and written to the key cache at the token's slot; v
 // heads are copied to the value cache.  cos_sin is [max_pos, hd] float: cos of hd/2 angles, then
 // sin.  A slot of -1 writes nothing.  The caches are [pages, kv_heads, block_size, hd]: slot s is row
 // s % block_size of page s / block_size, and the rows of one head within a page are contiguous.
-template <typename T>
+// Everything a head needs is a chain of dependent loads, so all loads of all the warp's heads are issued
+// before the first is used; with many tokens (prompt portions) a warp takes several heads and shares the
+// angles between them.  NV: 64-element steps a lane makes over half a head (hd <= 128 NV).
+template <typename T, int NV, int HPW>
 __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __restrict__ bias,
                                              const int* __restrict__ positions, const int* __restrict__ slots,
                                              const float* __restrict__ wq, const float* __restrict__ wk,
@@ -245,78 +250,206 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  const int head0 = (blockIdx.y * (blockDim.x >> 5) + warp) * HPW;
   const int total_heads = nh + 2 * kvh;
   const int pos = positions[t];
   const int slot = slots ? slots[t] : -1;
-  pdl_wait();
-  if (head >= total_heads) return;
-  const int width = total_heads * hd;
-  T* row = qkv + (size_t)t * width + (size_t)head * hd;
-  const T* brow = bias ? bias + (size_t)head * hd : nullptr;
-  const bool is_q = head < nh, is_k = !is_q && head < nh + kvh;
-  if (!is_q && (!write_kv || slot < 0)) return;
-  if (!is_q && slot >= num_slots) {
-    if (lane == 0) atomicOr(err, VOB_ERR_SLOT);
-    return;
-  }
-  if (!is_q && !is_k) {  // value head: bias, then copy
-    T* dst = vcache + (((size_t)(slot / block_size) * kvh + (head - nh - kvh)) * block_size + slot % block_size) * hd;
-    for (int i = 2 * lane; i < hd; i += 64) {
-      float2 v = load2<T>(row + i);
-      if (brow) { const float2 bv = load2<T>(brow + i); v.x = round_to<T>(v.x + bv.x); v.y = round_to<T>(v.y + bv.y); }
-      store2<T>(dst + i, v);
-    }
-    return;
-  }
-  if (pos < 0 || pos >= max_pos) {
-    if (lane == 0) atomicOr(err, VOB_ERR_POSITION);
-    return;
-  }
-  // a lane owns pairs (i, i + hd/2) for i = 2*lane, 2*lane+1 (+64, +128, ...): two neighbouring elements per access
   const int half = hd >> 1;
-  const float* w = is_q ? wq : wk;
-  constexpr int MAXV = 4;  // hd <= 512
-  float2 x1[MAXV], x2[MAXV];
-  float ss = 0.f;
+  const bool pos_ok = pos >= 0 && pos < max_pos;
+  // the angles of this token, shared by the warp's heads (they do not depend on the kernel before)
+  float2 c[NV], sn[NV];
 #pragma unroll
-  for (int j = 0; j < MAXV; ++j) {
+  for (int j = 0; j < NV; ++j) {
     const int i = 2 * lane + 64 * j;
-    if (i < half) {
-      float2 a = load2<T>(row + i), b = load2<T>(row + i + half);
-      if (brow) {
-        const float2 ba = load2<T>(brow + i), bb = load2<T>(brow + i + half);
-        a.x = round_to<T>(a.x + ba.x); a.y = round_to<T>(a.y + ba.y);
-        b.x = round_to<T>(b.x + bb.x); b.y = round_to<T>(b.y + bb.y);
-      }
-      x1[j] = a; x2[j] = b;
-      ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+    if (i < half && pos_ok) {
+      c[j] = *reinterpret_cast<const float2*>(cos_sin + (size_t)pos * hd + i);
+      sn[j] = *reinterpret_cast<const float2*>(cos_sin + (size_t)pos * hd + i + half);
     }
   }
-  if (w) {
-    ss = warp_sum(ss);
-    const float denom = sqrtf(ss / (float)hd + eps);
+  pdl_wait();
+  if (head0 >= total_heads) return;
+  const int width = total_heads * hd;
+  // a lane owns pairs (i, i + hd/2) for i = 2*lane, 2*lane+1 (+64, +128, ...): two neighbouring elements per access
+  float2 x1[HPW][NV], x2[HPW][NV], wa[HPW][NV], wb[HPW][NV];
 #pragma unroll
-    for (int j = 0; j < MAXV; ++j) {
+  for (int h = 0; h < HPW; ++h) {
+    const int head = head0 + h;
+    if (head >= total_heads) continue;
+    const T* row = qkv + (size_t)t * width + (size_t)head * hd;
+    const float* w = head < nh ? wq : (head < nh + kvh ? wk : nullptr);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
       const int i = 2 * lane + 64 * j;
       if (i < half) {
-        const float2 wa = *reinterpret_cast<const float2*>(w + i), wb = *reinterpret_cast<const float2*>(w + i + half);
-        x1[j].x = round_to<T>(round_to<T>(x1[j].x / denom) * wa.x); x1[j].y = round_to<T>(round_to<T>(x1[j].y / denom) * wa.y);
-        x2[j].x = round_to<T>(round_to<T>(x2[j].x / denom) * wb.x); x2[j].y = round_to<T>(round_to<T>(x2[j].y / denom) * wb.y);
+        x1[h][j] = load2<T>(row + i);
+        x2[h][j] = load2<T>(row + i + half);
+        if (w) {
+          wa[h][j] = *reinterpret_cast<const float2*>(w + i);
+          wb[h][j] = *reinterpret_cast<const float2*>(w + i + half);
+        }
       }
     }
   }
-  const float* cs = cos_sin + (size_t)pos * hd;
-  T* dst = is_q ? row : kcache + (((size_t)(slot / block_size) * kvh + (head - nh)) * block_size + slot % block_size) * hd;
 #pragma unroll
-  for (int j = 0; j < MAXV; ++j) {
-    const int i = 2 * lane + 64 * j;
-    if (i < half) {
-      const float2 c = *reinterpret_cast<const float2*>(cs + i), sn = *reinterpret_cast<const float2*>(cs + i + half);
-      store2<T>(dst + i, make_float2(x1[j].x * c.x - x2[j].x * sn.x, x1[j].y * c.y - x2[j].y * sn.y));
-      store2<T>(dst + i + half, make_float2(x2[j].x * c.x + x1[j].x * sn.x, x2[j].y * c.y + x1[j].y * sn.y));
+  for (int h = 0; h < HPW; ++h) {
+    const int head = head0 + h;
+    if (head >= total_heads) continue;
+    T* row = qkv + (size_t)t * width + (size_t)head * hd;
+    const T* brow = bias ? bias + (size_t)head * hd : nullptr;
+    const bool is_q = head < nh, is_k = !is_q && head < nh + kvh;
+    if (!is_q && (!write_kv || slot < 0)) continue;
+    if (!is_q && slot >= num_slots) {
+      if (lane == 0) atomicOr(err, VOB_ERR_SLOT);
+      continue;
+    }
+    if (brow) {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int i = 2 * lane + 64 * j;
+        if (i < half) {
+          const float2 ba = load2<T>(brow + i), bb = load2<T>(brow + i + half);
+          x1[h][j].x = round_to<T>(x1[h][j].x + ba.x); x1[h][j].y = round_to<T>(x1[h][j].y + ba.y);
+          x2[h][j].x = round_to<T>(x2[h][j].x + bb.x); x2[h][j].y = round_to<T>(x2[h][j].y + bb.y);
+        }
+      }
+    }
+    if (!is_q && !is_k) {  // value head: copy
+      T* dst = vcache + (((size_t)(slot / block_size) * kvh + (head - nh - kvh)) * block_size + slot % block_size) * hd;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int i = 2 * lane + 64 * j;
+        if (i < half) { store2<T>(dst + i, x1[h][j]); store2<T>(dst + i + half, x2[h][j]); }
+      }
+      continue;
+    }
+    if (!pos_ok) {
+      if (lane == 0) atomicOr(err, VOB_ERR_POSITION);
+      continue;
+    }
+    if (is_q ? wq != nullptr : wk != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < NV; ++j)
+        if (2 * lane + 64 * j < half)
+          ss += x1[h][j].x * x1[h][j].x + x1[h][j].y * x1[h][j].y + x2[h][j].x * x2[h][j].x + x2[h][j].y * x2[h][j].y;
+      ss = warp_sum(ss);
+      const float denom = sqrtf(ss / (float)hd + eps);
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        if (2 * lane + 64 * j < half) {
+          x1[h][j].x = round_to<T>(round_to<T>(x1[h][j].x / denom) * wa[h][j].x);
+          x1[h][j].y = round_to<T>(round_to<T>(x1[h][j].y / denom) * wa[h][j].y);
+          x2[h][j].x = round_to<T>(round_to<T>(x2[h][j].x / denom) * wb[h][j].x);
+          x2[h][j].y = round_to<T>(round_to<T>(x2[h][j].y / denom) * wb[h][j].y);
+        }
+      }
+    }
+    T* dst = is_q ? row : kcache + (((size_t)(slot / block_size) * kvh + (head - nh)) * block_size + slot % block_size) * hd;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = 2 * lane + 64 * j;
+      if (i < half) {
+        store2<T>(dst + i, make_float2(x1[h][j].x * c[j].x - x2[h][j].x * sn[j].x, x1[h][j].y * c[j].y - x2[h][j].y * sn[j].y));
+        store2<T>(dst + i + half, make_float2(x2[h][j].x * c[j].x + x1[h][j].x * sn[j].x, x2[h][j].y * c[j].y + x1[h][j].y * sn[j].y));
+      }
     }
   }
+}
+
+// The same for bfloat16 and head sizes 16 * LPH (LPH a power of two up to 32) with 16-byte accesses: LPH lanes share
+// a head (a lane owns elements 8*li .. 8*li+7 of both halves), a warp takes 32 / LPH heads.  The quotient
+// x / sqrt(..) is formed as x * (1 / sqrt(..)): one float unit of difference at most, far below bfloat16's step.
+template <int LPH>
+__global__ void qk_norm_rope_kv_write_wide_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ bias,
+                                                  const int* __restrict__ positions, const int* __restrict__ slots,
+                                                  const float* __restrict__ wq, const float* __restrict__ wk,
+                                                  const float* __restrict__ cos_sin, __nv_bfloat16* __restrict__ kcache,
+                                                  __nv_bfloat16* __restrict__ vcache, int nh, int kvh, float eps, int max_pos,
+                                                  long num_slots, int block_size, int write_kv, int* err) {
+  using T = __nv_bfloat16;
+  constexpr int HD_ = 16 * LPH, HALF = 8 * LPH, HPW = 32 / LPH;
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int li = lane % LPH;
+  const int head = (blockIdx.y * (blockDim.x >> 5) + warp) * HPW + lane / LPH;
+  const int total_heads = nh + 2 * kvh;
+  const int pos = positions[t];
+  const int slot = slots ? slots[t] : -1;
+  const bool pos_ok = pos >= 0 && pos < max_pos;
+  const int i = li * 8;
+  const bool is_q = head < nh, is_k = !is_q && head < nh + kvh, is_v = !is_q && !is_k && head < total_heads;
+  const float* w = is_q ? wq : (is_k ? wk : nullptr);
+  float c[8], sn[8], wa[8], wb[8];
+  if (pos_ok && (is_q || is_k)) {
+    const float* cs = cos_sin + (size_t)pos * HD_ + i;
+    *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cs);
+    *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cs + 4);
+    *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(cs + HALF);
+    *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(cs + HALF + 4);
+  }
+  if (w) {
+    *reinterpret_cast<float4*>(wa) = *reinterpret_cast<const float4*>(w + i);
+    *reinterpret_cast<float4*>(wa + 4) = *reinterpret_cast<const float4*>(w + i + 4);
+    *reinterpret_cast<float4*>(wb) = *reinterpret_cast<const float4*>(w + HALF + i);
+    *reinterpret_cast<float4*>(wb + 4) = *reinterpret_cast<const float4*>(w + HALF + i + 4);
+  }
+  pdl_wait();
+  float x1[8], x2[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x1[j] = x2[j] = 0.f;
+  T* row = qkv + (size_t)t * total_heads * HD_ + (size_t)head * HD_;
+  if (head < total_heads) {
+    load16<T>(row + i, x1);
+    load16<T>(row + i + HALF, x2);
+    if (bias) {
+      float ba[8], bb[8];
+      load16<T>(bias + (size_t)head * HD_ + i, ba);
+      load16<T>(bias + (size_t)head * HD_ + i + HALF, bb);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { x1[j] = round_to<T>(x1[j] + ba[j]); x2[j] = round_to<T>(x2[j] + bb[j]); }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss += x1[j] * x1[j] + x2[j] * x2[j];
+#pragma unroll
+  for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (head >= total_heads) return;
+  if (!is_q) {
+    if (!write_kv || slot < 0) return;
+    if (slot >= num_slots) {
+      if (li == 0) atomicOr(err, VOB_ERR_SLOT);
+      return;
+    }
+  }
+  if (is_v) {
+    T* dst = vcache + (((size_t)(slot / block_size) * kvh + (head - nh - kvh)) * block_size + slot % block_size) * HD_;
+    store16<T>(dst + i, x1);
+    store16<T>(dst + i + HALF, x2);
+    return;
+  }
+  if (!pos_ok) {
+    if (li == 0) atomicOr(err, VOB_ERR_POSITION);
+    return;
+  }
+  if (w) {
+    const float inv = 1.f / sqrtf(ss / (float)HD_ + eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      x1[j] = round_to<T>(round_to<T>(x1[j] * inv) * wa[j]);
+      x2[j] = round_to<T>(round_to<T>(x2[j] * inv) * wb[j]);
+    }
+  }
+  T* dst = is_q ? row : kcache + (((size_t)(slot / block_size) * kvh + (head - nh)) * block_size + slot % block_size) * HD_;
+  float o1[8], o2[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    o1[j] = x1[j] * c[j] - x2[j] * sn[j];
+    o2[j] = x2[j] * c[j] + x1[j] * sn[j];
+  }
+  store16<T>(dst + i, o1);
+  store16<T>(dst + i + HALF, o2);
 }
 
 // ---------------------------------------------------------------- page copy (utility)
@@ -347,22 +480,24 @@ static int add_rmsnorm_launch(const void* x, void* residual, const float* w, voi
                               int num_src_rows, float eps, int has_residual, int* err, cudaStream_t stream) {
   constexpr int NT = 256;
   const bool vec = ((size_t)H * sizeof(T)) % 16 == 0 && ((uintptr_t)x | (uintptr_t)residual | (uintptr_t)y) % 16 == 0;
-  const bool reg = vec && H <= 4 * NT * Vec16<T>::N;
+  const int pieces = vec ? (H / Vec16<T>::N + NT - 1) / NT : 0;          // 16-byte pieces of a row per thread
+  const int reg = vec && pieces <= 4 && (uintptr_t)w % 16 == 0 ? (pieces <= 1 ? 1 : (pieces <= 2 ? 2 : 4)) : 0;
   const size_t smem = reg ? 0 : (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return VOB_UNSUPPORTED;
   if (smem > 48 * 1024) {
-    cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                        : cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT, true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                        : cudaFuncSetAttribute(add_rmsnorm_kernel<T, NT, false, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  if (reg)
-    return launch_kernel(add_rmsnorm_kernel<T, NT, true, true>, n_out, NT, smem, stream, (const T*)x, (T*)residual, w, (T*)y, rows,
-                         H, num_src_rows, eps, has_residual, err);
-  if (vec)
-    return launch_kernel(add_rmsnorm_kernel<T, NT, true, false>, n_out, NT, smem, stream, (const T*)x, (T*)residual, w, (T*)y, rows,
-                         H, num_src_rows, eps, has_residual, err);
-  return launch_kernel(add_rmsnorm_kernel<T, NT, false, false>, n_out, NT, smem, stream, (const T*)x, (T*)residual, w, (T*)y, rows,
-                       H, num_src_rows, eps, has_residual, err);
+#define VOB_NORM_LAUNCH(VEC, REG)                                                                                         \
+  return launch_kernel(add_rmsnorm_kernel<T, NT, VEC, REG>, n_out, NT, smem, stream, (const T*)x, (T*)residual, w, (T*)y, \
+                       rows, H, num_src_rows, eps, has_residual, err)
+  if (reg == 1) VOB_NORM_LAUNCH(true, 1);
+  if (reg == 2) VOB_NORM_LAUNCH(true, 2);
+  if (reg == 4) VOB_NORM_LAUNCH(true, 4);
+  if (vec) VOB_NORM_LAUNCH(true, 0);
+  VOB_NORM_LAUNCH(false, 0);
+#undef VOB_NORM_LAUNCH
 }
 
 // y[n_out, H]; x and residual [num_src_rows, H]; rows may be null (then n_out == num_src_rows).
@@ -401,16 +536,41 @@ VOB_API int vob_qk_norm_rope_kv_write(void* qkv, const void* bias, const int* po
   if (T <= 0) return 0;
   if (hd <= 0 || hd % 2 || hd > 512 || block_size <= 0) return VOB_UNSUPPORTED;
   if ((wq == nullptr) != (wk == nullptr)) return VOB_BAD_ARGUMENT;
+  if (dtype == VOB_BF16 && hd >= 16 && (hd & (hd - 1)) == 0 &&
+      (((uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)cos_sin | (uintptr_t)wq | (uintptr_t)wk) % 16) == 0) {
+    // head sizes that are a power of two: 16-byte accesses, hd / 16 lanes a head
+    const int lph = hd / 16, warps = 4;
+    dim3 grid(T, (nh + 2 * kvh + warps * (32 / lph) - 1) / (warps * (32 / lph)));
+#define VOB_ROPE_WIDE(LPH)                                                                                                  \
+  if (lph == LPH)                                                                                                           \
+    return launch_kernel(qk_norm_rope_kv_write_wide_kernel<LPH>, grid, warps * 32, 0, stream, (__nv_bfloat16*)qkv,          \
+                         (const __nv_bfloat16*)bias, positions, slots, wq, wk, cos_sin, (__nv_bfloat16*)kcache,             \
+                         (__nv_bfloat16*)vcache, nh, kvh, eps, max_pos, num_slots, block_size, write_kv, err)
+    VOB_ROPE_WIDE(1); VOB_ROPE_WIDE(2); VOB_ROPE_WIDE(4); VOB_ROPE_WIDE(8); VOB_ROPE_WIDE(16); VOB_ROPE_WIDE(32);
+#undef VOB_ROPE_WIDE
+  }
+  // a warp takes one head when there are few tokens (decoding), four when there are many
+  const int nv = hd <= 128 ? 1 : (hd <= 256 ? 2 : 4);
+  const int hpw = T >= 256 ? 4 : 1;
   const int warps = 4;
-  dim3 grid(T, (nh + 2 * kvh + warps - 1) / warps);
-  if (dtype == VOB_F32)
-    return launch_kernel(qk_norm_rope_kv_write_kernel<float>, grid, warps * 32, 0, stream, (float*)qkv, (const float*)bias,
-                         positions, slots, wq, wk, cos_sin, (float*)kcache, (float*)vcache, nh, kvh, hd, eps, max_pos,
-                         num_slots, block_size, write_kv, err);
-  if (dtype == VOB_BF16)
-    return launch_kernel(qk_norm_rope_kv_write_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream, (__nv_bfloat16*)qkv,
-                         (const __nv_bfloat16*)bias, positions, slots, wq, wk, cos_sin, (__nv_bfloat16*)kcache,
-                         (__nv_bfloat16*)vcache, nh, kvh, hd, eps, max_pos, num_slots, block_size, write_kv, err);
+  dim3 grid(T, (nh + 2 * kvh + warps * hpw - 1) / (warps * hpw));
+#define VOB_ROPE_LAUNCH(TYPE, NV, HPW)                                                                                   \
+  return launch_kernel(qk_norm_rope_kv_write_kernel<TYPE, NV, HPW>, grid, warps * 32, 0, stream, (TYPE*)qkv,            \
+                       (const TYPE*)bias, positions, slots, wq, wk, cos_sin, (TYPE*)kcache, (TYPE*)vcache, nh, kvh, hd,  \
+                       eps, max_pos, num_slots, block_size, write_kv, err)
+#define VOB_ROPE_DISPATCH(TYPE)                                      \
+  if (hpw == 1) {                                                    \
+    if (nv == 1) VOB_ROPE_LAUNCH(TYPE, 1, 1);                        \
+    if (nv == 2) VOB_ROPE_LAUNCH(TYPE, 2, 1);                        \
+    VOB_ROPE_LAUNCH(TYPE, 4, 1);                                     \
+  }                                                                  \
+  if (nv == 1) VOB_ROPE_LAUNCH(TYPE, 1, 4);                          \
+  if (nv == 2) VOB_ROPE_LAUNCH(TYPE, 2, 4);                          \
+  VOB_ROPE_LAUNCH(TYPE, 4, 4)
+  if (dtype == VOB_F32) { VOB_ROPE_DISPATCH(float); }
+  if (dtype == VOB_BF16) { VOB_ROPE_DISPATCH(__nv_bfloat16); }
+#undef VOB_ROPE_DISPATCH
+#undef VOB_ROPE_LAUNCH
   return VOB_BAD_ARGUMENT;
 }
 

@@ -5,14 +5,18 @@
 // key/value head share every key and value brought in) and walks the keys in steps of 64:
 //   warps 0 .. 4NQ-1   softmax: warp w of a tile owns rows 32(w%4) .. +31 of it, a thread owns ONE row: it reads the
 //                      row's 64 scores from tensor memory (tcgen05.ld), masks, takes the maximum and the sum without
-//                      any exchange between threads, writes P in bfloat16 to shared memory (128-byte swizzled, the A
+//                      any exchange between threads, writes P in bfloat16 back to tensor memory over the scores (the A
 //                      operand of the second product), and at the end divides the row of O by its sum and stores it;
 //   warp 4NQ           producer: looks the pages up a chunk ahead and brings K and V tiles in by TMA into a ring of
 //                      stages (the K tile is the K-major B operand of the first product as it lands, the V tile the
 //                      MN-major B operand of the second one: no transposition anywhere);
-//   warp 4NQ+1         allocates tensor memory and issues the products from one thread: the scores of step j+1 go
-//                      into a second S buffer while the softmax of step j runs; tcgen05.commit tells the softmax warps
-//                      that S is complete, that O has been updated, and the producer that a stage is free.
+//   warps 4NQ+1 ..     one per query tile (the first of them allocates tensor memory): a thread issues the tile's
+//                      products, the scores of step j+1 into a second S buffer while the softmax of step j runs;
+//                      tcgen05.commit tells the softmax warps that S is complete and that O has been updated, and
+//                      the producer that the tile is done with a stage.  The tiles do not wait for one another.
+// A wait on an mbarrier goes by the parity of the phase, so a waiter must never fall two phases behind: the scores
+// and P have a barrier per buffer (a buffer's next use needs the waiter's own progress), and O's barrier is waited on
+// for every phase or for the last two in turn.
 // O stays in tensor memory over all steps.  The running maximum that the exponentials refer to is moved only when a
 // row's new maximum exceeds it by more than 8 (in base-2 units: P stays below 256, exact enough in bfloat16 since
 // its error is relative); only then the row's O is read, scaled and written back, which is rare after the first
@@ -29,18 +33,19 @@ constexpr int F5_ROWS = 128;                               // rows of a query ti
 constexpr int F5_TILE = 64;                                // keys per step
 constexpr int F5_SLICES = HD / 64;                         // 64-column slices of a head
 constexpr int F5_Q_BYTES = F5_SLICES * F5_ROWS * 128;      // a query tile: [slice][128 rows][128 bytes]
-constexpr int F5_P_BYTES = F5_ROWS * 128;                  // P of one step: [128 rows][64 keys]
 constexpr int F5_KV_BYTES = F5_SLICES * F5_TILE * 128;     // one of K or V: [slice][64 keys][128 bytes]
 constexpr int F5_STAGE_BYTES = 2 * F5_KV_BYTES;
 constexpr float F5_MAX_SLACK = 8.f;                        // how far a row's maximum may run ahead of its reference
 
 template <int NQ> struct F5 {
-  static constexpr int THREADS = (4 * NQ + 2) * 32;
-  static constexpr int STAGES = NQ == 1 ? 4 : 3;
+  static constexpr int THREADS = (5 * NQ + 1) * 32;        // 4 softmax warps and one issuing warp per tile, a producer
+  // shared memory left after the query tiles (and P, if it lives there) goes to the ring: a copy takes about as long
+  // as several steps, so the ring's depth is what keeps the tensor cores fed
+  static constexpr int STAGES = (220 * 1024 - NQ * F5_Q_BYTES) / F5_STAGE_BYTES;
   static constexpr int TILE_COLS = 2 * F5_TILE + HD;       // tensor-memory columns of a query tile: S, S, O
   static constexpr int TMEM_COLS = NQ * TILE_COLS <= 256 ? 256 : 512;
-  static constexpr int DATA_BYTES = NQ * (F5_Q_BYTES + F5_P_BYTES) + STAGES * F5_STAGE_BYTES;
-  static constexpr int NUM_BARRIERS = 2 * STAGES + 4 * NQ + 1;
+  static constexpr int DATA_BYTES = NQ * F5_Q_BYTES + STAGES * F5_STAGE_BYTES;
+  static constexpr int NUM_BARRIERS = 2 * STAGES + 5 * NQ + 1;
   static constexpr int SMEM_BYTES = 1024 + DATA_BYTES + NUM_BARRIERS * 8 + 16;
 };
 
@@ -56,13 +61,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   extern __shared__ __align__(1024) char smem_raw[];
   char* smem = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   char* q_s = smem;                                         // [NQ] query tiles
-  char* p_s = q_s + NQ * F5_Q_BYTES;                        // [NQ] P tiles
-  char* kv_s = p_s + NQ * F5_P_BYTES;                       // [ST] stages: K tile, V tile
+  char* kv_s = q_s + NQ * F5_Q_BYTES;                       // [ST] stages: K tile, V tile
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + C::DATA_BYTES);
   uint64_t* kv_empty = kv_full + ST;
   uint64_t* s_full = kv_empty + ST;                         // [NQ][2] scores of a step are complete
-  uint64_t* p_full = s_full + 2 * NQ;                       // [NQ] P is written (and S read, O rescaled)
-  uint64_t* o_done = p_full + NQ;                           // [NQ] O holds the step's contribution
+  uint64_t* p_full = s_full + 2 * NQ;                       // [NQ][2] P of a step is written (and S read, O rescaled)
+  uint64_t* o_done = p_full + 2 * NQ;                       // [NQ] O holds the step's contribution
   uint64_t* drained = o_done + NQ;                          // every product issued has completed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -101,10 +105,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   }
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int i = 0; i < 2 * NQ; ++i) mbar_init(&s_full[i], 1);
-    for (int i = 0; i < NQ; ++i) { mbar_init(&p_full[i], 4); mbar_init(&o_done[i], 1); }
-    mbar_init(drained, 1);
+    for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], NQ); }
+    for (int i = 0; i < 2 * NQ; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); }
+    for (int i = 0; i < NQ; ++i) mbar_init(&o_done[i], 1);
+    mbar_init(drained, NQ);
     *abort_flag = 0;
     tma_prefetch_map(&tmK);
     tma_prefetch_map(&tmV);
@@ -185,52 +189,58 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
         if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
       }
     }
-  } else if (warp == 4 * NQ + 1) {
-    // ------------------------------------------------ the products (one thread)
+  } else if (warp > 4 * NQ) {
+    // ------------------------------------------------ the products of query tile qt (one thread per tile)
     if (lane == 0) {
+      const int qt = warp - (4 * NQ + 1);
       const uint32_t idesc_qk = t5_instr_desc(F5_ROWS, F5_TILE);
       const uint32_t idesc_pv = t5_instr_desc_b_mn(F5_ROWS, HD);
+      const int lo = jlo[qt], hi = jhi[qt];
+      const uint32_t s_tmem = tmem_base + qt * C::TILE_COLS, o_tmem = s_tmem + 2 * F5_TILE;
+      // descriptors differ from one k-step or stage to the next only in the start address (in units of 16 bytes)
+      const uint64_t q_desc = t5_smem_desc(q_s + qt * F5_Q_BYTES);
+      const uint64_t k_desc0 = t5_smem_desc(kv_s);
+      const uint64_t v_desc0 = t5_smem_desc_mn(kv_s + F5_KV_BYTES, F5_TILE * 128, 1024);
       bool ok = true;
-      // S[qt][buffer] = Q[qt] K_j^T for every query tile that takes part in step j
+      // S[buffer] = Q K_j^T
       auto scores = [&](int j) {
-        const char* kt = kv_s + (j % ST) * F5_STAGE_BYTES;
+        const int i = j - lo;
+        const uint64_t kd = k_desc0 + (uint64_t)(((j % ST) * F5_STAGE_BYTES) >> 4);
 #pragma unroll
-        for (int qt = 0; qt < NQ; ++qt) {
-          if (j < jlo[qt] || j >= jhi[qt]) continue;
-          const int i = j - jlo[qt];
-          const uint32_t d = tmem_base + qt * C::TILE_COLS + (i & 1) * F5_TILE;
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks)
-            t5_mma(d, t5_smem_desc(q_s + qt * F5_Q_BYTES + (ks >> 2) * (F5_ROWS * 128) + (ks & 3) * 32),
-                   t5_smem_desc(kt + (ks >> 2) * (F5_TILE * 128) + (ks & 3) * 32), idesc_qk, ks > 0);
-          t5_commit(&s_full[qt * 2 + (i & 1)]);
-        }
+        for (int ks = 0; ks < HD / 16; ++ks)
+          t5_mma(s_tmem + (i & 1) * F5_TILE, q_desc + (uint64_t)(((ks >> 2) * (F5_ROWS * 128) + (ks & 3) * 32) >> 4),
+                 kd + (uint64_t)(((ks >> 2) * (F5_TILE * 128) + (ks & 3) * 32) >> 4), idesc_qk, ks > 0);
+        t5_commit(&s_full[qt * 2 + (i & 1)]);
       };
-      ok = mbar_wait(&kv_full[0], 0u, abort_flag, err);
-      if (ok) { t5_fence_after(); scores(0); }
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) {
+        if (j < lo || j >= hi) {
+          // this tile does not need the step's keys: it only tells the producer so, once they have arrived
+          ok = mbar_wait(&kv_full[j % ST], (unsigned)((j / ST) & 1), abort_flag, err);
+          if (ok) mbar_arrive(&kv_empty[j % ST]);
+          continue;
+        }
+        const int i = j - lo;
+        if (i == 0) {
+          ok = mbar_wait(&kv_full[j % ST], (unsigned)((j / ST) & 1), abort_flag, err);
+          if (!ok) break;
+          t5_fence_after();
+          scores(j);
+        }
+        if (j + 1 < hi) {      // the scores of the next step go into the other buffer while this step's softmax runs
           ok = mbar_wait(&kv_full[(j + 1) % ST], (unsigned)(((j + 1) / ST) & 1), abort_flag, err);
           if (!ok) break;
           t5_fence_after();
           scores(j + 1);
         }
-        const char* vt = kv_s + (j % ST) * F5_STAGE_BYTES + F5_KV_BYTES;
-#pragma unroll
-        for (int qt = 0; qt < NQ; ++qt) {
-          if (j < jlo[qt] || j >= jhi[qt]) continue;
-          const int i = j - jlo[qt];
-          ok = mbar_wait(&p_full[qt], (unsigned)(i & 1), abort_flag, err);
-          if (!ok) break;
-          t5_fence_after();
-          const uint32_t d = tmem_base + qt * C::TILE_COLS + 2 * F5_TILE;
-#pragma unroll
-          for (int ks = 0; ks < F5_TILE / 16; ++ks)
-            t5_mma(d, t5_smem_desc(p_s + qt * F5_P_BYTES + ks * 32),
-                   t5_smem_desc_mn(vt + ks * 16 * 128, F5_TILE * 128, 1024), idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
-          t5_commit(&o_done[qt]);
-        }
+        ok = mbar_wait(&p_full[qt * 2 + (i & 1)], (unsigned)((i >> 1) & 1), abort_flag, err);
         if (!ok) break;
+        t5_fence_after();
+        const uint64_t vd = v_desc0 + (uint64_t)(((j % ST) * F5_STAGE_BYTES) >> 4);
+#pragma unroll
+        for (int ks = 0; ks < F5_TILE / 16; ++ks)
+          t5_mma_a_tmem(o_tmem, s_tmem + (i & 1) * F5_TILE + ks * 8, vd + (uint64_t)((ks * 16 * 128) >> 4), idesc_pv,
+                        (i > 0 || ks > 0) ? 1u : 0u);
+        t5_commit(&o_done[qt]);
         t5_commit(&kv_empty[j % ST]);
       }
       // nothing may still read shared or tensor memory when the block ends
@@ -251,7 +261,6 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     const int t_pos_lo = first_pos + r_first / G, t_pos_hi = first_pos + r_last / G;
     const bool all_rows = r_first + F5_ROWS <= total_rows;
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + qt * C::TILE_COLS;
-    char* p_row = p_s + qt * F5_P_BYTES;
     const float sc = scale * LOG2E;
     float m_ref = -INFINITY, l = 0.f;
     const int my_lo = jlo[qt], my_hi = jhi[qt];
@@ -306,36 +315,37 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       }
       const float sum = sum0 + sum1;
       l += sum;
-      if (i > 0) {
-        // the product of the step before has left P and updated O
+      // O is touched only to rescale it, and then the product of the step before must have updated it
+      const bool rescale = i > 0 && __any_sync(0xffffffffu, grow);
+      if (rescale) {
         ok = mbar_wait(&o_done[qt], (unsigned)((i - 1) & 1), abort_flag, err);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         t5_fence_after();
-        if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-          for (int c0 = 0; c0 < HD; c0 += 32) {
-            uint32_t o[32];
-            t5_ld32_issue(lane_base + 2 * F5_TILE + c0, o);
-            t5_wait_ld();
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t o[32];
+          t5_ld32_issue(lane_base + 2 * F5_TILE + c0, o);
+          t5_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
-            t5_st32(lane_base + 2 * F5_TILE + c0, o);
-          }
-          t5_wait_st();
+          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+          t5_st32(lane_base + 2 * F5_TILE + c0, o);
         }
+        t5_wait_st();
       }
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(p_row + swizzled_offset(r, c)) =
-            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      // P (bfloat16, two keys per 32-bit column) takes the place of the first 32 columns of the scores it was made
+      // from: all of them are in registers now, and the buffer's next scores come after the product that reads P
+      t5_st32(lane_base + (i & 1) * F5_TILE, packed);
+      t5_wait_st();
       t5_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[qt]);
+      if (lane == 0) mbar_arrive(&p_full[qt * 2 + (i & 1)]);
     }
     if (ok && my_hi > my_lo) {
-      ok = mbar_wait(&o_done[qt], (unsigned)((my_hi - my_lo - 1) & 1), abort_flag, err);
+      // the last two products may both be pending: a wait by parity can tell only the latest phase from the one before
+      const int steps = my_hi - my_lo;
+      if (steps > 1) ok = mbar_wait(&o_done[qt], (unsigned)((steps - 2) & 1), abort_flag, err);
+      if (ok) ok = mbar_wait(&o_done[qt], (unsigned)((steps - 1) & 1), abort_flag, err);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         t5_fence_after();

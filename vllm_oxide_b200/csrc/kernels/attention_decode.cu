@@ -173,11 +173,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                             const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                             const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
                             long num_pages, float* __restrict__ part_o, float* __restrict__ part_lse,
-                            int box_keys, int* err) {
+                            int box_keys, int cluster, int* err) {
   extern __shared__ __align__(1024) char smem_raw[];
   char* smem = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int MERGE_BYTES = (2 * DEC_WARPS * 16 + DEC_WARPS * 16 * HD) * 4;
-  constexpr int DATA_BYTES = DT_STAGES * DT_STAGE_BYTES > MERGE_BYTES ? DT_STAGES * DT_STAGE_BYTES : MERGE_BYTES;
+  constexpr int FINAL_BYTES = (16 * HD + 16) * 4;
+  constexpr int DATA_BYTES = DT_STAGES * DT_STAGE_BYTES > MERGE_BYTES + FINAL_BYTES ? DT_STAGES * DT_STAGE_BYTES : MERGE_BYTES + FINAL_BYTES;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + DATA_BYTES);
   uint64_t* empty = full + DT_STAGES;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + DT_STAGES);
@@ -316,10 +317,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   }
   pdl_wait();             // (a no-op for threads that have waited) nothing is written before the kernels before are done
   __syncthreads();        // every stage has been read (or given up): the merge may reuse the memory
-  if (*abort_flag) return;
+  const bool aborted = *abort_flag != 0;
+  if (aborted && !cluster) return;
   float* wm = reinterpret_cast<float*>(smem);                 // [DEC_WARPS][16]
   float* wl = wm + DEC_WARPS * 16;
   float* wo = wl + DEC_WARPS * 16;                            // [DEC_WARPS][16][HD]
+  float* fo = reinterpret_cast<float*>(smem + MERGE_BYTES);   // [16][HD] this block's result, for the other blocks of a cluster
+  float* fl = fo + 16 * HD;                                   // [16] its log-sum-exp
   if (warp < DEC_WARPS) {
     const int g = lane >> 2, tq = lane & 3;
 #pragma unroll
@@ -353,15 +357,53 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
       O += wo[((size_t)w * 16 + r) * HD + d] * f;
     }
     const float val = L > 0.f ? O / L : 0.f;
+    const float lse = (L > 0.f && !aborted) ? M + log2f(L) : -INFINITY;
     const int head = kh * G + r;
     if (num_splits == 1) {
       out[(size_t)t * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(val);
+    } else if (cluster) {
+      fo[idx] = val;
+      if (d == 0) fl[r] = lse;
     } else {
       const size_t p = ((size_t)b * nh + head) * num_splits + split;
       part_o[p * HD + d] = val;
-      if (d == 0) part_lse[p] = L > 0.f ? M + log2f(L) : -INFINITY;
+      if (d == 0) part_lse[p] = lse;
     }
   }
+  if (num_splits == 1 || !cluster) return;
+  // The blocks of a (request, kv head) form a thread-block cluster: each reads the others' results from their shared
+  // memory and merges a share of the outputs (weights 2^(lse - max lse), in the order of the splits).  Every block
+  // of the cluster comes to both barriers, also one that gave up (its log-sum-exp is -inf: weight zero).
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+  {
+    const unsigned fo_addr = smem_addr(fo), fl_addr = smem_addr(fl);
+    for (int idx = split * DT_THREADS + threadIdx.x; idx < G * HD; idx += num_splits * DT_THREADS) {
+      const int r = idx / HD;
+      float M = -INFINITY;
+      for (int sp = 0; sp < num_splits; ++sp) {
+        unsigned ra; float lse;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(fl_addr + r * 4), "r"(sp));
+        asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(lse) : "r"(ra) : "memory");
+        M = fmaxf(M, lse);
+      }
+      float W = 0.f, O = 0.f;
+      for (int sp = 0; sp < num_splits; ++sp) {
+        unsigned ra, rb; float lse, v;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(fl_addr + r * 4), "r"(sp));
+        asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(lse) : "r"(ra) : "memory");
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(rb) : "r"(fo_addr + idx * 4), "r"(sp));
+        asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(rb) : "memory");
+        const float w = lse == -INFINITY ? 0.f : fast_exp2(lse - M);
+        W += w;
+        O += w * v;
+      }
+      out[(size_t)t * nh * HD + (size_t)(kh * G) * HD + idx] = __float2bfloat16_rn(W > 0.f ? O / W : 0.f);
+    }
+  }
+  // nobody may leave while another block still reads its shared memory
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 #endif  // VOB_HD % 64 == 0
 
@@ -404,6 +446,10 @@ VOB_API long vob_attention_decode_scratch_floats(int num_requests, int nh, int n
   return num_splits > 1 ? (long)num_requests * nh * num_splits * (HD + 1) : 0;
 }
 
+static bool g_decode_cluster_merge = true;
+// Up to 8 splits merge through a thread-block cluster (default) or through scratch memory and a second kernel.
+VOB_API void vob_attention_decode_cluster_merge(int on) { g_decode_cluster_merge = on != 0; }
+
 static int attention_decode_launch(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
                                    const void* kcache, const void* vcache, const int* block_tables, int table_stride,
                                    const int* cu_q, const int* context_lens, int num_requests, int nh, int kvh,
@@ -411,7 +457,6 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
                                    int* err, cudaStream_t stream) {
   if (num_requests <= 0) return 0;
   if (kvh <= 0 || nh % kvh || nh / kvh > 16 || block_size <= 0 || num_splits < 1 || num_splits > 65535) return VOB_UNSUPPORTED;
-  if (num_splits > 1 && !scratch) return VOB_BAD_ARGUMENT;
   static bool configured = false;
   const int merge_bytes = (2 * DEC_WARPS * 16 + DEC_WARPS * 16 * HD) * (int)sizeof(float);
   const int smem = DEC_STAGES * DEC_STAGE_BYTES > merge_bytes ? DEC_STAGES * DEC_STAGE_BYTES : merge_bytes;
@@ -427,7 +472,7 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
 #if VOB_HD % 64 == 0
   if (map_k && map_v && block_size % 16 == 0) {
     static bool tma_configured = false;
-    constexpr int MERGE = (2 * DEC_WARPS * 16 + DEC_WARPS * 16 * HD) * 4;
+    constexpr int MERGE = (2 * DEC_WARPS * 16 + DEC_WARPS * 16 * HD) * 4 + (16 * HD + 16) * 4;
     constexpr int DATA = DT_STAGES * DT_STAGE_BYTES > MERGE ? DT_STAGES * DT_STAGE_BYTES : MERGE;
     const int tma_smem = 1024 + DATA + 2 * DT_STAGES * 8 + 32;
     if (!tma_configured) {
@@ -435,15 +480,24 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
       if (e != cudaSuccess) return (int)e;
       tma_configured = true;
     }
+    const int box_keys = block_size % DEC_TILE == 0 ? DEC_TILE : RUN_KEYS;
+    // up to 8 splits: the blocks of a (request, kv head) are a cluster and merge through shared memory
+    if (num_splits > 1 && num_splits <= 8 && g_decode_cluster_merge)
+      return launch_kernel_cluster(attention_decode_tma_kernel, grid, DT_THREADS, tma_smem, stream, (unsigned)num_splits,
+                                   *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride,
+                                   (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size,
+                                   window, scale, num_pages, part_o, part_lse, box_keys, 1, err);
+    if (num_splits > 1 && !scratch) return VOB_BAD_ARGUMENT;
     rc = launch_kernel(attention_decode_tma_kernel, grid, DT_THREADS, tma_smem, stream, *(const CUtensorMap*)map_k,
                        *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, block_tables,
                        table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, part_o, part_lse,
-                       block_size % DEC_TILE == 0 ? DEC_TILE : RUN_KEYS, err);
+                       box_keys, 0, err);
     if (rc || num_splits == 1) return rc;
     return launch_kernel(attention_decode_combine_kernel, dim3(nh, num_requests), HD < 128 ? 64 : 128, 0, stream,
                          (const float*)part_o, (const float*)part_lse, (__nv_bfloat16*)out, cu_q, nh, num_splits);
   }
 #endif
+  if (num_splits > 1 && !scratch) return VOB_BAD_ARGUMENT;
   rc = launch_kernel(attention_decode_kernel, grid, DEC_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, q_stride,
                          (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,
                          table_stride, cu_q, context_lens, nh, kvh, block_size, window, scale, num_pages, part_o, part_lse,

@@ -112,10 +112,11 @@ class Attention(Mixer):
 
 def decode_splits(num_requests: int, kv_heads: int, max_keys: int) -> int:
     """Splits of the key range per (request, kv head): as many as keep every block resident at once
-    (two blocks per SM on 148 SMs), but at least two 64-key tiles per split."""
+    (two blocks per SM on 148 SMs), but at least two 64-key tiles per split, and at most 8: up to that the
+    blocks of a (request, kv head) merge their results as a thread-block cluster, without a second kernel."""
     tiles = -(-max_keys // 64)
     fit = (2 * 148) // max(1, num_requests * kv_heads)
-    return max(1, min(fit, tiles // 2))
+    return max(1, min(fit, tiles // 2, 8))
 
 
 register_part("mixer", "attention", Attention)

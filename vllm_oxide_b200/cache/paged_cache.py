@@ -74,6 +74,10 @@ class PagedCache:
         total = sum(2 * p.k.numel() * p.k.element_size() for p in self.planes if p is not None)
         return total + sum(s.numel() * s.element_size() for s in self.states if s is not None)
 
+    @property
+    def has_states(self) -> bool:
+        return any(s is not None for s in self.states)
+
     def zero_states(self, slots: List[int]) -> None:
         if not slots:
             return

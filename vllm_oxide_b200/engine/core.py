@@ -65,6 +65,7 @@ class _DecodeGraph:
         self.layout, self.ws, self.dev = layout, ws, dev
         self.graph = None
         self.logits = None
+        self.host_view = self.dev_view = None     # the step's arrays in the pinned buffer and on the device
         self.launches = 0     # this package's kernel launches inside the graph
 
 
@@ -126,12 +127,16 @@ class EngineCore:
     def _fill_fixed(self, g: _DecodeGraph, entries) -> "host.BatchCounts":
         if self._copied is not None:
             self._copied.synchronize()
-        counts = host.fill_step_batch(self.manager, list(entries), g.layout, self._host_np)
+        counts = host.fill_step_batch(self.manager, entries if isinstance(entries, list) else list(entries), g.layout,
+                                      self._host_np)
         L = g.layout
-        fresh = [int(s) for s, f in zip(self._host_np[L.state_slots:L.state_slots + counts.num_requests],
-                                        self._host_np[L.state_fresh:L.state_fresh + counts.num_requests]) if f]
-        self.cache.zero_states(fresh)
-        g.dev[:L.total].copy_(self._host_buf[:L.total], non_blocking=True)
+        if self.cache.has_states:
+            fresh = [int(s) for s, f in zip(self._host_np[L.state_slots:L.state_slots + counts.num_requests],
+                                            self._host_np[L.state_fresh:L.state_fresh + counts.num_requests]) if f]
+            self.cache.zero_states(fresh)
+        if g.host_view is None:
+            g.host_view, g.dev_view = self._host_buf[:L.total], g.dev[:L.total]
+        g.dev_view.copy_(g.host_view, non_blocking=True)
         if self._copied is not None:
             self._copied.record()
         self.h2d_bytes_last = L.total * 4
@@ -190,7 +195,10 @@ class EngineCore:
 
     def check_errors(self) -> None:
         """Raises if a kernel met a bad index since the last check (synchronises)."""
-        word = int(self.err.item())
+        self.raise_for(int(self.err.item()))
+
+    def raise_for(self, word: int) -> None:
+        """Raises for a non-zero value of the error word (read by the caller, e.g. together with the sampled tokens)."""
         if word:
             self.err.zero_()
             raise kernels.KernelError("a kernel refused an access: " + kernels.describe_error_word(word))

@@ -186,13 +186,29 @@ class LLM:
                 self._penalties(logits, reqs)
             keys = [row_key(r[5], r[0], r[1]) for r in reqs]
             toks = self.sampler.forward(logits, [r[2] for r in reqs], [r[3] for r in reqs], [r[4] for r in reqs], keys)
-            sampled = toks.cpu().tolist()
-        self.core.check_errors()
+            sampled = self._read_back(toks)
+        else:
+            self.core.check_errors()
         outs = [RequestOutput(o.id, list(o.token_ids), "", o.finished, o.finish_reason)
                 for o in self.scheduler.postprocess(sampled)]
         if want_logits:
             return outs, (logits.float().cpu().numpy().copy() if reqs else None)
         return outs
+
+    def _read_back(self, toks: torch.Tensor) -> List[int]:
+        """The sampled tokens and the kernels' error word in one wait: two copies into one pinned buffer."""
+        n = toks.shape[0]
+        buf = getattr(self, "_readback", None)
+        if buf is None or buf.numel() < n + 1:
+            buf = self._readback = torch.empty(max(n + 1, 1025), dtype=torch.int32,
+                                               pin_memory=torch.device(self.core.device).type == "cuda")
+        buf[:n].copy_(toks, non_blocking=True)
+        buf[n:n + 1].copy_(self.core.err, non_blocking=True)
+        if torch.device(self.core.device).type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        vals = buf[:n + 1].tolist()
+        self.core.raise_for(vals[n])
+        return vals[:n]
 
     def _penalties(self, logits, reqs) -> None:
         hist, pres, freq, rep = [], [], [], []

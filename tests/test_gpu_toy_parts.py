@@ -181,6 +181,157 @@ def test_toy_architecture_steps_like_its_plain_form(toy_folder, dtype):
     close(c, want_b, "state slot used again")
 
 
+E, RI, RL = 3, 40, 2          # experts, their width, layers of the routed toy
+
+
+def toy_angles():
+    """[max_pos, hd] = cos || sin of angles that grow linearly with the pair index (not a power law)."""
+    i = torch.arange(HD // 2, dtype=torch.float32)
+    t = torch.arange(MAXPOS, dtype=torch.float32)
+    ang = t[:, None] * (0.02 * (i + 1.0))[None, :]
+    return torch.cat([ang.cos(), ang.sin()], dim=-1)
+
+
+def register_routed_toy():
+    from vllm_oxide_b200.models import ExecStep, ModelPlan, register_architecture
+    from vllm_oxide_b200.parts import FeedForward, PartSpec, PositionEncoding, register_part
+    from vllm_oxide_b200.weights import TensorSpec
+
+    class LinearAngles(PositionEncoding):
+        """Another table for the attention part's rotation: the interface is the `cos_sin` attribute."""
+
+        def __init__(self, device=None, **_):
+            self.cos_sin = toy_angles().contiguous().to(device)
+
+    class Top1Experts(FeedForward):
+        """Each token goes to the expert with the largest router logit (float, ties to the lowest index):
+        y = down_e(relu(up_e(x)))."""
+
+        def __init__(self, hidden_size, width, experts, prefix, **_):
+            self.H, self.W, self.E, self.prefix = hidden_size, width, experts, prefix
+
+        def tensor_specs(self):
+            p = self.prefix
+            specs = [TensorSpec(p + "router.weight", (self.E, self.H), "norm")]          # kept in float
+            for e in range(self.E):
+                specs += [TensorSpec(f"{p}experts.{e}.up.weight", (self.W, self.H), "matrix", self.H),
+                          TensorSpec(f"{p}experts.{e}.down.weight", (self.H, self.W), "matrix", self.W)]
+            return specs
+
+        def load(self, tensors):
+            p = self.prefix
+            self.router = tensors[p + "router.weight"]
+            self.up = [tensors[f"{p}experts.{e}.up.weight"] for e in range(self.E)]
+            self.down = [tensors[f"{p}experts.{e}.down.weight"] for e in range(self.E)]
+
+        def forward(self, x, ctx):
+            logits = x.float() @ self.router.float().t()
+            choice = logits.argmax(dim=-1)
+            out = torch.zeros_like(x)
+            for e in range(self.E):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    h = torch.relu((x[rows].float() @ self.up[e].float().t()).to(x.dtype))
+                    out[rows] = (h.float() @ self.down[e].float().t()).to(x.dtype)
+            return out
+
+    register_part("position", "toy_linear_angles", LinearAngles)
+    register_part("feed_forward", "toy_top1", Top1Experts)
+
+    @dataclass
+    class RoutedConfig:
+        raw: dict
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+    def norm(name):
+        return PartSpec("rmsnorm", dict(size=H, eps=EPS, weight_name=name))
+
+    def plan(cfg):
+        def layer(i):
+            p = f"routed.layers.{i}."
+            return PartSpec("pre_norm", dict(
+                mixer=PartSpec("attention", dict(hidden_size=H, num_heads=NH, num_kv_heads=KVH, head_dim=HD, eps=EPS,
+                                                 qkv_bias=False, qk_norm=False, window=None, position="angles",
+                                                 prefix=p + "self_attn.")),
+                feed_forward=PartSpec("toy_top1", dict(hidden_size=H, width=RI, experts=E, prefix=p + "moe.")),
+                input_norm=norm(p + "input_layernorm.weight"), post_mixer_norm=norm(p + "post_attention_layernorm.weight")))
+        return ModelPlan(
+            architecture="ToyRoutedForCausalLM", hidden_size=H, vocab_size=V, max_position=MAXPOS,
+            embedding_name="routed.embed.weight", lm_head_name=None, final_norm=norm("routed.norm.weight"),
+            positions={"angles": PartSpec("toy_linear_angles", {})},
+            layers=[layer(i) for i in range(RL)], order=[ExecStep(i, i) for i in range(RL)])
+
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig.from_dict, plan)
+
+
+def plain_routed(weights, tokens, dt):
+    """The routed toy, whole sequence, from the plain parts; returns the logits and each layer's expert choices."""
+    ids = torch.as_tensor(tokens)
+    pos = torch.arange(len(tokens))
+    table = toy_angles()
+    it = torch.float64 if dt == torch.float64 else torch.float32
+    hidden, residual = P.embedding(weights["routed.embed.weight"], ids, dt), None
+    choices, margins = [], []
+    for i in range(RL):
+        p = f"routed.layers.{i}."
+        normed, residual = P.add_rms_norm(hidden, residual, weights[p + "input_layernorm.weight"], EPS, dt)
+        q = P.linear(normed, weights[p + "self_attn.q_proj.weight"], dt)
+        k = P.linear(normed, weights[p + "self_attn.k_proj.weight"], dt)
+        v = P.linear(normed, weights[p + "self_attn.v_proj.weight"], dt)
+        q, k, v = P.split_qkv(torch.cat([q, k, v], -1), NH, KVH, HD)
+        q, k = P.apply_rope(q, pos, table, dt), P.apply_rope(k, pos, table, dt)
+        a = P.linear(P.attention(q, k, v, pos, None, dt), weights[p + "self_attn.o_proj.weight"], dt)
+        normed, residual = P.add_rms_norm(a, residual, weights[p + "post_attention_layernorm.weight"], EPS, dt)
+        logits = normed.to(it) @ weights[p + "moe.router.weight"].to(it).t()
+        top = logits.topk(2, dim=-1).values
+        margins.append((top[:, 0] - top[:, 1]).double())
+        choice = logits.argmax(dim=-1)
+        choices.append(choice)
+        hidden = torch.zeros_like(normed)
+        for e in range(E):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                h = torch.relu(P.linear(normed[rows], weights[f"{p}moe.experts.{e}.up.weight"], dt))
+                hidden[rows] = P.linear(h, weights[f"{p}moe.experts.{e}.down.weight"], dt)
+    hf, _ = P.add_rms_norm(hidden, residual, weights["routed.norm.weight"], EPS, dt)
+    return P.linear(hf, weights["routed.embed.weight"], dt).double().numpy(), choices, torch.stack(margins).min(dim=0).values
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
+    register_routed_toy()
+    from vllm_oxide_b200.engine.loading import write_random_model_folder
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    folder = str(tmp_path / "routed")
+    write_random_model_folder(folder, dict(architectures=["ToyRoutedForCausalLM"]), 23, "fan_in", torch.float32)
+    _, weights = P.read_folder(folder)
+    g = torch.Generator().manual_seed(9)
+    a = torch.randint(0, V, (60,), generator=g).tolist()
+    dt = torch.float64 if dtype == "float32" else torch.bfloat16
+    want, choices, margin = plain_routed(weights, a, dt)
+    assert all(len(set(c.tolist())) == E for c in choices), "every expert must be used, or routing is not tested"
+    # a token whose two best router logits nearly tie may be routed otherwise after rounding: it is left out
+    sure = (margin > (1e-4 if dtype == "float32" else 0.05)).numpy()
+    assert sure.sum() > 40
+
+    def close(got, what):
+        scale = np.abs(want).max()
+        worst = np.abs(np.asarray(got, np.float64) - want)[sure].max() / scale
+        assert worst < (2e-5 if dtype == "float32" else 0.04), f"{what}: {worst:.3e}"
+
+    r = TraceRunner(folder, dtype, 128, 16)
+    close(r.step([dict(id="a", tokens=a, want=list(range(60)))], ["a"]), "whole")
+    r = TraceRunner(folder, dtype, 128, 16)
+    got = [r.step([dict(id="a", tokens=a[:37], want=list(range(37)))], [])]
+    got.append(r.step([dict(id="a", tokens=a[37:39], want=[0, 1])], []))
+    for t in range(39, 60):
+        got.append(r.step([dict(id="a", tokens=[a[t]], want=[0])], []))
+    close(np.concatenate(got), "portions and single tokens")
+
+
 def test_unknown_parts_and_bad_orders_are_refused():
     register_toy()
     from vllm_oxide_b200.models import ExecStep, ModelPlan

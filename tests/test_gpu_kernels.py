@@ -299,6 +299,10 @@ DECODE_CASES = [  # nh, kvh, hd, block_size, window, ctx_lens, splits
     (5, 5, 80, 48, 0, [200], 7),
     (8, 8, 64, 48, 30, [200, 31, 47, 48, 49], 2),
     (12, 3, 192, 32, 0, [333, 1, 65], 3),
+    (32, 8, 128, 256, 0, [701], 8),              # the most splits that merge as a cluster
+    (32, 8, 128, 256, 0, [2050, 701, 100], 8),
+    (8, 2, 64, 64, 0, [1000, 130], 6),
+    (32, 8, 128, 256, 0, [2050], 16),            # more: merged by the second kernel
 ]
 
 

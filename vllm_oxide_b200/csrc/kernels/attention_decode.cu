@@ -20,11 +20,11 @@ constexpr int DEC_STAGES = HD <= 128 ? 3 : 2;
 constexpr int DEC_STAGE_BYTES = 2 * DEC_TILE * ROW_BYTES;   // K tile, then V tile
 
 __global__ void __launch_bounds__(DEC_WARPS * 32)
-attention_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __nv_bfloat16* __restrict__ out,
-                        const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
+attention_decode_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
+                        const __nv_bfloat16* kcache, const __nv_bfloat16* vcache,
                         const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
-                        long num_pages, float* __restrict__ part_o, float* __restrict__ part_lse, int* err) {
+                        long num_pages, float* part_o, float* part_lse, int* err) {
   extern __shared__ __align__(16) char smem[];
   pdl_launch_dependents();
   const int split = blockIdx.x, num_splits = gridDim.x, kh = blockIdx.y, b = blockIdx.z;
@@ -169,10 +169,10 @@ constexpr int DT_THREADS = (DEC_WARPS + 1) * 32;
 
 __global__ void __launch_bounds__(DT_THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                            const __nv_bfloat16* __restrict__ q, long q_stride, __nv_bfloat16* __restrict__ out,
+                            const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
                             const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                             const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
-                            long num_pages, float* __restrict__ part_o, float* __restrict__ part_lse,
+                            long num_pages, float* part_o, float* part_lse,
                             int box_keys, int cluster, int* err) {
   extern __shared__ __align__(1024) char smem_raw[];
   char* smem = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -408,8 +408,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
 #endif  // VOB_HD % 64 == 0
 
 // Merges the splits of every (decoding request, head): weights 2^(lse - max lse).
-__global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                                                __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q, int nh,
+__global__ void attention_decode_combine_kernel(const float* part_o, const float* part_lse,
+                                                __nv_bfloat16* out, const int* __restrict__ cu_q, int nh,
                                                 int num_splits) {
   pdl_launch_dependents();
   const int b = blockIdx.y, head = blockIdx.x;

@@ -20,10 +20,10 @@ constexpr int ATT_WARPS = 4;
 constexpr int ATT_MAXD = 16;  // value dims per lane: hd <= 512
 
 template <typename T>
-__device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int hd);
+__device__ __forceinline__ float dot_row(const float* q, const T* k, int hd);
 
 template <>
-__device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, const float* __restrict__ k, int hd) {
+__device__ __forceinline__ float dot_row<float>(const float* q, const float* k, int hd) {
   float s = 0.f;
   const float4* k4 = reinterpret_cast<const float4*>(k);
   for (int i = 0; i < hd / 4; ++i) {
@@ -34,7 +34,7 @@ __device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, con
 }
 
 template <>
-__device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+__device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* q, const __nv_bfloat16* k,
                                                          int hd) {
   float s = 0.f;
   const uint4* k8 = reinterpret_cast<const uint4*>(k);
@@ -53,8 +53,8 @@ __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict_
 
 template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
-paged_attention_generic_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ out,
-                               const T* __restrict__ kcache, const T* __restrict__ vcache,
+paged_attention_generic_kernel(const T* q, long q_stride, T* out,
+                               const T* kcache, const T* vcache,
                                const int* __restrict__ block_tables, int table_stride,
                                const int* __restrict__ token_req, const int* __restrict__ positions,
                                const int* __restrict__ skip_single_cu_q, int nh, int kvh, int hd, int block_size,

@@ -154,8 +154,8 @@ __device__ __forceinline__ void tile_pages(int (&pages)[TILE / RUN_KEYS], const 
 // first, V rows after them; `pages` comes from tile_pages for the same tile.  Keys outside [begin, end) are
 // zero-filled (a window group has given the pages below its window back).
 template <int TILE, int THREADS>
-__device__ __forceinline__ void load_kv_tile(char* stage, const __nv_bfloat16* __restrict__ kcache,
-                                             const __nv_bfloat16* __restrict__ vcache, const int (&pages)[TILE / RUN_KEYS],
+__device__ __forceinline__ void load_kv_tile(char* stage, const __nv_bfloat16* kcache,
+                                             const __nv_bfloat16* vcache, const int (&pages)[TILE / RUN_KEYS],
                                              int block_size, int kvh, int kh, int tile_start, int begin, int end,
                                              long num_pages, int* err) {
   constexpr int CHUNKS = HD / 8;                       // 16-byte chunks per row

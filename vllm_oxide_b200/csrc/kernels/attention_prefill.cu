@@ -20,8 +20,8 @@ constexpr int PF_STAGES = HD <= 128 ? 3 : 2;
 constexpr int PF_STAGE_BYTES = 2 * PF_TILE * ROW_BYTES;
 
 __global__ void __launch_bounds__(PF_WARPS * 32)
-attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long q_stride, __nv_bfloat16* __restrict__ out,
-                         const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
+attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
+                         const __nv_bfloat16* kcache, const __nv_bfloat16* vcache,
                          const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                          const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
                          long num_pages, int* err) {
@@ -163,7 +163,7 @@ constexpr int PT_THREADS = (PT_WARPS + 1) * 32;
 
 __global__ void __launch_bounds__(PT_THREADS, 1)
 attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                             const __nv_bfloat16* __restrict__ q, long q_stride, __nv_bfloat16* __restrict__ out,
+                             const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
                              const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                              const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
                              long num_pages, int box_keys, int* err) {

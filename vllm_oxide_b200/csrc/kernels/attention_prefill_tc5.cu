@@ -52,7 +52,7 @@ template <int NQ> struct F5 {
 template <int NQ>
 __global__ void __launch_bounds__(F5<NQ>::THREADS, 1)
 attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                             const __nv_bfloat16* __restrict__ q, long q_stride, __nv_bfloat16* __restrict__ out,
+                             const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
                              const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                              const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
                              long num_pages, int box_keys, int* err) {

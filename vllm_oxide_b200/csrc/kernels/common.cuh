@@ -65,6 +65,12 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
 // is still running: it sets up, reads what no earlier kernel writes (weights, tables, the step's index
 // arrays), and only then waits for the earlier kernel to finish (pdl_wait) before it touches
 // activations or the cache.  A kernel launched without the attribute sees both calls as no-ops.
+// One rule follows for every kernel launched this way.  Data that another kernel of the same step has written
+// (activations, partial results, this step's rows of the cache) must not be read through the non-coherent path: such a
+// kernel is alive before its predecessor has finished, and a `const T* __restrict__` parameter lets the compiler use
+// ld.global.nc, which then may return what was there before the predecessor wrote (seen as stale queries in decode
+// attention inside a CUDA graph).  Pointers to such data are declared WITHOUT __restrict__; weights, tables and
+// the step's index arrays, which are complete before the step's first kernel starts, may keep it.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 

@@ -83,7 +83,7 @@ template <> __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16*
 // REG > 0: the row's sums stay in registers between the two passes (rows of at most REG * NT 16-byte pieces); else
 // they are parked in shared memory.  The order of additions is the same in all three and depends on H only.
 template <typename T, int NT, bool VEC, int REG>
-__global__ void __launch_bounds__(NT) add_rmsnorm_kernel(const T* __restrict__ x, T* residual, const float* __restrict__ w, T* __restrict__ y,
+__global__ void __launch_bounds__(NT) add_rmsnorm_kernel(const T* x, T* residual, const float* __restrict__ w, T* y,
                                    const int* __restrict__ rows, int H, int num_src_rows, float eps, int has_residual,
                                    int* err) {
   extern __shared__ float srow[];  // H floats (unused with REG)
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(NT) add_rmsnorm_kernel(const T* __restrict__ x
 // eight gate values and the eight up values of the same outputs.  VEC: eight outputs per thread with 16-byte
 // accesses (I a multiple of 8, 16-byte aligned rows).
 template <typename T, bool VEC>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved) {
+__global__ void silu_mul_kernel(const T* gu, T* out, int I, size_t total, int interleaved) {
   pdl_launch_dependents();
   pdl_wait();
   if (VEC) {
@@ -241,7 +241,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 // before the first is used; with many tokens (prompt portions) a warp takes several heads and shares the
 // angles between them.  NV: 64-element steps a lane makes over half a head (hd <= 128 NV).
 template <typename T, int NV, int HPW>
-__global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __restrict__ bias,
+__global__ void qk_norm_rope_kv_write_kernel(T* qkv, const T* __restrict__ bias,
                                              const int* __restrict__ positions, const int* __restrict__ slots,
                                              const float* __restrict__ wq, const float* __restrict__ wk,
                                              const float* __restrict__ cos_sin, T* __restrict__ kcache,
@@ -360,7 +360,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const T* __res
 // a head (a lane owns elements 8*li .. 8*li+7 of both halves), a warp takes 32 / LPH heads.  The quotient
 // x / sqrt(..) is formed as x * (1 / sqrt(..)): one float unit of difference at most, far below bfloat16's step.
 template <int LPH>
-__global__ void qk_norm_rope_kv_write_wide_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ bias,
+__global__ void qk_norm_rope_kv_write_wide_kernel(__nv_bfloat16* qkv, const __nv_bfloat16* __restrict__ bias,
                                                   const int* __restrict__ positions, const int* __restrict__ slots,
                                                   const float* __restrict__ wq, const float* __restrict__ wk,
                                                   const float* __restrict__ cos_sin, __nv_bfloat16* __restrict__ kcache,

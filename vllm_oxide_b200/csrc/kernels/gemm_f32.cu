@@ -11,7 +11,7 @@ namespace vob {
 constexpr int GM = 64, GN = 64, GK = 16;
 
 __global__ void __launch_bounds__(256)
-gemm_f32_kernel(const float* __restrict__ A, long lda, const float* __restrict__ W, long ldw, float* __restrict__ C,
+gemm_f32_kernel(const float* A, long lda, const float* __restrict__ W, long ldw, float* C,
                 long ldc, const float* __restrict__ bias, int M, int N, int K) {
   __shared__ float As[GK][GM + 4];
   __shared__ float Ws[GK][GN + 4];

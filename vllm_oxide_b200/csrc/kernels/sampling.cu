@@ -57,7 +57,7 @@ __device__ __forceinline__ unsigned long long fixed_mass(float x, float maxv) {
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_kernel(const float* __restrict__ logits, long ld, int V, const float* __restrict__ temperature,
+sample_kernel(const float* logits, long ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const unsigned long long* __restrict__ keys, int* __restrict__ out) {
   __shared__ unsigned long long scratch[32];

@@ -39,9 +39,10 @@ constexpr float F5_MAX_SLACK = 8.f;                        // how far a row's ma
 
 template <int NQ> struct F5 {
   static constexpr int THREADS = (5 * NQ + 1) * 32;        // 4 softmax warps and one issuing warp per tile, a producer
-  // shared memory left after the query tiles (and P, if it lives there) goes to the ring: a copy takes about as long
-  // as several steps, so the ring's depth is what keeps the tensor cores fed
-  static constexpr int STAGES = (220 * 1024 - NQ * F5_Q_BYTES) / F5_STAGE_BYTES;
+  // One tile a block: two blocks share an SM (half the shared memory and half the tensor memory each).  Two tiles a
+  // block: one block per SM.  Shared memory left after the query tiles goes to the ring of K/V stages.
+  static constexpr int BLOCKS_PER_SM = NQ == 1 ? 2 : 1;
+  static constexpr int STAGES = (220 * 1024 / BLOCKS_PER_SM - NQ * F5_Q_BYTES) / F5_STAGE_BYTES;
   static constexpr int TILE_COLS = 2 * F5_TILE + HD;       // tensor-memory columns of a query tile: S, S, O
   static constexpr int TMEM_COLS = NQ * TILE_COLS <= 256 ? 256 : 512;
   static constexpr int DATA_BYTES = NQ * F5_Q_BYTES + STAGES * F5_STAGE_BYTES;
@@ -50,7 +51,7 @@ template <int NQ> struct F5 {
 };
 
 template <int NQ>
-__global__ void __launch_bounds__(F5<NQ>::THREADS, 1)
+__global__ void __launch_bounds__(F5<NQ>::THREADS, F5<NQ>::BLOCKS_PER_SM)
 attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                              const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
                              const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,

@@ -73,7 +73,17 @@ sample_kernel(const float* logits, long ld, int V, const float* __restrict__ tem
 
   if (temp <= 0.f || k == 1) {  // greedy
     unsigned long long best = 0;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+    // four logits a load where the row starts on a 16-byte boundary, the rest one by one
+    const int v4 = ((uintptr_t)l % 16 == 0) ? V / 4 : 0;
+    for (int i = tid; i < v4; i += SAMPLE_THREADS) {
+      const float4 x = reinterpret_cast<const float4*>(l)[i];
+      const unsigned long long c0 = pack_candidate(x.x, 4 * i), c1 = pack_candidate(x.y, 4 * i + 1);
+      const unsigned long long c2 = pack_candidate(x.z, 4 * i + 2), c3 = pack_candidate(x.w, 4 * i + 3);
+      const unsigned long long m01 = c0 > c1 ? c0 : c1, m23 = c2 > c3 ? c2 : c3;
+      const unsigned long long m = m01 > m23 ? m01 : m23;
+      best = m > best ? m : best;
+    }
+    for (int i = 4 * v4 + tid; i < V; i += SAMPLE_THREADS) {
       const unsigned long long c = pack_candidate(l[i], i);
       best = c > best ? c : best;
     }

@@ -68,7 +68,9 @@ class PagedCache:
             None if s is None else torch.zeros((num_state_slots, *s.shape), dtype=s.dtype, device=device)
             for s in state_specs]
         self.manager = host.KvCacheManager(
-            [host.GroupSpec(g.block_size, g.num_blocks, g.window) for g in self.groups], num_state_slots, prefix_caching)
+            [host.GroupSpec(g.block_size, g.num_blocks, g.window) for g in self.groups], num_state_slots,
+            # state of fixed size is not snapshotted at page boundaries: with such a layer nothing is skipped on a hit
+            prefix_caching and not any(s is not None for s in state_specs))
 
     def bytes(self) -> int:
         total = sum(2 * p.k.numel() * p.k.element_size() for p in self.planes if p is not None)

@@ -29,7 +29,9 @@ def _cfg(**kw):
     return base
 
 
-# Three tiny configurations that differ in every size and option.
+# Tiny configurations that differ in every size and option (A, B, C), and one whose sizes reach the kernels that
+# serving sizes use (D: 64-wide heads for the TMA and tcgen05 attention kernels, widths that are multiples of 64
+# for the weight-streaming product and its fused SiLU*up, a window in one layer, pages of 64 keys).
 TINY = {
     # all-keys attention, tied output, 4 query heads over 2 key/value heads
     "A": dict(config=_cfg(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
@@ -47,6 +49,11 @@ TINY = {
                           max_position_embeddings=2048, tie_word_embeddings=False, use_sliding_window=True,
                           sliding_window=24, max_window_layers=2),
               seed=2, block_size=16),
+    "D": dict(config=_cfg(num_hidden_layers=2, hidden_size=128, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                          intermediate_size=192, vocab_size=400, rope_theta=10000.0, rms_norm_eps=1e-6,
+                          max_position_embeddings=1024, tie_word_embeddings=False, use_sliding_window=True,
+                          sliding_window=40, max_window_layers=1),
+              seed=3, block_size=64),
 }
 
 

@@ -20,7 +20,8 @@ def make_llm(model_folders, name, dtype="float32", **kw):
     return LLM(model_folders[name], EngineOptions(**opts))
 
 
-@pytest.mark.parametrize("name,lengths,new", [("A", [7, 33, 1, 64], 16), ("B", [1, 5, 31, 32, 33, 100], 20), ("C", [40, 3], 30)])
+@pytest.mark.parametrize("name,lengths,new", [("A", [7, 33, 1, 64], 16), ("B", [1, 5, 31, 32, 33, 100], 20), ("C", [40, 3], 30),
+                                              ("D", [70, 2, 130], 24)])
 def test_greedy_generation_matches_the_plain_implementation(model_folders, plain_models, name, lengths, new):
     from vllm_oxide_b200 import SamplingParams
     cfg, w = plain_models[name]
@@ -35,11 +36,13 @@ def test_greedy_generation_matches_the_plain_implementation(model_folders, plain
     assert llm.cache.manager.num_requests == 0 and llm.cache.manager.check_invariants() == ""
 
 
-def test_greedy_bfloat16_agrees_with_the_plain_bfloat16_run_where_it_is_sure(model_folders, plain_models):
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_greedy_bfloat16_agrees_with_the_plain_bfloat16_run_where_it_is_sure(model_folders, plain_models, name):
+    """B runs on the plain kernels, D on the tensor-core and weight-streaming ones, decoding from CUDA graphs."""
     from vllm_oxide_b200 import SamplingParams
-    cfg, w = plain_models["B"]
-    prompt = tokens_for("B", 25, salt=5)
-    llm = make_llm(model_folders, "B", "bfloat16")
+    cfg, w = plain_models[name]
+    prompt = tokens_for(name, 25, salt=5)
+    llm = make_llm(model_folders, name, "bfloat16")
     got = llm.generate([prompt], SamplingParams(max_tokens=12, ignore_eos=True))[0].token_ids
     ids = list(prompt)
     for tok in got:       # follow the engine's tokens; wherever the plain top-2 gap is clear they must agree

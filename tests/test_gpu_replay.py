@@ -15,9 +15,9 @@ from conftest import ROOT, TINY, tokens_for
 from plain import qwen3_plain as P
 
 pytestmark = pytest.mark.gpu
-NAMES = ["A", "B", "C"]
+NAMES = ["A", "B", "C", "D"]
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"A": [7, 33, 1, 64, 150], "B": [1, 5, 31, 32, 33, 100], "C": [3, 70, 41, 129, 16]}
+LENGTHS = {"A": [7, 33, 1, 64, 150], "B": [1, 5, 31, 32, 33, 100], "C": [3, 70, 41, 129, 16], "D": [2, 65, 130, 257, 64]}
 
 _plain_cache = {}
 
@@ -179,8 +179,8 @@ def test_mixed_batches_with_pages_used_again(model_folders, plain_models, name, 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding(model_folders, plain_models, dtype):
-    """300 tokens decoded one by one across many pages (and, in C, far past the window)."""
-    for name in ["A", "C"]:
+    """300 tokens decoded one by one across many pages (and, in C and D, far past the window)."""
+    for name in ["A", "C", "D"]:
         toks = tokens_for(name, 320, salt=9)
         want = plain_logits(plain_models, name, toks, dtype)
         r = runner(model_folders, name, dtype, 320)

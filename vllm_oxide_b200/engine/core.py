@@ -137,8 +137,6 @@ class EngineCore:
         if g.host_view is None:
             g.host_view, g.dev_view = self._host_buf[:L.total], g.dev[:L.total]
         g.dev_view.copy_(g.host_view, non_blocking=True)
-        if self._copied is not None:
-            self._copied.record()
         self.h2d_bytes_last = L.total * 4
         return counts
 
@@ -175,6 +173,8 @@ class EngineCore:
         else:
             counts = self._fill_fixed(g, entries)
         g.graph.replay()
+        if self._copied is not None:
+            self._copied.record()     # after the launch: it guards the pinned buffer, and recording it is not free
         kernels.launch_count += g.launches
         self.graph_replays += 1
         return g.logits[:counts.num_rows]

@@ -93,8 +93,16 @@ def test_sampled_generation_is_seeded_and_independent_of_the_batch(model_folders
     assert [o.token_ids for o in llm2.generate(prompts, [sp] * 4)] == together          # same seed, same tokens
     other = SamplingParams(temperature=0.8, max_tokens=16, ignore_eos=True, seed=124)
     assert [o.token_ids for o in make_llm(model_folders, name).generate(prompts, [other] * 4)] != together
-    # request 0 alone in a fresh engine has the same request index, so it draws the same numbers
+    # a request that brings its seed draws the same numbers alone, later in the same engine, or in another order
     assert make_llm(model_folders, name).generate(prompts[:1], [sp])[0].token_ids == together[0]
+    assert llm.generate(prompts[2:3], [sp])[0].token_ids == together[2]
+    assert [o.token_ids for o in llm2.generate(prompts[::-1], [sp] * 4)] == together[::-1]
+    # without a seed of its own a request's numbers are keyed by the engine's seed and its id: two copies of one
+    # prompt in one call differ, and a fresh engine with the same seed repeats the call
+    free = SamplingParams(temperature=0.8, max_tokens=16, ignore_eos=True)
+    a = [o.token_ids for o in make_llm(model_folders, name, seed=9).generate([prompts[1]] * 2, [free] * 2)]
+    assert a[0] != a[1]
+    assert [o.token_ids for o in make_llm(model_folders, name, seed=9).generate([prompts[1]] * 2, [free] * 2)] == a
     greedy = [o.token_ids for o in make_llm(model_folders, name).generate(prompts, SamplingParams(max_tokens=16, ignore_eos=True))]
     assert greedy != together
     topk = SamplingParams(temperature=1.0, top_k=8, top_p=0.9, max_tokens=20, ignore_eos=True, seed=5)

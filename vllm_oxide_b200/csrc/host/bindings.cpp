@@ -93,7 +93,8 @@ PYBIND11_MODULE(_host, m) {
       .def_readwrite("presence_penalty", &SamplingParams::presence_penalty)
       .def_readwrite("frequency_penalty", &SamplingParams::frequency_penalty)
       .def_readwrite("repetition_penalty", &SamplingParams::repetition_penalty)
-      .def_readwrite("seed", &SamplingParams::seed);
+      .def_readwrite("seed", &SamplingParams::seed)
+      .def_readwrite("own_seed", &SamplingParams::own_seed);
 
   py::class_<Sequence>(m, "Sequence")
       .def_readonly("id", &Sequence::id)
@@ -147,13 +148,14 @@ PYBIND11_MODULE(_host, m) {
       // For every scheduled request that wants logits, in entry order:
       // (id, generated so far, temperature, top_k, top_p, seed, has penalties).
       .def("sample_requests", [](const Scheduler& s) {
-        std::vector<std::tuple<int64_t, int, float, int, float, uint64_t, bool>> out;
+        std::vector<std::tuple<int64_t, int, float, int, float, uint64_t, bool, int64_t>> out;
         for (const auto& e : s.last_entries()) {
           if (!e.wants_logits) continue;
           const Sequence& q = s.sequence(e.id);
           const SamplingParams& p = q.params;
           out.emplace_back(q.id, q.num_generated(), p.temperature, p.top_k, p.top_p, p.seed,
-                           p.presence_penalty != 0.f || p.frequency_penalty != 0.f || p.repetition_penalty != 0.f);
+                           p.presence_penalty != 0.f || p.frequency_penalty != 0.f || p.repetition_penalty != 0.f,
+                           p.own_seed ? int64_t(0) : q.id);   // what the random numbers are keyed by, beside seed and index
         }
         return out;
       })

@@ -36,6 +36,7 @@ struct SamplingParams {
   bool ignore_eos = false;
   float presence_penalty = 0.0f, frequency_penalty = 0.0f, repetition_penalty = 0.0f;
   uint64_t seed = 0;
+  bool own_seed = false;     // the request brought its seed: its random numbers then do not depend on its id
 };
 
 struct Sequence {

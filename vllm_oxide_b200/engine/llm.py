@@ -164,6 +164,7 @@ class LLM:
         p.frequency_penalty = float(params.frequency_penalty)
         p.repetition_penalty = float(params.repetition_penalty)
         p.seed = int(params.seed if params.seed is not None else self.options.seed) & ((1 << 64) - 1)
+        p.own_seed = params.seed is not None
         return self.scheduler.add_request([int(t) for t in token_ids], p)
 
     def is_running(self) -> bool:
@@ -184,7 +185,7 @@ class LLM:
         if reqs:
             if any(r[6] for r in reqs):
                 self._penalties(logits, reqs)
-            keys = [row_key(r[5], r[0], r[1]) for r in reqs]
+            keys = [row_key(r[5], r[7], r[1]) for r in reqs]
             toks = self.sampler.forward(logits, [r[2] for r in reqs], [r[3] for r in reqs], [r[4] for r in reqs], keys)
             sampled = self._read_back(toks)
         else:

@@ -16,7 +16,9 @@ class SamplingParams:
     presence_penalty: float = 0.0     # 0 = off for all three
     frequency_penalty: float = 0.0
     repetition_penalty: float = 0.0
-    seed: Optional[int] = None        # None: the engine's seed; a request's tokens depend on (seed, its index)
+    # None: the engine's seed, and the random numbers are keyed by (seed, request id, token index).  Given: they are
+    # keyed by (seed, token index) only, so the same prompt and seed give the same tokens in any call and any batch.
+    seed: Optional[int] = None
 
     def validate(self) -> None:
         if self.temperature < 0:

@@ -153,3 +153,19 @@ def test_command_line(model_folders, plain_models):
                           capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert [int(t) for t in proc.stdout.split()] == P.greedy_generate(cfg, w, prompt, 6, torch.float32)
+
+
+def test_the_same_work_twice_gives_the_same_tokens_bit_for_bit(model_folders):
+    """bfloat16 on the fast kernels, decoding from CUDA graphs: a second run in the same engine lands on other pages
+    and replays the graphs the first run captured; without prefix hits (which change how prompts are cut, and with
+    that the rounding) every token must repeat exactly.  A kernel that read another kernel's output too early, or
+    whose result depended on where its pages lie, would show here."""
+    from vllm_oxide_b200 import SamplingParams
+    llm = make_llm(model_folders, "D", "bfloat16", enable_prefix_caching=False, max_num_batched_tokens=96)
+    prompts = [tokens_for("D", n, salt=600 + i) for i, n in enumerate([70, 2, 130, 64, 33])]
+    sps = [SamplingParams(temperature=0.0 if i % 2 == 0 else 0.9, top_k=20 if i == 3 else None, max_tokens=60,
+                          ignore_eos=True, seed=i) for i in range(len(prompts))]
+    first = [o.token_ids for o in llm.generate(prompts, sps)]
+    assert llm.core.graph_replays > 0
+    llm.generate(prompts[:2], sps[:2])                 # other work in between: the free list is in another order now
+    assert [o.token_ids for o in llm.generate(prompts, sps)] == first

@@ -156,10 +156,13 @@ attention_decode_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* ou
 // ---- the same kernel with the keys and values brought in by TMA ------------------------------------------
 // cp.async moves about 16 bytes per clock and SM on this GPU, the copy engine about twice that, so head sizes
 // that are a multiple of 64 (one or more 128-byte swizzled column slices) take this kernel.  A fifth warp is the
-// producer: one thread looks the pages up (one tile ahead), and issues one copy of K and one of V per tile when
-// pages hold a multiple of 64 keys (a tile then lies in one page), else one per run of 16 keys; a copy brings all
-// column slices at once.  An mbarrier per stage counts the bytes in, a second one the four consumer warps out.
-// Every wait is bounded.  tmK / tmV describe a cache plane as a matrix [pages * kv_heads * block_size, HD] in
+// producer: its lanes look the pages of eight tiles up at once, a chunk ahead (a look-up is a load with a long
+// latency, and a producer that needs one per tile cannot run ahead of it), and one thread issues one copy of K and
+// one of V per tile when pages hold a multiple of 64 keys (a tile then lies in one page), else one per run of 16
+// keys; a copy brings all column slices at once.  An mbarrier per stage counts the bytes in, a second one the four
+// consumer warps out.  Every wait is bounded.  With 2 to 8 splits the blocks of a (request, kv head) are launched as
+// a thread-block cluster and merge their results through each other's shared memory; with more they write partial
+// results to scratch memory for the merge kernel.  tmK / tmV describe a cache plane as a matrix [pages * kv_heads * block_size, HD] in
 // column slices, with boxes of `box_keys` (64 or 16) rows.
 constexpr int DT_SLICES = HD / 64;
 constexpr int DT_TILE_BYTES = DT_SLICES * DEC_TILE * 128;       // one of K or V

@@ -146,9 +146,10 @@ attention_prefill_kernel(const __nv_bfloat16* q, long q_stride, __nv_bfloat16* o
 
 #if VOB_HD % 64 == 0
 // ---- the same attention with TMA copies, 128 rows per block and 64 keys per softmax step ----------------
-// For head sizes that are a multiple of 64.  Eight consumer warps own 16 rows each (128 rows: twice the
-// reuse of every key and value brought in); a ninth warp is the producer: one thread looks the pages up one
-// tile ahead and issues one TMA copy of K and one of V per tile (per run of 16 keys when pages do not hold
+// For head sizes that are a multiple of 64 (head sizes 64 and 128 normally take the tcgen05 kernel of
+// attention_prefill_tc5.cu instead).  Eight consumer warps own 16 rows each (128 rows: twice the reuse of every key
+// and value brought in); a ninth warp is the producer: its lanes look the pages of eight tiles up at once, a chunk
+// ahead, and one thread issues one TMA copy of K and one of V per tile (per run of 16 keys when pages do not hold
 // a multiple of 64), into a ring of stages guarded by mbarriers with bounded waits.  A consumer multiplies
 // its rows with all 64 keys of a tile before it updates the running maximum, so the accumulator is rescaled
 // once per tile; tiles that need no mask (wholly below the diagonal and inside the window) skip the masking.

@@ -13,6 +13,13 @@ of 8 requests whose context starts at 2,048 tokens, and prints ONE JSON line:
   points    decode at batch 1 and 64.
 Every timed step reads 15 GB of weights, far more than the 126 MB L2, so nothing stays cached
 between iterations.  Peaks come from MEASURED_PEAKS.json beside this file when present.
+
+    python bench.py --workload serving-0.6b | mixed-32b
+
+runs one of the two other workloads instead (whole requests through LLM.generate, wall clock, a JSON line of its
+own): 256 requests with prompts of 16 to 1,024 tokens and 128 new tokens each at Qwen3-0.6B sizes (continuous
+batching), or 32 requests with prompts of 512 to 8,192 tokens and 256 new tokens at Qwen3-32B sizes under an
+8,192-token step budget and a cache pool too small for all of them (portions, recompute preemption).
 """
 from __future__ import annotations
 
@@ -206,6 +213,55 @@ def prefill_run(llm, T, reps=3, warmup=2):
     return best
 
 
+WORKLOADS = {
+    "serving-0.6b": dict(
+        config=dict(num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+                    intermediate_size=3072, tie_word_embeddings=True),
+        requests=256, prompt=(16, 1024), new=128, seed=2,
+        options=dict(max_model_len=2048, block_size=256, max_num_seqs=256, max_num_batched_tokens=8192, num_kv_blocks=2048)),
+    "mixed-32b": dict(
+        config=dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                    intermediate_size=25600, tie_word_embeddings=False),
+        requests=32, prompt=(512, 8192), new=256, seed=3,
+        # all 32 contexts together would need about 580 pages of 256 tokens: the pool holds 400
+        options=dict(max_model_len=8192 + 256, block_size=256, max_num_seqs=32, max_num_batched_tokens=8192, num_kv_blocks=400)),
+}
+
+
+def workload_run(name: str) -> int:
+    """Whole requests through the public entry point; prints one JSON line."""
+    import random
+    import torch
+    from vllm_oxide_b200 import LLM, EngineOptions, SamplingParams
+    w = WORKLOADS[name]
+    cfg = dict(QWEN3_8B)
+    cfg.update(w["config"])
+    llm = LLM.from_config(cfg, EngineOptions(dtype="bfloat16", **w["options"]), seed=w["seed"], init_scheme="0.02")
+    rng = random.Random(0)
+    lo, hi = w["prompt"]
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(rng.randint(lo, hi))] for _ in range(w["requests"])]
+    sp = SamplingParams(temperature=0.0, max_tokens=w["new"], ignore_eos=True)
+    llm.generate(prompts[:2], [SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)] * 2)     # warm-up: graphs, libraries
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = llm.generate(prompts, [sp] * len(prompts))
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert all(o.finished and len(o.token_ids) == w["new"] for o in outs)
+    st = llm.last_stats
+    print(json.dumps({
+        "metric": f"tokens/s over whole requests ({name})", "value": round(st.total_tokens / dt, 1), "unit": "tokens/s",
+        "generated_tokens_per_s": round(w["requests"] * w["new"] / dt, 1), "seconds": round(dt, 3), "steps": st.steps,
+        "preemptions": st.preemptions, "n_gpus": 1, "dtype": "bf16", "impl": "ours",
+        "data": "synthetic token ids, seeded random weights",
+        "config": {"model": name, "layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "requests": w["requests"],
+                   "prompt_min": lo, "prompt_max": hi, "new_tokens": w["new"], "step_budget": w["options"]["max_num_batched_tokens"],
+                   "pool_pages": w["options"]["num_kv_blocks"], "block_size": w["options"]["block_size"]}}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -215,6 +271,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (reported)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None, help="another workload instead of the default run")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase and print its time only (for short profiler captures)")
     args = ap.parse_args()
@@ -225,6 +282,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (use --gpus 1)")
         return 2
+    if args.workload:
+        return workload_run(args.workload)
     import torch
     from vllm_oxide_b200 import LLM, EngineOptions
 

@@ -31,7 +31,8 @@ def _cfg(**kw):
 
 # Tiny configurations that differ in every size and option (A, B, C), and one whose sizes reach the kernels that
 # serving sizes use (D: 64-wide heads for the TMA and tcgen05 attention kernels, widths that are multiples of 64
-# for the weight-streaming product and its fused SiLU*up, a window in one layer, pages of 64 keys).
+# for the weight-streaming product and its fused SiLU*up, a window in one layer, pages of 64 keys; E: 128-wide
+# heads on pages of 16 keys).
 TINY = {
     # all-keys attention, tied output, 4 query heads over 2 key/value heads
     "A": dict(config=_cfg(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
@@ -54,6 +55,12 @@ TINY = {
                           max_position_embeddings=1024, tie_word_embeddings=False, use_sliding_window=True,
                           sliding_window=40, max_window_layers=1),
               seed=3, block_size=64),
+    # 128-wide heads (two 64-column slices a tile) on pages of 16 keys (a tile is then copied in runs of 16 keys,
+    # slice by slice), one key/value head for two query heads, tied output
+    "E": dict(config=_cfg(num_hidden_layers=2, hidden_size=192, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+                          intermediate_size=320, vocab_size=211, rope_theta=50000.0, rms_norm_eps=1e-5,
+                          max_position_embeddings=512, tie_word_embeddings=True),
+              seed=4, block_size=16),
 }
 
 

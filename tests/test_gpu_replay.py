@@ -15,9 +15,9 @@ from conftest import ROOT, TINY, tokens_for
 from plain import qwen3_plain as P
 
 pytestmark = pytest.mark.gpu
-NAMES = ["A", "B", "C", "D"]
+NAMES = ["A", "B", "C", "D", "E"]
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"A": [7, 33, 1, 64, 150], "B": [1, 5, 31, 32, 33, 100], "C": [3, 70, 41, 129, 16], "D": [2, 65, 130, 257, 64]}
+LENGTHS = {"A": [7, 33, 1, 64, 150], "B": [1, 5, 31, 32, 33, 100], "C": [3, 70, 41, 129, 16], "D": [2, 65, 130, 257, 64], "E": [1, 17, 64, 129, 200]}
 
 _plain_cache = {}
 

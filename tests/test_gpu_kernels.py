@@ -456,6 +456,62 @@ def test_sampler_against_the_plain_sampler(V):
             assert keep[got[r]]
 
 
+def test_sampler_top_p_on_peaked_and_flat_rows():
+    """top-p gathers the tokens that can still matter into shared memory when they are few (a peaked row, as a
+    language model gives) and searches the whole row when they are many (a flat row): both against the plain sampler."""
+    from vllm_oxide_b200.sampling import Sampler, row_key
+    g = torch.Generator().manual_seed(3)
+    V = 151936
+    rows = []
+    for spread, lift, n_lifted in [(2.0, 12.0, 30), (1.0, 9.0, 3000), (3.0, 0.0, 0), (0.5, 6.0, 5000), (2.0, 15.0, 1), (1.5, 8.0, 4090)]:
+        x = spread * torch.randn(V, generator=g)
+        if n_lifted:
+            idx = torch.randperm(V, generator=g)[:n_lifted]
+            x[idx] += lift + torch.rand(n_lifted, generator=g)
+        rows.append(x)
+    logits = torch.stack(rows).float()
+    R = logits.shape[0]
+    temperature = [1.0, 0.8, 1.0, 1.2, 0.7, 1.0]
+    top_k = [0, 0, 0, 2000, 0, 0]
+    top_p = [0.9, 0.95, 0.9, 0.8, 0.5, 0.99]
+    keys = [row_key(11, r, r) for r in range(R)]
+    s = Sampler(DEV, 8)
+    for trial in range(3):
+        keys = [row_key(11 + trial, r, r) for r in range(R)]
+        got = s.forward(logits.to(DEV), temperature, top_k, top_p, keys).cpu().tolist()
+        want = [S.sample_row(logits[r].numpy(), temperature[r], top_k[r] or None, top_p[r], keys[r]) for r in range(R)]
+        assert got == want
+
+
+def test_sampler_top_k_with_few_and_with_many_tokens_near_the_kth():
+    """top-k gathers the tokens that share the k-th largest's sign and exponent range into shared memory when they are
+    few, and searches the whole row when they are many (a row whose values lie within one factor of two; negative
+    rows; a row of equal values): with and without top-p, against the plain sampler."""
+    from vllm_oxide_b200.sampling import Sampler, row_key
+    g = torch.Generator().manual_seed(5)
+    V = 151936
+    peaked = 2.0 * torch.randn(V, generator=g)
+    narrow = 2.0 + 0.9 * torch.rand(V, generator=g)          # all of the row in one exponent: nothing to gather
+    negative = -3.0 - 0.5 * torch.rand(V, generator=g)
+    equal = torch.full((V,), 1.25)
+    equal[77] = 1.5
+    ties = peaked.clone()
+    ties[torch.randperm(V, generator=g)[:300]] = ties.max() + 1   # 300 equal values at the top, k inside them
+    rows = [peaked, narrow, negative, equal, ties, peaked, narrow, ties]
+    logits = torch.stack(rows).float()
+    R = logits.shape[0]
+    temperature = [1.0, 0.01, 1.0, 1.0, 0.9, 1.5, 0.02, 1.0]
+    top_k = [50, 50, 7, 20, 100, 4000, 5000, 301]
+    top_p = [1.0, 1.0, 0.9, 1.0, 1.0, 0.95, 0.7, 0.5]
+    s = Sampler(DEV, 8)
+    for trial in range(3):
+        keys = [row_key(23 + trial, r, 2 * r) for r in range(R)]
+        got = s.forward(logits.to(DEV), temperature, top_k, top_p, keys).cpu().tolist()
+        want = [S.sample_row(logits[r].numpy(), temperature[r], top_k[r], top_p[r] if top_p[r] < 1 else None, keys[r])
+                for r in range(R)]
+        assert got == want
+
+
 def test_sampler_rows_do_not_depend_on_the_batch_and_follow_the_distribution():
     from vllm_oxide_b200.sampling import Sampler, row_key
     s = Sampler(DEV, 4)

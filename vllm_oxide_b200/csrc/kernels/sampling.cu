@@ -18,6 +18,7 @@
 namespace vob {
 
 constexpr int SAMPLE_THREADS = 1024;
+constexpr int SAMPLE_CANDIDATES = 4096;    // tokens that top-p may still keep after one look at the row, held in shared memory
 
 __device__ __forceinline__ uint32_t ordered_key(float x) {
   const uint32_t b = __float_as_uint(x);
@@ -80,6 +81,11 @@ sample_kernel(const float* logits, long ld, int V, const float* __restrict__ tem
   __shared__ unsigned long long mass[256];
   __shared__ unsigned int s_prefix, s_remaining_k;
   __shared__ unsigned long long s_remaining_mass;
+  __shared__ unsigned int s_ncand, s_short, s_gather;
+  extern __shared__ unsigned long long cand_raw[];              // SAMPLE_CANDIDATES x (mass, key, index)
+  unsigned long long* cand_mass = cand_raw;
+  uint32_t* cand_key = reinterpret_cast<uint32_t*>(cand_raw + SAMPLE_CANDIDATES);
+  uint32_t* cand_idx = cand_key + SAMPLE_CANDIDATES;
   const int row = blockIdx.x, tid = threadIdx.x;
   const float* l = logits + (size_t)row * ld;
   const float temp = temperature[row];
@@ -109,18 +115,30 @@ sample_kernel(const float* logits, long ld, int V, const float* __restrict__ tem
   const float inv_t = 1.0f / temp;
 
   // ---- top-k: key of the k-th largest scaled logit (0 keeps everything)
+  // The first digit (sign and most of the exponent) is found over the whole row.  If the tokens whose first digit is
+  // at least that of the k-th largest are few, they are gathered into shared memory and everything after (the other
+  // three digits, the maximum, top-p, the draw) runs over them alone instead of over the row.
   uint32_t thr = 0;
+  bool gathered = false;
   if (k >= 1 && k < V) {
-    if (tid == 0) { s_prefix = 0; s_remaining_k = (unsigned)k; }
+    if (tid == 0) { s_prefix = 0; s_remaining_k = (unsigned)k; s_gather = 0; }
     for (int pass = 0; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
       if (tid < 256) hist[tid] = 0;
       __syncthreads();
       const uint32_t prefix = s_prefix;
       const uint32_t mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
-      for (int i = tid; i < V; i += SAMPLE_THREADS) {
-        const uint32_t key = ordered_key(l[i] * inv_t);
-        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+      if (gathered) {
+        const unsigned ncand = s_ncand;
+        for (unsigned c = tid; c < ncand; c += SAMPLE_THREADS) {
+          const uint32_t key = cand_key[c];
+          if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        }
+      } else {
+        for (int i = tid; i < V; i += SAMPLE_THREADS) {
+          const uint32_t key = ordered_key(l[i] * inv_t);
+          if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        }
       }
       __syncthreads();
       if (tid == 0) {
@@ -132,17 +150,39 @@ sample_kernel(const float* logits, long ld, int V, const float* __restrict__ tem
         }
         s_remaining_k = need - cum;
         s_prefix = prefix | ((uint32_t)b << shift);
+        if (pass == 0 && cum + hist[b] <= (unsigned)SAMPLE_CANDIDATES) { s_gather = 1; s_ncand = 0; }
       }
       __syncthreads();
+      if (pass == 0 && s_gather) {
+        const uint32_t first = s_prefix >> 24;
+        for (int i = tid; i < V; i += SAMPLE_THREADS) {
+          const uint32_t key = ordered_key(l[i] * inv_t);
+          if ((key >> 24) >= first) {
+            const unsigned pos = atomicAdd(&s_ncand, 1u);
+            cand_key[pos] = key; cand_idx[pos] = (uint32_t)i;
+          }
+        }
+        gathered = true;
+        __syncthreads();
+      }
     }
     thr = s_prefix;
   }
 
   // ---- maximum of the scaled logits (always a survivor)
   unsigned long long best = 0;
-  for (int i = tid; i < V; i += SAMPLE_THREADS) {
-    const unsigned long long c = pack_candidate(l[i] * inv_t, i);
-    best = c > best ? c : best;
+  if (gathered) {
+    const unsigned ncand = s_ncand;
+    for (unsigned c = tid; c < ncand; c += SAMPLE_THREADS) {
+      const int i = (int)cand_idx[c];
+      const unsigned long long cnd = pack_candidate(l[i] * inv_t, i);
+      best = cnd > best ? cnd : best;
+    }
+  } else {
+    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+      const unsigned long long c = pack_candidate(l[i] * inv_t, i);
+      best = c > best ? c : best;
+    }
   }
   best = block_max_u64(best, scratch);
   const int imax = (int)(0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull));
@@ -151,9 +191,18 @@ sample_kernel(const float* logits, long ld, int V, const float* __restrict__ tem
   // ---- top-p over the survivors
   if (p > 0.f && p < 1.f) {
     unsigned long long z = 0;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
-      const float x = l[i] * inv_t;
-      if (ordered_key(x) >= thr) z += fixed_mass(x, maxv);
+    if (gathered) {
+      const unsigned ncand = s_ncand;
+      for (unsigned c = tid; c < ncand; c += SAMPLE_THREADS) {
+        const unsigned long long m = cand_key[c] >= thr ? fixed_mass(l[cand_idx[c]] * inv_t, maxv) : 0ull;
+        cand_mass[c] = m;
+        z += m;
+      }
+    } else {
+      for (int i = tid; i < V; i += SAMPLE_THREADS) {
+        const float x = l[i] * inv_t;
+        if (ordered_key(x) >= thr) z += fixed_mass(x, maxv);
+      }
     }
     // integer sum over the block: any order gives the same total
 #pragma unroll
@@ -170,12 +219,61 @@ sample_kernel(const float* logits, long ld, int V, const float* __restrict__ tem
       s_prefix = 0;
     }
     __syncthreads();
+    // The short way.  A token whose mass is below (1 - p) * total / V cannot lie above the boundary unless it IS the
+    // boundary token (all tokens after it together weigh less than (1 - p) * total), so the tokens at or above that
+    // mass are gathered into shared memory in one pass; if they fit and together reach the target, the boundary is
+    // among them and the search (and later the draw) runs over them alone: a language model's distribution leaves
+    // a few hundred.  Otherwise (a flat distribution) the row is searched as a whole, four more passes.
+    if (tid == 0) { s_short = gathered ? 1u : 0u; if (!gathered) s_ncand = 0; }
+    __syncthreads();
+    if (!gathered) {
+      unsigned long long total = 0;
+      for (int i = 0; i < SAMPLE_THREADS / 32; ++i) total += scratch[i];
+      const unsigned long long floor_mass = (unsigned long long)((1.0 - (double)p) * (double)total / (double)V);
+      if (floor_mass >= 1) {
+        for (int i = tid; i < V; i += SAMPLE_THREADS) {
+          const float x = l[i] * inv_t;
+          const uint32_t key = ordered_key(x);
+          if (key < thr) continue;
+          const unsigned long long m = fixed_mass(x, maxv);
+          if (m < floor_mass) continue;
+          const unsigned pos = atomicAdd(&s_ncand, 1u);
+          if (pos < (unsigned)SAMPLE_CANDIDATES) { cand_mass[pos] = m; cand_key[pos] = key; cand_idx[pos] = (uint32_t)i; }
+        }
+      } else if (tid == 0) {
+        s_ncand = SAMPLE_CANDIDATES + 1;
+      }
+    }
+    __syncthreads();
+    const unsigned ncand = s_ncand;
+    if (!gathered && ncand <= (unsigned)SAMPLE_CANDIDATES) {
+      unsigned long long z2 = 0;
+      for (unsigned i = tid; i < ncand; i += SAMPLE_THREADS) z2 += cand_mass[i];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) z2 += __shfl_xor_sync(0xffffffffu, z2, o);
+      __syncthreads();
+      if ((tid & 31) == 0) scratch[tid >> 5] = z2;
+      __syncthreads();
+      if (tid == 0) {
+        unsigned long long have = 0;
+        for (int i = 0; i < SAMPLE_THREADS / 32; ++i) have += scratch[i];
+        s_short = have >= s_remaining_mass ? 1u : 0u;
+      }
+      __syncthreads();
+    }
+    const bool short_way = s_short != 0;
     for (int pass = 0; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
       if (tid < 256) mass[tid] = 0;
       __syncthreads();
       const uint32_t prefix = s_prefix;
       const uint32_t mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+      if (short_way) {
+        for (unsigned i = tid; i < ncand; i += SAMPLE_THREADS) {
+          const uint32_t key = cand_key[i];
+          if ((key & mask) == prefix) atomicAdd(&mass[(key >> shift) & 255u], cand_mass[i]);
+        }
+      } else
       for (int base = 0; base < V; base += SAMPLE_THREADS) {
         const int i = base + tid;
         const float x = i < V ? l[i] * inv_t : 0.f;
@@ -203,6 +301,19 @@ sample_kernel(const float* logits, long ld, int V, const float* __restrict__ tem
   // ---- Gumbel-max over the survivors
   const unsigned long long key_row = keys[row];
   best = 0;
+  if (gathered || (p > 0.f && p < 1.f && s_short != 0)) {
+    // the survivors are among the gathered tokens
+    const unsigned ncand = s_ncand;
+    for (unsigned c = tid; c < ncand; c += SAMPLE_THREADS) {
+      if (cand_key[c] < thr) continue;
+      const int i = (int)cand_idx[c];
+      const float x = l[i] * inv_t;
+      const float u = counter_uniform(key_row, (uint32_t)i);
+      const float g = -logf(-logf(u));
+      const unsigned long long cnd = pack_candidate(x + g, i);
+      best = cnd > best ? cnd : best;
+    }
+  } else
   for (int i = tid; i < V; i += SAMPLE_THREADS) {
     const float x = l[i] * inv_t;
     if (ordered_key(x) < thr) continue;
@@ -239,7 +350,14 @@ VOB_API int vob_sample(const float* logits, long ld, int R, int V, const float* 
                        const float* top_p, const unsigned long long* keys, int* out, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0) return VOB_BAD_ARGUMENT;
-  sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, keys, out);
+  const int smem = SAMPLE_CANDIDATES * 16;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  sample_kernel<<<R, SAMPLE_THREADS, smem, stream>>>(logits, ld, V, temperature, top_k, top_p, keys, out);
   return launch_status();
 }
 

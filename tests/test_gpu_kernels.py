@@ -600,7 +600,8 @@ def test_gemm_skinny_refuses_what_it_cannot_take():
 
 
 @pytest.mark.parametrize("M,N,K", [(17, 128, 64), (32, 256, 128), (33, 331, 80), (64, 4096, 4096), (100, 517, 200),
-                                   (128, 1000, 1024), (8, 128, 64), (64, 24576 // 8, 512), (48, 130, 12288)])
+                                   (128, 1000, 1024), (8, 128, 64), (64, 24576 // 8, 512), (48, 130, 12288), (40, 24576, 320),
+                                   (128, 8192, 1024), (23, 6144, 4096)])
 def test_gemm_tc5(M, N, K):
     """The tcgen05 product (accumulator in tensor memory) against a float64 product."""
     from vllm_oxide_b200 import kernels
@@ -618,14 +619,15 @@ def test_gemm_tc5(M, N, K):
     outf = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
     kernels.gemm_tc5(x, w, outf, kernels.EPI_F32, err)
     assert torch.equal(outf, out.float()) and err.item() == 0
-    # with and without a split along K, twice in a row (the counters must come back to zero)
-    for ksplit in (1, 2, 3):
+    # split along K over the blocks of a cluster, twice in a row; the choice of the library is one of them
+    assert 1 <= kernels.gemm_tc5_cluster(x, w, kernels.EPI_BF16) <= 8
+    for cluster in (1, 2, 3, 4, 5, 8):
         k_iters = -(-K // 64)
-        if (ksplit - 1) * -(-k_iters // ksplit) >= k_iters:
+        if (cluster - 1) * -(-k_iters // cluster) >= k_iters:
             continue                      # a K range would be empty
         for _ in range(2):
             o2 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-            kernels.gemm_tc5(x, w, o2, kernels.EPI_BF16, err, ksplit=ksplit)
+            kernels.gemm_tc5(x, w, o2, kernels.EPI_BF16, err, cluster=cluster)
             assert torch.allclose(o2.double(), ref, rtol=1e-2, atol=1e-2) and err.item() == 0
 
 
@@ -644,5 +646,5 @@ def test_gemm_tc5_swiglu(M, I, K):
     assert torch.allclose(out.cpu().float(), want.float(), rtol=2e-2, atol=2e-2) and err.item() == 0
     if K >= 128:
         out.fill_(float("nan"))
-        kernels.gemm_tc5(x.to(DEV), wgu.to(DEV), out, kernels.EPI_SWIGLU, err, ksplit=2)
+        kernels.gemm_tc5(x.to(DEV), wgu.to(DEV), out, kernels.EPI_SWIGLU, err, cluster=2)
         assert torch.allclose(out.cpu().float(), want.float(), rtol=2e-2, atol=2e-2) and err.item() == 0

@@ -260,37 +260,16 @@ def gemm_tc5_supported(x, w) -> bool:
             and (w.stride(0) * 2) % 16 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-_tc5_scratch = {}
-
-
-def _tc5_buffers(device, floats: int, counters: int):
-    """Scratch of the split-K product: partial tiles (grown on demand) and counters (zero; the kernel keeps them so)."""
-    part, cnt = _tc5_scratch.get(device, (None, None))
-    if part is None or part.numel() < floats:
-        part = torch.empty(max(floats, 1), dtype=torch.float32, device=device)
-    if cnt is None or cnt.numel() < counters:
-        cnt = torch.zeros(max(counters, 1), dtype=torch.int32, device=device)
-    _tc5_scratch[device] = (part, cnt)
-    return part, cnt
-
-
-def gemm_tc5_scratch(x, w):
-    """(ksplit, floats of partial tiles, counters) the tcgen05 product wants for x @ w^T."""
+def gemm_tc5_cluster(x, w, epilogue: int) -> int:
+    """The number of K ranges (blocks of a thread-block cluster) the tcgen05 product chooses for x @ w^T on this device."""
     L = lib()
-    L.vob_gemm_tc5_scratch_floats.restype = ctypes.c_long
-    L.vob_gemm_tc5_counters.restype = ctypes.c_long
-    N, K = w.shape
-    ksplit = int(L.vob_gemm_tc5_ksplit(ctypes.c_long(N), ctypes.c_long(K)))
-    if ksplit <= 1:
-        return 1, 0, 0
-    return (ksplit, int(L.vob_gemm_tc5_scratch_floats(x.shape[0], ctypes.c_long(N), ksplit)),
-            int(L.vob_gemm_tc5_counters(ctypes.c_long(N))))
+    return int(L.vob_gemm_tc5_cluster(x.shape[0], ctypes.c_long(w.shape[0]), ctypes.c_long(w.shape[1]), epilogue))
 
 
-def gemm_tc5(x, w, out, epilogue: int, err, ksplit: Optional[int] = None, scratch=None) -> None:
+def gemm_tc5(x, w, out, epilogue: int, err, cluster: int = 0) -> None:
     """out = x @ w^T on the tcgen05 tensor cores for at most 128 rows of x; epilogues as gemm_skinny.  The product
-    is split along K where that fills the GPU better (`ksplit` None: chosen by the library); `scratch` is a pair
-    (float partials, zeroed int counters) for a caller that keeps buffers of its own (CUDA graphs)."""
+    is split along K over the blocks of a thread-block cluster where that fills the GPU better (`cluster` 0: chosen
+    by the library; 1 to 8: that many K ranges); the partial tiles meet in shared memory, no scratch is needed."""
     _cuda(x, w, out)
     if not gemm_tc5_supported(x, w):
         raise KernelError("gemm_tc5: this product is not supported (bfloat16, at most 128 rows, K a multiple of 8, "
@@ -301,19 +280,9 @@ def gemm_tc5(x, w, out, epilogue: int, err, ksplit: Optional[int] = None, scratc
     assert out.shape[1] == (N // 2 if epilogue == EPI_SWIGLU else N)
     assert out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16)
     L = lib()
-    L.vob_gemm_tc5_scratch_floats.restype = ctypes.c_long
-    L.vob_gemm_tc5_counters.restype = ctypes.c_long
-    if ksplit is None:
-        ksplit = int(L.vob_gemm_tc5_ksplit(ctypes.c_long(N), ctypes.c_long(K)))
-    part = cnt = None
-    if ksplit > 1:
-        floats = int(L.vob_gemm_tc5_scratch_floats(M, ctypes.c_long(N), ksplit))
-        counters = int(L.vob_gemm_tc5_counters(ctypes.c_long(N)))
-        part, cnt = scratch if scratch is not None else _tc5_buffers(x.device, floats, counters)
-        assert part.numel() >= floats and cnt.numel() >= counters
     map_w = tensor_map_2d(w, 128)
     map_x = tensor_map_2d(x, int(L.vob_gemm_tc5_token_box(M)))
-    _check(L.vob_gemm_tc5(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, ksplit, _p(part), _p(cnt),
+    _check(L.vob_gemm_tc5(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, int(cluster),
                           _p(err), _stream()), "gemm_tc5")
 
 

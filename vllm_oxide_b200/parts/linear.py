@@ -16,24 +16,22 @@ from .. import kernels
 
 
 # Steps of 17 to 128 tokens: this package's tcgen05 product (True) or the library's (False).  Off by default: at batch 64
-# the decode step measures 7.10 ms with the library's product and 8.79 ms with this kernel (Qwen3-8B sizes).
+# the decode step measures 6.79 ms with the library's product and 8.63 ms with this kernel (Qwen3-8B sizes).
 USE_TC5 = False
 # The output matrix is another matter: there the tcgen05 product is as fast as the library's (232 vs 225 us at 64
 # rows) and writes float logits itself, which saves the conversion pass the library's bfloat16 result needs (27 us).
 USE_TC5_LOGITS = True
+# The gate|up product with the activation as its epilogue: 6.92 ms a decode step at batch 64 against 6.80 ms with the
+# library's product followed by the activation kernel, so off as well.
+USE_TC5_SWIGLU = False
 
 
 def tc5_product(x, weight, out, epilogue: int, ctx) -> bool:
     """Runs x @ weight^T on the tcgen05 kernel if it takes the case (17 to 128 tokens); False if it does not."""
-    on = USE_TC5_LOGITS if epilogue == kernels.EPI_F32 else USE_TC5
+    on = USE_TC5_LOGITS if epilogue == kernels.EPI_F32 else (USE_TC5_SWIGLU if epilogue == kernels.EPI_SWIGLU else USE_TC5)
     if not (on and ctx is not None and 16 < x.shape[0] <= 128 and kernels.gemm_tc5_supported(x, weight)):
         return False
-    ksplit, floats, counters = kernels.gemm_tc5_scratch(x, weight)
-    scratch = None
-    if ksplit > 1:
-        scratch = (ctx.ws.get_flat("tc5_partials", floats, torch.float32),
-                   ctx.ws.get_flat("tc5_counters", counters, torch.int32, zero=True))
-    kernels.gemm_tc5(x, weight, out, epilogue, ctx.err, ksplit=ksplit, scratch=scratch)
+    kernels.gemm_tc5(x, weight, out, epilogue, ctx.err)
     return True
 
 

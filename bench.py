@@ -241,7 +241,11 @@ def workload_run(name: str) -> int:
     lo, hi = w["prompt"]
     prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(rng.randint(lo, hi))] for _ in range(w["requests"])]
     sp = SamplingParams(temperature=0.0, max_tokens=w["new"], ignore_eos=True)
-    llm.generate(prompts[:2], [SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)] * 2)     # warm-up: graphs, libraries
+    # warm-up: the same shape of work once with other prompts (libraries, a CUDA graph per batch size met; nothing of the
+    # timed prompts may lie in the prefix cache)
+    wrng = random.Random(1)
+    warm = [[wrng.randrange(cfg["vocab_size"]) for _ in range(len(p))] for p in prompts]
+    llm.generate(warm, [sp] * len(warm))
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     outs = llm.generate(prompts, [sp] * len(prompts))

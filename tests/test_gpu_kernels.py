@@ -378,6 +378,39 @@ def test_attention_prefill_reads_the_right_far_key(key_pos, window, expect_hit, 
     assert (got[0].mean() > 4.9) == expect_hit
 
 
+@pytest.mark.parametrize("kernel", ["tc5x2", "tc5x1"])
+def test_attention_prefill_tc5_many_launches_end_and_repeat(kernel):
+    """Thousands of blocks at the head counts of a large model, launched again and again: no bounded wait runs out (a
+    softmax thread that reaches the end late must not miss the last product's signal) and the result repeats bit for bit."""
+    from vllm_oxide_b200 import kernels
+    nh, kvh, hd, bs = 64, 8, 128, 256
+    q_lens, ctx_lens = [1580, 1615], [1580, 4049]
+    g = torch.Generator().manual_seed(11)
+    pages = [-(-c // bs) for c in ctx_lens]
+    kc = torch.randn(sum(pages) + 1, kvh, bs, hd, generator=g).bfloat16().to(DEV)
+    vc = torch.randn(sum(pages) + 1, kvh, bs, hd, generator=g).bfloat16().to(DEV)
+    bt = torch.full((2, max(pages)), -1, dtype=torch.int32)
+    bt[0, :pages[0]] = torch.arange(1, 1 + pages[0])
+    bt[1, :pages[1]] = torch.arange(1 + pages[0], 1 + pages[0] + pages[1])
+    T = sum(q_lens)
+    q = torch.randn(T, nh * hd, generator=g).bfloat16().to(DEV)
+    cu_q = torch.tensor([0, q_lens[0], T], dtype=torch.int32, device=DEV)
+    ctx = torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)
+    err = err_word()
+    first = None
+    for _ in range(40):
+        out = torch.zeros(T, nh * hd, dtype=torch.bfloat16, device=DEV)
+        kernels.attention_prefill(q, nh * hd, out, kc, vc, bt.to(DEV), cu_q, ctx, 2, max(q_lens), nh, kvh, hd, 0,
+                                  1.0 / math.sqrt(hd), err, **PREFILL_KERNELS[kernel])
+        torch.cuda.synchronize()
+        assert err.item() == 0
+        if first is None:
+            first = out
+            assert torch.isfinite(out.float()).all() and out.float().abs().max() > 0
+        else:
+            assert torch.equal(out, first)
+
+
 def test_attention_decode_and_prefill_share_a_mixed_batch():
     def both(q, out, kc, vc, bt, token_req, positions, cu_q, ctx, T, nh, kvh, hd, window, err, **_):
         out.fill_(777.0)

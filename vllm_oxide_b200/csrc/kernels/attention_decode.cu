@@ -10,6 +10,7 @@
 // normalised partial result and its log-sum-exp to scratch memory, and a second kernel merges the
 // splits.  Requests that bring more than one token are skipped (the prefill kernel takes them).
 // Compiled once per head size (-DVOB_HD).
+#define VOB_TIMEOUT_WHERE 0x400
 #include "attention_mma.cuh"
 
 namespace vob {
@@ -271,7 +272,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         for (int j = first; j < it; ++j) {
           bool done = false;
           for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % DT_STAGES], (unsigned)((j / DT_STAGES) & 1));
-          if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+          if (!done) atomicOr(err, VOB_ERR_TIMEOUT_BITS);
         }
       }
     }

@@ -9,6 +9,7 @@
 // cp.async in 3 stages; each warp masks by its rows' own positions (causal, and the window if any)
 // and runs the online softmax of attention_mma.cuh.  Requests that bring exactly one token are
 // skipped (the decode kernel takes them).  Compiled once per head size (-DVOB_HD).
+#define VOB_TIMEOUT_WHERE 0x800
 #include "attention_mma.cuh"
 
 namespace vob {
@@ -256,7 +257,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
         for (int j = first; j < it; ++j) {
           bool done = false;
           for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % PT_STAGES], (unsigned)((j / PT_STAGES) & 1));
-          if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+          if (!done) atomicOr(err, VOB_ERR_TIMEOUT_BITS);
         }
       }
     }

@@ -14,14 +14,17 @@
 //                      products, the scores of step j+1 into a second S buffer while the softmax of step j runs;
 //                      tcgen05.commit tells the softmax warps that S is complete and that O has been updated, and
 //                      the producer that the tile is done with a stage.  The tiles do not wait for one another.
-// A wait on an mbarrier goes by the parity of the phase, so a waiter must never fall two phases behind: the scores
-// and P have a barrier per buffer (a buffer's next use needs the waiter's own progress), and O's barrier is waited on
-// for every phase or for the last two in turn.
+// A wait on an mbarrier goes by the parity of the phase, so it can tell only two states apart: the scores and P have
+// a barrier per buffer (a buffer's next use needs the waiter's own progress).  O's barrier gets a phase per step; a
+// softmax thread that has to rescale O at step i waits on it for step i - 1, when it can be in two states only (that
+// product pending or done: the next one needs this thread's own P).  At the end it could be in three (the last two
+// products pending, the last one, none), so the end of a tile's last product has a barrier of its own, used once.
 // O stays in tensor memory over all steps.  The running maximum that the exponentials refer to is moved only when a
 // row's new maximum exceeds it by more than 8 (in base-2 units: P stays below 256, exact enough in bfloat16 since
 // its error is relative); only then the row's O is read, scaled and written back, which is rare after the first
 // steps.  Sums, maxima and the scaling are in float.  Every wait on an mbarrier is bounded; a block that gives up
 // sets an error bit, stops issuing work, waits for what is in flight, and frees its tensor memory.
+#define VOB_TIMEOUT_WHERE 0x1000
 #include "attention_mma.cuh"
 #include "tcgen05.cuh"
 
@@ -46,7 +49,7 @@ template <int NQ> struct F5 {
   static constexpr int TILE_COLS = 2 * F5_TILE + HD;       // tensor-memory columns of a query tile: S, S, O
   static constexpr int TMEM_COLS = NQ * TILE_COLS <= 256 ? 256 : 512;
   static constexpr int DATA_BYTES = NQ * F5_Q_BYTES + STAGES * F5_STAGE_BYTES;
-  static constexpr int NUM_BARRIERS = 2 * STAGES + 5 * NQ + 1;
+  static constexpr int NUM_BARRIERS = 2 * STAGES + 6 * NQ + 1;
   static constexpr int SMEM_BYTES = 1024 + DATA_BYTES + NUM_BARRIERS * 8 + 16;
 };
 
@@ -68,7 +71,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   uint64_t* s_full = kv_empty + ST;                         // [NQ][2] scores of a step are complete
   uint64_t* p_full = s_full + 2 * NQ;                       // [NQ][2] P of a step is written (and S read, O rescaled)
   uint64_t* o_done = p_full + 2 * NQ;                       // [NQ] O holds the step's contribution
-  uint64_t* drained = o_done + NQ;                          // every product issued has completed
+  uint64_t* o_final = o_done + NQ;                          // [NQ] O holds the last step's contribution (one phase)
+  uint64_t* drained = o_final + NQ;                         // every product issued has completed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -108,7 +112,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   if (threadIdx.x == 0) {
     for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], NQ); }
     for (int i = 0; i < 2 * NQ; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); }
-    for (int i = 0; i < NQ; ++i) mbar_init(&o_done[i], 1);
+    for (int i = 0; i < NQ; ++i) { mbar_init(&o_done[i], 1); mbar_init(&o_final[i], 1); }
     mbar_init(drained, NQ);
     *abort_flag = 0;
     tma_prefetch_map(&tmK);
@@ -187,7 +191,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       for (int j = first; j < it; ++j) {
         bool done = false;
         for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&kv_full[j % ST], (unsigned)((j / ST) & 1));
-        if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+        if (!done) atomicOr(err, VOB_ERR_TIMEOUT_BITS);
       }
     }
   } else if (warp > 4 * NQ) {
@@ -242,13 +246,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
           t5_mma_a_tmem(o_tmem, s_tmem + (i & 1) * F5_TILE + ks * 8, vd + (uint64_t)((ks * 16 * 128) >> 4), idesc_pv,
                         (i > 0 || ks > 0) ? 1u : 0u);
         t5_commit(&o_done[qt]);
+        if (j + 1 == hi) t5_commit(&o_final[qt]);
         t5_commit(&kv_empty[j % ST]);
       }
       // nothing may still read shared or tensor memory when the block ends
       t5_commit(drained);
       bool done = false;
       for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(drained, 0u);
-      if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+      if (!done) atomicOr(err, VOB_ERR_TIMEOUT_BITS);
     }
   } else {
     // ------------------------------------------------ softmax: a thread owns a row
@@ -343,10 +348,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       if (lane == 0) mbar_arrive(&p_full[qt * 2 + (i & 1)]);
     }
     if (ok && my_hi > my_lo) {
-      // the last two products may both be pending: a wait by parity can tell only the latest phase from the one before
-      const int steps = my_hi - my_lo;
-      if (steps > 1) ok = mbar_wait(&o_done[qt], (unsigned)((steps - 2) & 1), abort_flag, err);
-      if (ok) ok = mbar_wait(&o_done[qt], (unsigned)((steps - 1) & 1), abort_flag, err);
+      ok = mbar_wait(&o_final[qt], 0u, abort_flag, err);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         t5_fence_after();

@@ -18,6 +18,7 @@
 //
 // Every wait on an mbarrier is bounded: a wait that runs out sets an error bit and a block-wide
 // abort flag; the block then waits (bounded again) for the copies it still has in flight and returns.
+#define VOB_TIMEOUT_WHERE 0x100
 #include "tensor_map.cuh"
 
 
@@ -113,7 +114,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       for (long j = first; j < it; ++j) {
         bool done = false;
         for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % S], (unsigned)((j / S) & 1));
-        if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+        if (!done) atomicOr(err, VOB_ERR_TIMEOUT_BITS);
       }
     }
   } else {

@@ -24,6 +24,7 @@
 // interleaved gate/up rows.  Every wait on an mbarrier is bounded; on a timeout the block sets an error bit,
 // stops issuing work, and still frees its TMEM before it returns; the blocks of a cluster leave together, so
 // none is signalled after it has gone.
+#define VOB_TIMEOUT_WHERE 0x200
 #include "tcgen05.cuh"
 
 namespace vob {
@@ -74,7 +75,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, unsigned parity
     if (*abort_flag) return false;
   }
   *abort_flag = 1;
-  atomicOr(err, VOB_ERR_TIMEOUT);
+  atomicOr(err, VOB_ERR_TIMEOUT_BITS);
   return false;
 }
 __device__ __forceinline__ void cluster_sync_all() {
@@ -161,7 +162,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       for (long j = first; j < p_it; ++j) {
         bool done = false;
         for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % S], (unsigned)((j / S) & 1));
-        if (!done) atomicOr(err, VOB_ERR_TIMEOUT);
+        if (!done) atomicOr(err, VOB_ERR_TIMEOUT_BITS);
       }
     }
   } else if (warp == 1) {

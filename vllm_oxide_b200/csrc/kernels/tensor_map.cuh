@@ -16,6 +16,17 @@
 namespace vob {
 
 #define VOB_ERR_TIMEOUT 32
+// A kernel whose bounded wait runs out also says which kernel it is: its source file defines VOB_TIMEOUT_WHERE
+// (one of the bits below) before it includes this header.
+#define VOB_WHERE_GEMM_SKINNY 0x100
+#define VOB_WHERE_GEMM_TC5 0x200
+#define VOB_WHERE_ATTENTION_DECODE 0x400
+#define VOB_WHERE_ATTENTION_PREFILL 0x800
+#define VOB_WHERE_ATTENTION_PREFILL_TC5 0x1000
+#ifndef VOB_TIMEOUT_WHERE
+#define VOB_TIMEOUT_WHERE 0
+#endif
+#define VOB_ERR_TIMEOUT_BITS (VOB_ERR_TIMEOUT | VOB_TIMEOUT_WHERE)
 
 constexpr unsigned MBAR_SPIN_LIMIT = 1u << 22;   // tries before a wait on an mbarrier gives up
 
@@ -43,7 +54,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volati
     if (*abort_flag) return false;
   }
   *abort_flag = 1;
-  atomicOr(err, VOB_ERR_TIMEOUT);
+  atomicOr(err, VOB_ERR_TIMEOUT_BITS);
   return false;
 }
 

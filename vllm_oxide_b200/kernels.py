@@ -24,7 +24,9 @@ DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1}
 
 ERR_BITS = {1: "a token id outside the vocabulary", 2: "a position beyond max_position_embeddings",
             4: "a cache slot outside the pool", 8: "a block-table entry that names no page",
-            16: "a wanted row outside the batch", 32: "a bounded wait inside a kernel ran out"}
+            16: "a wanted row outside the batch", 32: "a bounded wait inside a kernel ran out",
+            0x100: "(in the weight-streaming product)", 0x200: "(in the tcgen05 product)", 0x400: "(in decode attention)",
+            0x800: "(in the attention for portions, mma.sync)", 0x1000: "(in the attention for portions, tcgen05)"}
 
 
 def lib():

@@ -119,3 +119,27 @@ def test_decode_from_graphs_agrees_with_decode_launched_kernel_by_kernel():
     # bfloat16 itself is away from the 32-bit path; a kernel that read stale data was 0.04 to 0.08 away
     assert err.pow(2).mean().sqrt() < 8e-3 * scale, err.pow(2).mean().sqrt() / scale
     assert err.abs().max() < 6e-2 * scale, err.abs().max() / scale
+
+
+@pytest.mark.parametrize("name", list(SIZES))
+def test_a_mixed_workload_at_real_head_counts_repeats_bit_for_bit(name):
+    """Many requests of mixed lengths and sampling settings, so few pages that some are preempted and recomputed, at the
+    head counts of real checkpoints (thousands of attention blocks a step): no kernel gives up a wait, and the second
+    run of the same work gives the same tokens (the prefix cache is off, so it is the same work)."""
+    import random
+    from vllm_oxide_b200 import LLM, EngineOptions, SamplingParams
+    cfg = dict(architectures=["Qwen3ForCausalLM"], vocab_size=2048, rope_theta=1e6, rms_norm_eps=1e-6,
+               max_position_embeddings=4096, tie_word_embeddings=False, hidden_act="silu", torch_dtype="bfloat16",
+               **SIZES[name])
+    opts = EngineOptions(dtype="bfloat16", max_model_len=2048 + 64, block_size=256, max_num_seqs=24,
+                         max_num_batched_tokens=2048, num_kv_blocks=70, enable_prefix_caching=False)
+    llm = LLM.from_config(cfg, opts, seed=5)
+    rng = random.Random(7)
+    prompts = [[rng.randrange(2048) for _ in range(rng.randint(2, 2048))] for _ in range(32)]
+    params = [SamplingParams(temperature=0.0 if i % 3 else 0.8, top_k=None if i % 2 else 40, top_p=None if i % 4 else 0.9,
+                             seed=i, max_tokens=rng.randint(1, 48), ignore_eos=True) for i in range(32)]
+    first = [o.token_ids for o in llm.generate(prompts, params)]
+    assert llm.last_stats.preemptions > 0
+    assert all(len(t) == p.max_tokens for t, p in zip(first, params))
+    again = [o.token_ids for o in llm.generate(prompts, params)]
+    assert again == first

@@ -16,13 +16,14 @@ SIZES = {
 }
 
 
-def engines(sizes, seed):
+def engines(sizes, seed, max_len=2048, pages=12, budget=512):
     from vllm_oxide_b200 import LLM, EngineOptions
     from vllm_oxide_b200.engine.loading import resolve
     from vllm_oxide_b200.models.causal_lm import CausalLM
     from vllm_oxide_b200.weights.random_init import random_weights
     cfg = dict(architectures=["Qwen3ForCausalLM"], vocab_size=2048, rope_theta=1e6, rms_norm_eps=1e-6,
-               max_position_embeddings=4096, tie_word_embeddings=False, hidden_act="silu", torch_dtype="bfloat16", **sizes)
+               max_position_embeddings=max(4096, max_len), tie_word_embeddings=False, hidden_act="silu", torch_dtype="bfloat16",
+               **sizes)
     config, plan = resolve(cfg, where="config")
     half = CausalLM(plan, torch.bfloat16, "cuda:0")
     weights = random_weights(half.tensor_specs(), seed, "fan_in", "cuda:0", torch.bfloat16)
@@ -32,8 +33,8 @@ def engines(sizes, seed):
     del weights
     out = []
     for model, dtype in ((half, "bfloat16"), (full, "float32")):
-        opts = EngineOptions(max_model_len=2048, block_size=256, num_kv_blocks=12, max_num_seqs=2,
-                             max_num_batched_tokens=512, dtype=dtype)          # a 700-token prompt goes in two portions
+        opts = EngineOptions(max_model_len=max_len, block_size=256, num_kv_blocks=pages, max_num_seqs=2,
+                             max_num_batched_tokens=budget, dtype=dtype)        # a 700-token prompt goes in two portions
         out.append(LLM("<random weights>", opts, device="cuda:0", _model=(config, model)))
     return out
 
@@ -68,6 +69,23 @@ def test_real_layer_sizes_agree_with_the_32_bit_path(name):
     err = (got - want)
     # bfloat16 rounds to 2^-9 relative at some fifteen places a layer: the logits (of unit scale here) come out within
     # half a percent rms of the 32-bit path (measured 0.0055 and 0.0043); a structural fault gives errors of order one
+    assert err.pow(2).mean().sqrt() < 0.01 * scale, (err.pow(2).mean().sqrt() / scale)
+    assert err.abs().max() < 0.05 * scale, (err.abs().max() / scale)
+    assert got.argmax(dim=-1).tolist() == tokens
+
+
+def test_a_long_context_agrees_with_the_32_bit_path():
+    """One request of 8,300 tokens: decode attention splits its keys over more blocks than a cluster holds (a second
+    kernel merges them), the prompt goes in portions over 33 pages.  Greedy tokens and logits against the 32-bit path."""
+    half, full = engines(SIZES["8b"], seed=13, max_len=8448, pages=36, budget=2048)
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, 2048, (8300,), generator=g).tolist()
+    want = torch.from_numpy(full.generate_logits(prompt, 3)).double()
+    tokens = want.argmax(dim=-1).tolist()
+    got = torch.from_numpy(half.generate_logits(prompt, 3)).double()
+    assert half.core.graph_replays > 0
+    scale = want.pow(2).mean().sqrt()
+    err = got - want
     assert err.pow(2).mean().sqrt() < 0.01 * scale, (err.pow(2).mean().sqrt() / scale)
     assert err.abs().max() < 0.05 * scale, (err.abs().max() / scale)
     assert got.argmax(dim=-1).tolist() == tokens

@@ -411,6 +411,66 @@ def test_attention_prefill_tc5_many_launches_end_and_repeat(kernel):
             assert torch.equal(out, first)
 
 
+def test_attention_kernels_agree_with_the_plain_kernel_on_random_batches():
+    """Eighty random batches (head counts, groups up to 16, page sizes, windows, pages scattered over the pool, decoding
+    requests beside portions): every tensor-core kernel for portions and the decode kernel at several split counts
+    against the plain kernel (which the tests above hold to the plain implementation); each writes its own rows only."""
+    import random
+    from vllm_oxide_b200 import kernels
+    rng = random.Random(4)
+    for case in range(80):
+        hd, kvh = rng.choice([64, 128]), rng.choice([1, 2, 3, 4, 8])
+        nh = kvh * rng.choice([1, 2, 3, 4, 8, 16])
+        bs = rng.choice([16, 32, 64, 128, 256])
+        window = rng.choice([0, 0, 0, rng.randint(1, 300)])
+        B = rng.randint(1, 5)
+        ctx_lens = [rng.choice([rng.randint(1, 70), rng.randint(1, 700), rng.randint(1, 3000)]) for _ in range(B)]
+        q_lens = [1 if (k := rng.random()) < 0.3 else (c if k < 0.6 else rng.randint(1, c)) for c in ctx_lens]
+        g = torch.Generator().manual_seed(case)
+        pages = [-(-c // bs) for c in ctx_lens]
+        total = sum(pages) + 2
+        order = torch.randperm(total - 1, generator=g) + 1
+        kc = torch.randn(total, kvh, bs, hd, generator=g).bfloat16().to(DEV)
+        vc = torch.randn(total, kvh, bs, hd, generator=g).bfloat16().to(DEV)
+        bt = torch.full((B, max(pages)), -1, dtype=torch.int32)
+        at = 0
+        for b in range(B):
+            bt[b, :pages[b]] = order[at:at + pages[b]].int()
+            at += pages[b]
+        bt = bt.to(DEV)
+        T = sum(q_lens)
+        q = (torch.randn(T, nh * hd, generator=g) * rng.choice([0.3, 1.0, 3.0])).bfloat16().to(DEV)
+        cu = [0] + list(np.cumsum(q_lens))
+        token_req = torch.tensor([b for b, n in enumerate(q_lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+        positions = torch.tensor([c - n + i for n, c in zip(q_lens, ctx_lens) for i in range(n)], dtype=torch.int32, device=DEV)
+        cu_q = torch.tensor(cu, dtype=torch.int32, device=DEV)
+        ctx = torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)
+        scale = 1.0 / math.sqrt(hd)
+        err = err_word()
+        want = torch.zeros(T, nh * hd, dtype=torch.bfloat16, device=DEV)
+        kernels.paged_attention_generic(q, nh * hd, want, kc, vc, bt, token_req, positions, T, nh, kvh, hd, window, scale, err)
+        single = torch.tensor([cu[b] for b in range(B) if q_lens[b] == 1], dtype=torch.long, device=DEV)
+        portion = torch.tensor([t for b in range(B) if q_lens[b] > 1 for t in range(cu[b], cu[b + 1])], dtype=torch.long, device=DEV)
+        what = f"case {case}: nh={nh} kvh={kvh} hd={hd} page={bs} window={window} q={q_lens} ctx={ctx_lens}"
+        runs = []
+        if len(portion):
+            runs += [(name, portion, single, lambda out, kw=kw: kernels.attention_prefill(
+                q, nh * hd, out, kc, vc, bt, cu_q, ctx, B, max(q_lens), nh, kvh, hd, window, scale, err, **kw))
+                for name, kw in PREFILL_KERNELS.items()]
+        if len(single):
+            for splits in sorted({1, 2, rng.randint(3, 8), rng.randint(9, 20)}):
+                n = kernels.attention_decode_scratch_floats(hd, B, nh, splits)
+                scratch = torch.empty(max(n, 1), device=DEV) if n else None
+                runs.append((f"decode with {splits} splits", single, portion, lambda out, s=splits, sc=scratch: kernels.attention_decode(
+                    q, nh * hd, out, kc, vc, bt, cu_q, ctx, B, nh, kvh, hd, window, scale, s, sc, err)))
+        for name, mine, others, launch in runs:
+            out = torch.full((T, nh * hd), 777.0, dtype=torch.bfloat16, device=DEV)
+            launch(out)
+            assert err.item() == 0, (name, what)
+            assert (out[mine].float() - want[mine].float()).abs().max() < 4e-2, (name, what)
+            assert len(others) == 0 or (out[others] == 777).all(), (name, what)
+
+
 def test_attention_decode_and_prefill_share_a_mixed_batch():
     def both(q, out, kc, vc, bt, token_req, positions, cu_q, ctx, T, nh, kvh, hd, window, err, **_):
         out.fill_(777.0)

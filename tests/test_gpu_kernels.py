@@ -692,6 +692,23 @@ def test_gemm_skinny_refuses_what_it_cannot_take():
         kernels.gemm_skinny(x, w, torch.zeros(17, 8, dtype=torch.bfloat16, device=DEV), kernels.EPI_BF16, err_word())
 
 
+@pytest.mark.parametrize("M,N,K", [(14, 17464, 1536), (16, 17472, 1024), (5, 20000, 1280)])
+def test_gemm_skinny_a_fast_refill_does_not_overtake_the_readers(M, N, K):
+    """A matrix that stays in L2 and gives blocks two tiles each: the copy engine refills a stage of the ring as soon as
+    it is released, and must not overwrite what a warp is still reading (one launch in three was wrong before the
+    release was preceded by a proxy fence).  Thirty launches, each against a float64 product."""
+    from vllm_oxide_b200 import kernels
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().to(DEV)
+    ref = x.double() @ w.double().t()
+    err = err_word()
+    for _ in range(30):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_skinny(x, w, out, kernels.EPI_BF16, err)
+        assert torch.allclose(out.double(), ref, rtol=1e-2, atol=2e-2) and err.item() == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(17, 128, 64), (32, 256, 128), (33, 331, 80), (64, 4096, 4096), (100, 517, 200),
                                    (128, 1000, 1024), (8, 128, 64), (64, 24576 // 8, 512), (48, 130, 12288), (40, 24576, 320),
                                    (128, 8192, 1024), (23, 6144, 4096)])

@@ -315,6 +315,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         }
         softmax_pv_16keys_swizzled<DEC_TILE>(st, sv, kt + DT_TILE_BYTES, warp * 16, lane);
       }
+      // ordinary loads of the stage before the copy engine's next write to it: a proxy fence, then the release
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
     }

@@ -390,6 +390,8 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
         }
       }
     }
+    // ordinary loads of the stage before the copy engine's next write to it: a proxy fence, then the release
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[s]);
   }

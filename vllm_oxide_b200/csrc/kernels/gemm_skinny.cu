@@ -159,6 +159,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             if (MT == 16) sk_mma(acc[i][NT - 1], a, b[2], b[3]);
           }
         }
+        // The stage goes back to the copy engine.  What this warp read of it with ordinary loads (ldmatrix) is ordered
+        // before the engine's next write only across a proxy fence: without it a refill that came fast (the matrix in
+        // L2, a block with several tiles) overwrote a stage that was still being read.
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
       }

@@ -148,6 +148,48 @@ def test_qk_norm_rope_kv_write(dtype, nh, kvh, hd, norm, bias):
     assert err.item() & 4
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,kvh,hd,T", [(32, 8, 128, 300), (16, 8, 64, 257), (3, 1, 32, 300), (6, 2, 48, 300), (8, 1, 80, 256),
+                                         (2, 2, 256, 260), (5, 5, 16, 300), (7, 1, 128, 3), (9, 3, 64, 1), (4, 2, 96, 40),
+                                         (2, 1, 512, 5), (3, 3, 144, 270)])
+def test_qk_norm_rope_kv_write_many_tokens_and_head_sizes(dtype, nh, kvh, hd, T):
+    """The rotation kernel picks its shape by head size and token count (16-byte accesses for head sizes that are a power
+    of two, four heads a warp from 256 tokens on): each against the plain formulas, with norm and bias together."""
+    from vllm_oxide_b200 import kernels
+    bs, eps, max_pos, theta = 32, 1e-5, 700, 1e6
+    pages = -(-T // bs) + 2
+    g = torch.Generator().manual_seed(T + hd)
+    width = (nh + 2 * kvh) * hd
+    qkv = torch.randn(T, width, generator=g).to(dtype).to(DEV)
+    b = (0.1 * torch.randn(width, generator=g)).to(dtype).to(DEV)
+    wq = (1 + 0.1 * torch.randn(hd, generator=g)).to(dtype).float().to(DEV)
+    wk = (1 + 0.1 * torch.randn(hd, generator=g)).to(dtype).float().to(DEV)
+    pos = torch.randint(0, max_pos, (T,), generator=g).int().to(DEV)
+    slots = torch.randperm(pages * bs, generator=g)[:T].int()
+    slots[T // 2] = -1                                              # a token whose key goes nowhere
+    slots = slots.to(DEV)
+    table = P.rope_table(hd, max_pos, theta)
+    kc = torch.full((pages, kvh, bs, hd), 7.0, device=DEV).to(dtype)
+    vc = torch.full((pages, kvh, bs, hd), 7.0, device=DEV).to(dtype)
+    out = qkv.clone()
+    err = err_word()
+    kernels.qk_norm_rope_kv_write(out, b, pos, slots, wq, wk, table.to(DEV), kc, vc, T, nh, kvh, hd, eps, True, err)
+    assert err.item() == 0
+    q, k, v = P.split_qkv(qkv.cpu() + b.cpu(), nh, kvh, hd)
+    q = P.apply_rope(P.head_rms_norm(q, wq.cpu().to(dtype), eps, dtype), pos.cpu(), table, dtype)
+    k = P.apply_rope(P.head_rms_norm(k, wk.cpu().to(dtype), eps, dtype), pos.cpu(), table, dtype)
+    assert torch.allclose(out[:, :nh * hd].reshape(T, nh, hd).cpu().float(), q.float(), **tol(dtype))
+    kflat = kc.permute(0, 2, 1, 3).reshape(pages * bs, kvh, hd).cpu()
+    vflat = vc.permute(0, 2, 1, 3).reshape(pages * bs, kvh, hd).cpu()
+    keep = slots.cpu() >= 0
+    idx = slots.cpu()[keep].long()
+    assert torch.allclose(kflat[idx].float(), k[keep].float(), **tol(dtype))
+    assert torch.equal(vflat[idx], v[keep].to(dtype))
+    untouched = torch.ones(pages * bs, dtype=torch.bool)
+    untouched[idx] = False
+    assert (kflat[untouched] == 7).all() and (vflat[untouched] == 7).all()
+
+
 def paged_setup(dtype, kvh, hd, bs, ctx_lens, g):
     """Random keys/values for requests of the given context lengths, scattered over shuffled pages."""
     B = len(ctx_lens)

@@ -647,6 +647,22 @@ def test_sampler_top_k_with_few_and_with_many_tokens_near_the_kth():
         assert got == want
 
 
+def test_sampler_takes_minus_zero_for_zero():
+    """-0.0 and 0.0 are one value: among equal maxima the lowest index wins whatever the signs of the zeros, and top-p
+    cuts by value (rows of rounded logits against the plain sampler)."""
+    from vllm_oxide_b200.sampling import Sampler, row_key
+    s = Sampler(DEV, 4)
+    x = torch.full((1, 50), -3.0)
+    x[0, 7], x[0, 3] = 0.0, -0.0
+    assert s.forward(x.to(DEV), [0.0], [0], [1.0], [row_key(1, 0, 0)]).item() == 3
+    g = torch.Generator().manual_seed(131)
+    rows = torch.round(2 * torch.randn(6, 4097, generator=g)).float()
+    assert (rows == 0).any() and torch.signbit(rows[rows == 0]).any()
+    keys = [row_key(5, r, r) for r in range(6)]
+    got = s.forward(rows.to(DEV), [1.7] * 6, [0] * 6, [0.5] * 6, keys).cpu().tolist()
+    assert got == [S.sample_row(rows[r].numpy(), 1.7, None, 0.5, keys[r]) for r in range(6)]
+
+
 def test_sampler_rows_do_not_depend_on_the_batch_and_follow_the_distribution():
     from vllm_oxide_b200.sampling import Sampler, row_key
     s = Sampler(DEV, 4)

@@ -21,7 +21,7 @@ constexpr int SAMPLE_THREADS = 1024;
 constexpr int SAMPLE_CANDIDATES = 4096;    // tokens that top-p may still keep after one look at the row, held in shared memory
 
 __device__ __forceinline__ uint32_t ordered_key(float x) {
-  const uint32_t b = __float_as_uint(x);
+  const uint32_t b = __float_as_uint(x + 0.f);      // -0 becomes +0: equal values get equal keys
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 

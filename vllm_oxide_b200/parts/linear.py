@@ -14,6 +14,12 @@ import torch
 
 from .. import kernels
 
+# The library's bfloat16 products may add the partial sums of a split along K in bfloat16 (torch's default allows it).
+# A sum rounded to 8 bits at every partial is not the float accumulation the rest of the engine keeps: on a step of
+# 6 tokens a logit of a tiny model came out 2.6 off where the plain bfloat16 implementation is 0.6 off.  Off, for
+# every product this process runs.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
 
 # Steps of 17 to 128 tokens: this package's tcgen05 product (True) or the library's (False).  Off by default: at batch 64
 # the decode step measures 6.79 ms with the library's product and 8.63 ms with this kernel (Qwen3-8B sizes).

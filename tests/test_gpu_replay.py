@@ -238,3 +238,63 @@ def test_running_out_of_pages_is_an_error_not_a_wrong_result(model_folders):
     r.step([dict(id="a", tokens=list(range(30)), want=[])], [])
     with pytest.raises(RuntimeError, match="no pages left"):
         r.step([dict(id="b", tokens=list(range(10)), want=[])], [])
+
+
+def test_random_configurations_and_cuts(tmp_path):
+    """Thirty configurations drawn at random (layers, widths and vocabularies that are no multiple of anything, head
+    counts and groups, windows, eps, tied or not, page sizes; 64- and 128-wide heads in bfloat16, seven head sizes in
+    32-bit), three requests each, cut at random into portions and single tokens that share steps: every position
+    against the plain implementation."""
+    from conftest import _cfg
+    from vllm_oxide_b200.engine.loading import write_random_model_folder
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    rng = random.Random(12)
+    for case in range(30):
+        dtype = rng.choice(DTYPES)
+        hd = rng.choice([64, 128]) if dtype == "bfloat16" else rng.choice([16, 32, 48, 64, 80, 128, 144])
+        kvh = rng.choice([1, 2, 3, 4])
+        group = rng.choice([1, 2, 3, 4, 8] if hd <= 64 else [1, 2, 4])
+        layers = rng.randint(1, 3)
+        window = rng.choice([None, None, rng.randint(3, 70)])
+        cfg = _cfg(num_hidden_layers=layers, hidden_size=rng.choice([8 * rng.randint(2, 40), 64 * rng.randint(1, 5), rng.randint(10, 300)]),
+                   num_attention_heads=kvh * group, num_key_value_heads=kvh, head_dim=hd,
+                   intermediate_size=rng.choice([8 * rng.randint(2, 60), 64 * rng.randint(1, 6), rng.randint(10, 500)]),
+                   vocab_size=rng.randint(20, 1200), rope_theta=rng.choice([1e4, 5e5, 1e6]),
+                   rms_norm_eps=rng.choice([1e-6, 1e-5, 3e-4]), max_position_embeddings=512,
+                   tie_word_embeddings=rng.random() < 0.5)
+        if window:
+            cfg.update(use_sliding_window=True, sliding_window=window, max_window_layers=rng.randint(0, layers))
+        bs = rng.choice([16, 32, 64])
+        folder = str(tmp_path / f"case{case}")
+        os.makedirs(folder)
+        write_random_model_folder(folder, cfg, case, "fan_in", torch.float32)
+        plain_cfg, weights = P.read_folder(folder)
+        lengths = [rng.randint(1, 160) for _ in range(3)]
+        g = torch.Generator().manual_seed(case)
+        reqs = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lengths]
+        pool = sum((n + bs - 1) // bs * bs for n in lengths)
+        r = TraceRunner(folder, dtype, pool, bs)
+        pos, got = [0, 0, 0], [[], [], []]
+        while any(p < n for p, n in zip(pos, lengths)):
+            entries, ended = [], []
+            for i in range(3):
+                if pos[i] >= lengths[i] or rng.random() < 0.25:
+                    continue                          # this request sits the step out
+                m = min(rng.choice([1, 1, 2, 3, 17, bs, bs + 1, 40]), lengths[i] - pos[i])
+                entries.append(dict(id=f"r{i}", tokens=reqs[i][pos[i]:pos[i] + m], want=list(range(m))))
+                pos[i] += m
+                if pos[i] >= lengths[i]:
+                    ended.append(f"r{i}")
+            if not entries:
+                continue
+            out, at = r.step(entries, ended), 0
+            for e in entries:
+                got[int(e["id"][1:])].append(out[at:at + len(e["tokens"])])
+                at += len(e["tokens"])
+        what = f"case {case}: {dtype}, pages of {bs}, {cfg}"
+        for i, toks in enumerate(reqs):
+            truth = P.forward_logits(plain_cfg, weights, toks, torch.float64).numpy()
+            want = truth if dtype == "float32" else Both(truth, P.forward_logits(plain_cfg, weights, toks, torch.bfloat16).double().numpy())
+            check(np.concatenate(got[i]), want, dtype, f"{what}, request of {len(toks)}")
+        assert r.manager.check_invariants() == "", what
+        assert all(r.manager.num_free_blocks(grp) == pool // bs for grp in range(r.manager.num_groups)), what

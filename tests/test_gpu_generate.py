@@ -169,3 +169,17 @@ def test_the_same_work_twice_gives_the_same_tokens_bit_for_bit(model_folders):
     assert llm.core.graph_replays > 0
     llm.generate(prompts[:2], sps[:2])                 # other work in between: the free list is in another order now
     assert [o.token_ids for o in llm.generate(prompts, sps)] == first
+
+
+def test_a_decode_graph_padded_beyond_the_step_limits(model_folders):
+    """Five requests with max_num_seqs 5 and a budget of 6 tokens decode from the graph for 8 requests: a layout larger
+    than any step the limits allow (the staging buffers must hold it), with the same tokens as without graphs."""
+    from vllm_oxide_b200 import SamplingParams
+    name = "D"
+    prompts = [tokens_for(name, n, salt=700 + i) for i, n in enumerate([3, 9, 2, 11, 5])]
+    sp = [SamplingParams(max_tokens=12, ignore_eos=True)] * len(prompts)
+    eager = make_llm(model_folders, name, max_num_seqs=5, max_num_batched_tokens=6, enforce_eager=True)
+    want = [o.token_ids for o in eager.generate(prompts, sp)]
+    llm = make_llm(model_folders, name, max_num_seqs=5, max_num_batched_tokens=6)
+    assert [o.token_ids for o in llm.generate(prompts, sp)] == want
+    assert llm.core.graph_replays > 0 and 8 in llm.core._graphs

@@ -79,6 +79,10 @@ class EngineCore:
         self.num_groups = len(cache.groups)
         self.max_pages = (max_model_len + cache.block_size - 1) // cache.block_size
         cap = host.BatchLayout(self.max_tokens, self.max_seqs, self.max_tokens, self.num_groups, self.max_pages).total
+        # a decode step replayed from a graph is padded to the next batch size that has one, which may be more
+        # requests (and tokens) than a step may hold: the staging buffers take that layout too
+        padded = next((b for b in GRAPH_BUCKETS if b >= self.max_seqs), GRAPH_BUCKETS[-1])
+        cap = max(cap, host.BatchLayout(padded, padded, padded, self.num_groups, self.max_pages).total)
         self._host_buf = torch.empty(cap, dtype=torch.int32, pin_memory=torch.device(self.device).type == "cuda")
         self._host_np = self._host_buf.numpy()
         self._dev_buf = torch.empty(cap, dtype=torch.int32, device=self.device)

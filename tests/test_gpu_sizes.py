@@ -16,7 +16,7 @@ SIZES = {
 }
 
 
-def engines(sizes, seed, max_len=2048, pages=12, budget=512):
+def engines(sizes, seed, max_len=2048, pages=12, budget=512, seqs=2):
     from vllm_oxide_b200 import LLM, EngineOptions
     from vllm_oxide_b200.engine.loading import resolve
     from vllm_oxide_b200.models.causal_lm import CausalLM
@@ -33,7 +33,7 @@ def engines(sizes, seed, max_len=2048, pages=12, budget=512):
     del weights
     out = []
     for model, dtype in ((half, "bfloat16"), (full, "float32")):
-        opts = EngineOptions(max_model_len=max_len, block_size=256, num_kv_blocks=pages, max_num_seqs=2,
+        opts = EngineOptions(max_model_len=max_len, block_size=256, num_kv_blocks=pages, max_num_seqs=seqs,
                              max_num_batched_tokens=budget, dtype=dtype)        # a 700-token prompt goes in two portions
         out.append(LLM("<random weights>", opts, device="cuda:0", _model=(config, model)))
     return out

@@ -206,7 +206,7 @@ class LLM:
         buf[:n].copy_(toks, non_blocking=True)
         buf[n:n + 1].copy_(self.core.err, non_blocking=True)
         if torch.device(self.core.device).type == "cuda":
-            torch.cuda.current_stream().synchronize()
+            torch.cuda.current_stream(torch.cuda.current_device()).synchronize()
         vals = buf[:n + 1].tolist()
         self.core.raise_for(vals[n])
         return vals[:n]

@@ -737,6 +737,39 @@ def test_gemm_skinny_swiglu(M, I, K):
     assert torch.allclose(out.cpu().float(), want.float(), rtol=2e-2, atol=2e-2) and err.item() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 6144, 4096), (5, 331, 320), (13, 4096, 1024), (16, 520, 192), (3, 9472, 768)])
+def test_gemm_skinny_with_the_norm_in_front_and_the_residual_behind(M, N, K):
+    """The residual stream kept inside the products: RMSNorm of the tokens applied on the way (plain: norm, then the
+    product of the rounded result), and the product added to its output in place."""
+    from vllm_oxide_b200 import kernels
+    g = torch.Generator().manual_seed(M * 7 + N)
+    eps = 1e-5
+    x = (3 * torch.randn(M, K, generator=g)).bfloat16()
+    wn = (1 + 0.2 * torch.randn(K, generator=g)).bfloat16()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16()
+    normed, _ = P.add_rms_norm(x, None, wn, eps, torch.bfloat16)
+    want = P.linear(normed, w, torch.bfloat16)
+    err = err_word()
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_skinny(x.to(DEV), w.to(DEV), out, kernels.EPI_BF16, err, norm_weight=wn.float().to(DEV), eps=eps)
+    assert torch.allclose(out.cpu().float(), want.float(), rtol=2e-2, atol=2e-2) and err.item() == 0
+    # the same product without the norm, added to what is there
+    before = torch.randn(M, N, generator=g).bfloat16()
+    acc = before.clone().to(DEV)
+    kernels.gemm_skinny(x.to(DEV), w.to(DEV), acc, kernels.EPI_ADD, err)
+    plain = (P.linear(x, w, torch.bfloat16).float() + before.float()).bfloat16()
+    assert torch.allclose(acc.cpu().float(), plain.float(), rtol=2e-2, atol=2e-2) and err.item() == 0
+    # norm in front of the fused activation
+    if N % 16 == 0:
+        I = N // 2
+        wg, wu = w[:I], w[I:]
+        want_act = P.swiglu(normed, wg, wu, torch.eye(I).bfloat16(), torch.bfloat16)
+        wgu = torch.stack([wg.reshape(I // 8, 8, K), wu.reshape(I // 8, 8, K)], dim=1).reshape(N, K)
+        act = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_skinny(x.to(DEV), wgu.to(DEV), act, kernels.EPI_SWIGLU, err, norm_weight=wn.float().to(DEV), eps=eps)
+        assert torch.allclose(act.cpu().float(), want_act.float(), rtol=3e-2, atol=3e-2) and err.item() == 0
+
+
 def test_gemm_skinny_refuses_what_it_cannot_take():
     from vllm_oxide_b200 import kernels
     x = torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV)

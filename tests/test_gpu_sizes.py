@@ -161,3 +161,53 @@ def test_a_mixed_workload_at_real_head_counts_repeats_bit_for_bit(name):
     assert all(len(t) == p.max_tokens for t, p in zip(first, params))
     again = [o.token_ids for o in llm.generate(prompts, params)]
     assert again == first
+
+
+def test_the_residual_stream_inside_the_products_agrees_with_the_separate_norm_kernels():
+    """Decode steps of up to 8 tokens run two kernels less a layer: the norm inside the product that follows it, the
+    residual sum made by the product before it.  Same logits as with the add+norm kernels up to bfloat16 rounding,
+    at real layer sizes, and the kernels are really gone."""
+    import vllm_oxide_b200.parts.block as block
+    from vllm_oxide_b200 import host, kernels
+    half, _ = engines(SIZES["8b"], seed=14, seqs=8, pages=24)
+    del _
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (300, 5, 129)]
+    feed = torch.randint(0, 2048, (3, 4), generator=g).tolist()
+
+    def run(on, first_id):
+        block.STREAM_IN_PRODUCTS = on
+        half.core._graphs.clear()
+        mgr = half.cache.manager
+        ids = [first_id + i for i in range(3)]
+        for r, p in zip(ids, prompts):
+            mgr.add_request(r)
+            mgr.ensure(r, 0, len(p))
+            half.core.run([host.BatchEntry(r, 0, p, [])])
+            mgr.advance(r, len(p))
+        rows, launches = [], []
+        for step in range(4):
+            entries = []
+            for i, (r, p) in enumerate(zip(ids, prompts)):
+                mgr.ensure(r, len(p) + step, 1)
+                entries.append(host.BatchEntry(r, len(p) + step, [feed[i][step]], [0]))
+            before = kernels.launch_count
+            rows.append(half.core.run(entries).double().cpu())
+            launches.append(kernels.launch_count - before)
+            for r, p in zip(ids, prompts):
+                mgr.advance(r, len(p) + step + 1)
+        half.core.check_errors()
+        for r in ids:
+            mgr.free_request(r)
+        return torch.stack(rows), launches[-1]
+
+    try:
+        separate, n_separate = run(False, 100)
+        inside, n_inside = run(True, 200)
+    finally:
+        block.STREAM_IN_PRODUCTS = True
+    layers = SIZES["8b"]["num_hidden_layers"]
+    assert n_separate - n_inside == 2 * layers
+    scale = separate.pow(2).mean().sqrt()
+    err = inside - separate
+    assert err.pow(2).mean().sqrt() < 8e-3 * scale and err.abs().max() < 6e-2 * scale

@@ -16,6 +16,15 @@
 //     [M, 2*intermediate] tensor never exists.  Rounding follows the reference: the product is
 //     rounded to bfloat16 once; SiLU is rounded, then the product with `up` is rounded.
 //
+//   * the residual stream can stay inside the products (decode-sized steps have no other use for the separate
+//     add+norm kernel, and every kernel less in the chain of a layer saves about 4 us):
+//       - EPI_ADD rounds the product to bfloat16 and adds it to `out` in place: out is the residual stream,
+//         so the output product of the attention and the down product leave residual' = x + residual behind;
+//       - NORM reads that stream as its tokens and applies RMSNorm on the fly: the consumer warps multiply the
+//         token fragments by the norm's weight in registers and sum their squares on the way (a block reads
+//         all of K for its tile anyway), and the epilogue scales every sum by 1/sqrt(mean square + eps) of its
+//         token, which is the same product up to the place where bfloat16 rounds.
+//
 // Every wait on an mbarrier is bounded: a wait that runs out sets an error bit and a block-wide
 // abort flag; the block then waits (bounded again) for the copies it still has in flight and returns.
 #define VOB_TIMEOUT_WHERE 0x100
@@ -29,7 +38,7 @@ constexpr int SK_SLICES = SK_KC / TMA_BOX_COLS;   // boxes of 64 columns per sta
 constexpr int SK_CONSUMERS = 4;
 constexpr int SK_THREADS = (SK_CONSUMERS + 1) * 32;
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_ADD = 3 };
 
 __device__ __forceinline__ void sk_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -52,10 +61,10 @@ template <int R, int MT> struct SkStages { static constexpr int N = (96 * 1024) 
 // stride ldo).  EPI_SWIGLU: the rows of W alternate in groups of eight between gate and up (gate rows
 // 8i..8i+7 of the original at 16i..16i+7, the up rows of the same outputs at 16i+8..16i+15), so every 16
 // rows of a tile hold both halves of eight outputs; out [M, N/2].
-template <int R, int MT, int EPI>
+template <int R, int MT, int EPI, int NORM>
 __global__ void __launch_bounds__(SK_THREADS, 2)
-gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, void* __restrict__ out,
-                   long ldo, int M, int N, int K, int num_tiles, int* err) {
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, void* out,
+                   long ldo, int M, int N, int K, int num_tiles, const float* __restrict__ norm_w, float eps, int* err) {
   constexpr int S = SkStages<R, MT>::N;
   constexpr int RT = R / 16, NT = MT / 8;
   constexpr int W_SLICE = R * 128, X_SLICE = MT * 128;
@@ -63,7 +72,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   extern __shared__ __align__(1024) char smem_raw[];
   char* stages = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   float* red = reinterpret_cast<float*>(stages + S * STAGE_BYTES);          // [SK_CONSUMERS][R][MT]
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + SK_CONSUMERS * R * MT);
+  float* sumsq = red + SK_CONSUMERS * R * MT;                                // [SK_CONSUMERS][16] squares of a token, per warp
+  uint64_t* full = reinterpret_cast<uint64_t*>(sumsq + SK_CONSUMERS * 16);
   uint64_t* empty = full + S;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + S);
 
@@ -127,13 +137,40 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const int b_chunk = MT == 16 ? (mi & 1) : ((lane >> 3) & 1);
     long it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      // EPI_ADD: what the tile's outputs hold now, asked for before the products rather than at their end
+      constexpr int ADD_PER_THREAD = (R * MT + SK_CONSUMERS * 32 - 1) / (SK_CONSUMERS * 32);
+      float prev[ADD_PER_THREAD];
+      if (EPI == EPI_ADD) {
+#pragma unroll
+        for (int i = 0; i < ADD_PER_THREAD; ++i) {
+          const int idx = (int)threadIdx.x + i * SK_CONSUMERS * 32;
+          const int tok = idx / R;
+          const long n = (long)tile * R + idx % R;
+          prev[i] = (idx < R * m_rows && n < N) ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(out)[(long)tok * ldo + n]) : 0.f;
+        }
+      }
       float acc[RT][NT][4];
 #pragma unroll
       for (int i = 0; i < RT; ++i)
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+      float ss[2] = {0.f, 0.f};                                  // NORM: squares of tokens g and g + 8 seen by this thread
       for (int kc = 0; kc < k_iters; ++kc, ++it) {
         const int s = (int)(it % S);
+        // NORM: the norm's weights for this thread's columns of the stage, asked for before the wait for the stage
+        // (they come from L2 and would otherwise stand between every ldmatrix and its mma)
+        float2 nw[SK_KC / 16 / SK_CONSUMERS][2];
+        if (NORM) {
+#pragma unroll
+          for (int jj = 0; jj < SK_KC / 16 / SK_CONSUMERS; ++jj) {
+            const int k0 = kc * SK_KC + (warp + jj * SK_CONSUMERS) * 16 + tq * 2;
+            nw[jj][0] = nw[jj][1] = make_float2(0.f, 0.f);
+            if (k0 + 8 < K) {
+              nw[jj][0] = __ldg(reinterpret_cast<const float2*>(norm_w + k0));
+              nw[jj][1] = __ldg(reinterpret_cast<const float2*>(norm_w + k0 + 8));
+            }
+          }
+        }
         bool ok = mbar_wait(&full[s], (unsigned)((it / S) & 1), abort_flag, err);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -151,6 +188,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             sk_ldmatrix_x2(b2, xt + c * X_SLICE + swizzled_offset(b_row, ch + b_chunk));
             b[0] = b2[0]; b[1] = b2[1]; b[2] = b[3] = 0;
           }
+          if (NORM) {
+            // b[0], b[1]: token g at columns k, k+1 and k+8, k+9 of this 16-column step; b[2], b[3]: token g + 8
+            const float2 w0 = nw[jj][0], w1 = nw[jj][1];
+#pragma unroll
+            for (int r = 0; r < (MT == 16 ? 4 : 2); ++r) {
+              const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b[r]));
+              ss[r >> 1] = fmaf(v.x, v.x, fmaf(v.y, v.y, ss[r >> 1]));
+              const float2 wv = (r & 1) ? w1 : w0;
+              const __nv_bfloat162 scaled = __floats2bfloat162_rn(v.x * wv.x, v.y * wv.y);
+              b[r] = *reinterpret_cast<const uint32_t*>(&scaled);
+            }
+          }
 #pragma unroll
           for (int i = 0; i < RT; ++i) {
             uint32_t a[4];
@@ -165,6 +214,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
+      }
+      if (NORM) {
+        // the four lanes of a token hold different columns: add them, then one lane writes the warp's share
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          ss[h] += __shfl_xor_sync(0xffffffffu, ss[h], 1);
+          ss[h] += __shfl_xor_sync(0xffffffffu, ss[h], 2);
+        }
+        if (tq == 0) { sumsq[warp * 16 + g] = ss[0]; sumsq[warp * 16 + 8 + g] = ss[1]; }
       }
       // sum the four warps' partial tiles (a warp whose wait ran out still meets the others at the barriers)
 #pragma unroll
@@ -190,21 +248,35 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           float gate = 0.f, up = 0.f;
 #pragma unroll
           for (int w = 0; w < SK_CONSUMERS; ++w) { gate += red[(w * R + gr) * MT + tok]; up += red[(w * R + gr + 8) * MT + tok]; }
+          if (NORM) {
+            const float inv = 1.f / sqrtf((sumsq[tok] + sumsq[16 + tok] + sumsq[32 + tok] + sumsq[48 + tok]) / (float)K + eps);
+            gate *= inv;
+            up *= inv;
+          }
           gate = bf16_round(gate);
           up = bf16_round(up);
           const float act = bf16_round(gate / (1.f + expf(-gate)));
           reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(act * up);
         }
       } else {
-        for (int idx = tid; idx < R * m_rows; idx += SK_CONSUMERS * 32) {
+#pragma unroll
+        for (int i = 0; i < ADD_PER_THREAD; ++i) {
+          const int idx = tid + i * SK_CONSUMERS * 32;
+          if (idx >= R * m_rows) break;
           const int tok = idx / R, r = idx % R;
           const long n = (long)tile * R + r;
           if (n >= N) continue;
           float v = 0.f;
 #pragma unroll
           for (int w = 0; w < SK_CONSUMERS; ++w) v += red[(w * R + r) * MT + tok];
-          if (EPI == EPI_F32) reinterpret_cast<float*>(out)[(long)tok * ldo + n] = bf16_round(v);
-          else reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(v);
+          if (NORM) v *= 1.f / sqrtf((sumsq[tok] + sumsq[16 + tok] + sumsq[32 + tok] + sumsq[48 + tok]) / (float)K + eps);
+          if (EPI == EPI_F32) {
+            reinterpret_cast<float*>(out)[(long)tok * ldo + n] = bf16_round(v);
+          } else if (EPI == EPI_ADD) {
+            reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(bf16_round(v) + prev[i]);
+          } else {
+            reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(v);
+          }
         }
       }
       asm volatile("bar.sync 1, %0;\n" ::"n"(SK_CONSUMERS * 32) : "memory");
@@ -214,29 +286,35 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
 }
 
-template <int R, int MT, int EPI>
-static int skinny_launch(const CUtensorMap* tmW, const CUtensorMap* tmX, void* out, long ldo, int M, int N, int K, int* err,
-                         cudaStream_t stream) {
+template <int R, int MT, int EPI, int NORM>
+static int skinny_launch(const CUtensorMap* tmW, const CUtensorMap* tmX, void* out, long ldo, int M, int N, int K,
+                         const float* norm_w, float eps, int* err, cudaStream_t stream) {
   constexpr int S = SkStages<R, MT>::N;
-  const int smem = 1024 + S * SK_SLICES * (R + MT) * 128 + SK_CONSUMERS * R * MT * (int)sizeof(float) + 2 * S * 8 + 16;
+  const int smem = 1024 + S * SK_SLICES * (R + MT) * 128 + SK_CONSUMERS * (R * MT + 16) * (int)sizeof(float) + 2 * S * 8 + 16;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<R, MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<R, MT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int num_tiles = (N + R - 1) / R;
   const int grid = num_tiles < 2 * 148 ? num_tiles : 2 * 148;
-  return launch_kernel(gemm_skinny_kernel<R, MT, EPI>, grid, SK_THREADS, smem, stream, *tmW, *tmX, out, ldo, M, N, K,
-                       num_tiles, err);
+  return launch_kernel(gemm_skinny_kernel<R, MT, EPI, NORM>, grid, SK_THREADS, smem, stream, *tmW, *tmX, out, ldo, M, N, K,
+                       num_tiles, norm_w, eps, err);
 }
 
 template <int R, int MT>
 static int skinny_dispatch(int epilogue, const CUtensorMap* tw, const CUtensorMap* tx, void* out, long ldo, int M, int N,
-                           int K, int* err, cudaStream_t stream) {
-  if (epilogue == EPI_BF16) return skinny_launch<R, MT, EPI_BF16>(tw, tx, out, ldo, M, N, K, err, stream);
-  if (epilogue == EPI_F32) return skinny_launch<R, MT, EPI_F32>(tw, tx, out, ldo, M, N, K, err, stream);
-  if (epilogue == EPI_SWIGLU) return skinny_launch<R, MT, EPI_SWIGLU>(tw, tx, out, ldo, M, N, K, err, stream);
+                           int K, const float* norm_w, float eps, int* err, cudaStream_t stream) {
+  if (norm_w) {   // the norm in front is instantiated for the two products that follow a norm in a layer
+    if (epilogue == EPI_BF16) return skinny_launch<R, MT, EPI_BF16, 1>(tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream);
+    if (epilogue == EPI_SWIGLU) return skinny_launch<R, MT, EPI_SWIGLU, 1>(tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream);
+    return VOB_UNSUPPORTED;
+  }
+  if (epilogue == EPI_BF16) return skinny_launch<R, MT, EPI_BF16, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, err, stream);
+  if (epilogue == EPI_F32) return skinny_launch<R, MT, EPI_F32, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, err, stream);
+  if (epilogue == EPI_SWIGLU) return skinny_launch<R, MT, EPI_SWIGLU, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, err, stream);
+  if (epilogue == EPI_ADD) return skinny_launch<R, MT, EPI_ADD, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, err, stream);
   return VOB_BAD_ARGUMENT;
 }
 
@@ -254,17 +332,20 @@ VOB_API int vob_gemm_skinny_token_box(int M) { return M <= 8 ? 8 : 16; }
 // rows vob_gemm_skinny_token_box(M) (both from vob_tensor_map_bf16_sliced with 4 slices per box, host memory; K must be
 // a multiple of 64).
 // epilogue: 0 bfloat16 out [M,N]; 1 float out [M,N] (rounded to bfloat16 first); 2 SiLU(gate)*up over rows that
-// alternate in groups of eight between gate and up, out [M,N/2] bfloat16.  Needs M <= 16.
+// alternate in groups of eight between gate and up, out [M,N/2] bfloat16; 3 out [M,N] bfloat16 += the product rounded to
+// bfloat16 (the residual stream).  norm_w (may be null; epilogues 0 and 2): float [K], the weight of an RMSNorm with
+// `eps` that is applied to x on the way.  Needs M <= 16.
 VOB_API int vob_gemm_skinny(const void* map_w, const void* map_x, void* out, long ldo, int M, int N, int K, int epilogue,
-                            int* err, cudaStream_t stream) {
+                            const float* norm_w, float eps, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 16 || K <= 0 || K % 64 || !map_w || !map_x) return VOB_UNSUPPORTED;
   if (epilogue == EPI_SWIGLU && N % 16) return VOB_BAD_ARGUMENT;
+  if (norm_w && (uintptr_t)norm_w % 8) return VOB_BAD_ARGUMENT;
   const CUtensorMap* tw = (const CUtensorMap*)map_w;
   const CUtensorMap* tx = (const CUtensorMap*)map_x;
   const bool tall = vob_gemm_skinny_weight_box(N) == 32;
-  if (M <= 8) return tall ? skinny_dispatch<32, 8>(epilogue, tw, tx, out, ldo, M, N, K, err, stream)
-                          : skinny_dispatch<16, 8>(epilogue, tw, tx, out, ldo, M, N, K, err, stream);
-  return tall ? skinny_dispatch<32, 16>(epilogue, tw, tx, out, ldo, M, N, K, err, stream)
-              : skinny_dispatch<16, 16>(epilogue, tw, tx, out, ldo, M, N, K, err, stream);
+  if (M <= 8) return tall ? skinny_dispatch<32, 8>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream)
+                          : skinny_dispatch<16, 8>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream);
+  return tall ? skinny_dispatch<32, 16>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream)
+              : skinny_dispatch<16, 16>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream);
 }

@@ -217,7 +217,7 @@ def gemm_f32(a, w, out, bias=None) -> None:
                               ctypes.c_long(out.stride(0)), _p(bias), M, N, K, _stream()), "gemm_f32")
 
 
-EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
+EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_ADD = 0, 1, 2, 3
 _tensor_maps = {}
 
 
@@ -299,11 +299,13 @@ def gemm_skinny_supported(x, w) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_skinny(x, w, out, epilogue: int, err) -> None:
+def gemm_skinny(x, w, out, epilogue: int, err, norm_weight=None, eps: float = 0.0) -> None:
     """out = x @ w^T for at most 16 rows of x (see gemm_skinny_supported); epilogue EPI_BF16 (out bfloat16 [M,N]),
-    EPI_F32 (out float32 [M,N], rounded to bfloat16 first) or EPI_SWIGLU (the rows of w alternate in groups of
-    eight between gate and up; out bfloat16 [M,N/2] = SiLU(gate) * up)."""
-    _cuda(x, w, out)
+    EPI_F32 (out float32 [M,N], rounded to bfloat16 first), EPI_SWIGLU (the rows of w alternate in groups of
+    eight between gate and up; out bfloat16 [M,N/2] = SiLU(gate) * up) or EPI_ADD (out bfloat16 [M,N] += the
+    product rounded to bfloat16: out is the residual stream).  With `norm_weight` (float [K]; EPI_BF16 and EPI_SWIGLU)
+    the product is that of RMSNorm(x) * norm_weight, the norm computed on the way."""
+    _cuda(x, w, out, norm_weight)
     if not gemm_skinny_supported(x, w):
         raise KernelError("gemm_skinny: this product is not supported (bfloat16, at most 16 rows, K a multiple of 64, 16-byte aligned rows)")
     M, K = x.shape
@@ -311,10 +313,12 @@ def gemm_skinny(x, w, out, epilogue: int, err) -> None:
     assert w.shape[1] == K and out.stride(1) == 1 and out.shape[0] == M
     assert out.shape[1] == (N // 2 if epilogue == EPI_SWIGLU else N)
     assert out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16)
+    if norm_weight is not None:
+        assert epilogue in (EPI_BF16, EPI_SWIGLU) and norm_weight.dtype == torch.float32 and norm_weight.numel() == K
     map_w = tensor_map(w, int(lib().vob_gemm_skinny_weight_box(ctypes.c_long(N))), 4)
     map_x = tensor_map(x, 8 if M <= 8 else 16, 4)
-    _check(lib().vob_gemm_skinny(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, _p(err),
-                                 _stream()), "gemm_skinny")
+    _check(lib().vob_gemm_skinny(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, _p(norm_weight),
+                                 ctypes.c_float(eps), _p(err), _stream()), "gemm_skinny")
 
 
 def sample(logits, temperature, top_k, top_p, keys, out, num_rows: int) -> None:

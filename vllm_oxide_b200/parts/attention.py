@@ -88,6 +88,27 @@ class Attention(Mixer):
         self.attend(qkv, width, attn, cache, ctx, T)
         return linear(attn, self.wo, ctx.ws.get("attn_proj", T, self.H, x.dtype), ctx)
 
+    # ---- the same with the residual stream kept inside the products (decode-sized steps)
+    def can_forward_on_stream(self, stream, ctx) -> bool:
+        T = stream.shape[0]
+        attn = ctx.ws.get("attn_out", T, self.nh * self.hd, stream.dtype)
+        return (kernels.gemm_skinny_supported(stream, self.wqkv) and kernels.gemm_skinny_supported(attn, self.wo))
+
+    def forward_on_stream(self, stream, norm, ctx, cache, state=None, write_cache: bool = True) -> None:
+        """stream += attention(RMSNorm(stream)): the norm is applied inside the q|k|v product, the sum made by the
+        output product."""
+        T = stream.shape[0]
+        width = (self.nh + 2 * self.kvh) * self.hd
+        qkv = ctx.ws.get("qkv", T, width, stream.dtype)
+        kernels.gemm_skinny(stream, self.wqkv, qkv, kernels.EPI_BF16, ctx.err, norm_weight=norm.weight, eps=norm.eps)
+        g = cache.group
+        kernels.qk_norm_rope_kv_write(qkv, self.bqkv, ctx.positions, ctx.slot_mapping[g], self.wq_norm, self.wk_norm,
+                                      self.rope.cos_sin, cache.k, cache.v, T, self.nh, self.kvh, self.hd, self.eps,
+                                      write_cache, ctx.err)
+        attn = ctx.ws.get("attn_out", T, self.nh * self.hd, stream.dtype)
+        self.attend(qkv, width, attn, cache, ctx, T)
+        kernels.gemm_skinny(attn, self.wo, stream, kernels.EPI_ADD, ctx.err)
+
     def attend(self, qkv, q_stride, out, cache, ctx, T):
         """bfloat16: decoding requests (one token) go to the split-key tensor-core kernel, requests with a
         portion to the tensor-core kernel for portions.  The 32-bit path, and sizes those kernels refuse,

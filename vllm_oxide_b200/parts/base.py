@@ -119,6 +119,8 @@ class Part:
 
 class Norm(Part):
     def forward(self, x, residual, ctx, rows=None, n_rows=None):
+        """(norm(x + residual), x + residual).  x may be None: the block before has already added its output into
+        `residual`, and the norm is of `residual` itself."""
         raise NotImplementedError
 
 

@@ -12,6 +12,14 @@ import torch
 
 from ..weights.loader import TensorSpec
 from .base import Block, PartSpec, build_part, register_part
+from .norm import RMSNorm
+
+# Decode-sized steps keep the residual stream inside the products of the attention and the feed-forward (see
+# PreNormBlock._keeps_stream); False runs the separate add+norm kernels always.
+STREAM_IN_PRODUCTS = True
+# Measured at Qwen3-8B sizes: 323 against 314 tokens/s at batch 1, 2,385 against 2,306 at batch 8, no gain at batch 16
+# (the norm's arithmetic on 16-token fragments costs what the two kernels saved).
+STREAM_MAX_TOKENS = 8
 
 
 class PreNormBlock(Block):
@@ -32,10 +40,29 @@ class PreNormBlock(Block):
             p.load({s.name: tensors[s.name] for s in p.tensor_specs()})
 
     def forward(self, hidden, residual, ctx, cache, state, write_cache=True):
+        """(hidden, residual) in and out.  hidden None means that the part before has already added its output into
+        `residual` (the stream); this block leaves it so too when its parts can keep the stream inside their products."""
+        if (hidden is None or residual is None) and self._keeps_stream(hidden if residual is None else residual, ctx):
+            stream = hidden if residual is None else residual
+            self.mixer.forward_on_stream(stream, self.input_norm, ctx, cache, state, write_cache)
+            self.feed_forward.forward_on_stream(stream, self.post_mixer_norm, ctx)
+            return None, stream
         normed, residual = self.input_norm.forward(hidden, residual, ctx)
         mixed = self.mixer.forward(normed, ctx, cache, state, write_cache)
         normed, residual = self.post_mixer_norm.forward(mixed, residual, ctx)
         return self.feed_forward.forward(normed, ctx), residual
+
+    def _keeps_stream(self, stream, ctx) -> bool:
+        """Decode-sized bfloat16 steps whose norms are RMSNorm and whose mixer and feed-forward offer
+        forward_on_stream(stream, norm, ...): stream += part(norm(stream)), with the norm applied inside the part's
+        first product and the sum made by its last one (two kernels less a layer)."""
+        if not STREAM_IN_PRODUCTS or stream.dtype != torch.bfloat16 or stream.shape[0] > STREAM_MAX_TOKENS:
+            return False
+        if not (isinstance(self.input_norm, RMSNorm) and isinstance(self.post_mixer_norm, RMSNorm)):
+            return False
+        can_m = getattr(self.mixer, "can_forward_on_stream", None)
+        can_f = getattr(self.feed_forward, "can_forward_on_stream", None)
+        return bool(can_m and can_f and can_m(stream, ctx) and can_f(stream, ctx))
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -54,4 +54,18 @@ class SwiGLU(FeedForward):
         return linear(act, self.wdown, ctx.ws.get("mlp_out", T, self.H, x.dtype), ctx)
 
 
+    # ---- the same with the residual stream kept inside the products (decode-sized steps)
+    def can_forward_on_stream(self, stream, ctx) -> bool:
+        act = ctx.ws.get("act", stream.shape[0], self.I, stream.dtype)
+        return (self.interleaved and kernels.gemm_skinny_supported(stream, self.wgu)
+                and kernels.gemm_skinny_supported(act, self.wdown))
+
+    def forward_on_stream(self, stream, norm, ctx) -> None:
+        """stream += down(SiLU(gate) * up) of RMSNorm(stream): the norm inside the gate|up product, the sum made by
+        the down product."""
+        act = ctx.ws.get("act", stream.shape[0], self.I, stream.dtype)
+        kernels.gemm_skinny(stream, self.wgu, act, kernels.EPI_SWIGLU, ctx.err, norm_weight=norm.weight, eps=norm.eps)
+        kernels.gemm_skinny(act, self.wdown, stream, kernels.EPI_ADD, ctx.err)
+
+
 register_part("feed_forward", "swiglu", SwiGLU)

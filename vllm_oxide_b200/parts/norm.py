@@ -29,11 +29,16 @@ class RMSNorm(Norm):
         self.weight = tensors[self.weight_name].contiguous()
 
     def forward(self, x, residual, ctx, rows=None, n_rows=None, name="normed"):
+        # x None: the part before has already added its output into the residual stream; the norm is of the stream
+        # itself, which stays where it is (residual' = x, written onto itself)
+        summed = x is None
+        if summed:
+            x, residual = residual, None
         n = x.shape[0] if rows is None else n_rows
         y = ctx.ws.get(name, n, self.size, x.dtype)
         has_residual = residual is not None
         if residual is None:
-            residual = ctx.ws.get("residual", x.shape[0], self.size, x.dtype)
+            residual = x if summed else ctx.ws.get("residual", x.shape[0], self.size, x.dtype)
         kernels.add_rmsnorm(x, residual, self.weight, y, self.eps, has_residual, ctx.err, rows=rows, n_out=n)
         return y, residual
 

@@ -169,7 +169,7 @@ def attention(q, k, v, positions, window, dt):
     kvh = k.shape[1]
     g = nh // kvh
     scale = 1.0 / math.sqrt(hd)
-    out = torch.empty(T, nh, hd, dtype=it)
+    out = torch.empty(T, nh, hd, dtype=it, device=q.device)
     pi, pj = positions[:, None].long(), positions[None, :].long()
     allowed = pj <= pi
     if window is not None:
@@ -228,11 +228,16 @@ def decoder_layer(cfg, weights, i, hidden, residual, positions, table, dt, trace
 
 
 def forward_logits(cfg, weights, token_ids, dt=torch.float32, trace=None):
-    """Logits [T, V] at every position of one whole sequence (SRC/models/qwen3.rs:295-304,384-386)."""
+    """Logits [T, V] at every position of one whole sequence (SRC/models/qwen3.rs:295-304,384-386).
+
+    Everything happens where the weights lie (the tests at the layer sizes of large checkpoints hand in
+    weights on the GPU, so that a float64 run takes seconds); the table of angles is made on the CPU
+    either way, so that its values do not depend on the device."""
     z = sizes(cfg)
-    ids = torch.as_tensor(token_ids, dtype=torch.int64)
-    positions = torch.arange(len(ids))
-    table = rope_table(z["hd"], z["max_pos"], z["theta"])
+    dev = weights["model.embed_tokens.weight"].device
+    ids = torch.as_tensor(token_ids, dtype=torch.int64).to(dev)
+    positions = torch.arange(len(ids)).to(dev)
+    table = rope_table(z["hd"], z["max_pos"], z["theta"]).to(dev)
     hidden = embedding(weights["model.embed_tokens.weight"], ids, dt)
     residual = None
     for i in range(z["L"]):

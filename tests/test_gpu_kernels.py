@@ -783,6 +783,36 @@ def test_gemm_skinny_refuses_what_it_cannot_take():
         kernels.gemm_skinny(x, w, torch.zeros(17, 8, dtype=torch.bfloat16, device=DEV), kernels.EPI_BF16, err_word())
 
 
+def test_a_wait_that_runs_out_comes_back_as_an_error_word_and_the_next_launch_is_right():
+    """Failure detection without a fault: the producers of the weight-streaming product withhold their copies (a flag
+    that only this test sets), so every block waits for data that never comes; with the waits shortened to a few hundred
+    tries they run out at once: the kernel returns, the error word says 'a bounded wait ran out' and in which kernel,
+    nothing was written, and (limit and copies restored) the next ordinary launch on the same context gives the right
+    product.  Nothing spins without a bound, nothing faults, and no copy is in flight when a block leaves."""
+    from vllm_oxide_b200 import kernels
+    M, N, K = 8, 4096, 4096
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().to(DEV)
+    ref = x.double() @ w.double().t()
+    err = err_word()
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_skinny_set_wait_limit(300, withhold_copies=True)
+    try:
+        kernels.gemm_skinny(x, w, out, kernels.EPI_BF16, err)
+        torch.cuda.synchronize()
+    finally:
+        kernels.gemm_skinny_set_wait_limit(0)
+    word = int(err.item())
+    assert word == 0x20 | 0x100, hex(word)                       # VOB_ERR_TIMEOUT | VOB_WHERE_GEMM_SKINNY
+    assert "a bounded wait inside a kernel ran out" in kernels.describe_error_word(word)
+    assert "weight-streaming product" in kernels.describe_error_word(word)
+    assert bool((out == 7.0).all())                              # a block that gave up wrote nothing
+    err.zero_()
+    kernels.gemm_skinny(x, w, out, kernels.EPI_BF16, err)
+    assert torch.allclose(out.double(), ref, rtol=1e-2, atol=1e-2) and err.item() == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(14, 17464, 1536), (16, 17472, 1024), (5, 20000, 1280)])
 def test_gemm_skinny_a_fast_refill_does_not_overtake_the_readers(M, N, K):
     """A matrix that stays in L2 and gives blocks two tiles each: the copy engine refills a stage of the ring as soon as

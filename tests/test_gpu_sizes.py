@@ -16,27 +16,97 @@ SIZES = {
 }
 
 
-def engines(sizes, seed, max_len=2048, pages=12, budget=512, seqs=2):
-    from vllm_oxide_b200 import LLM, EngineOptions
+def config_of(sizes, max_len=2048):
+    return dict(architectures=["Qwen3ForCausalLM"], vocab_size=2048, rope_theta=1e6, rms_norm_eps=1e-6,
+                max_position_embeddings=max(4096, max_len), tie_word_embeddings=False, hidden_act="silu", torch_dtype="bfloat16",
+                **sizes)
+
+
+def models(sizes, seed, max_len=2048, keep_weights=False):
+    """The same bfloat16-valued random weights as a bfloat16 model and as a float32 model, both on the device
+    (and, with `keep_weights`, as a {name: float32 tensor} dict for the plain implementation)."""
     from vllm_oxide_b200.engine.loading import resolve
     from vllm_oxide_b200.models.causal_lm import CausalLM
     from vllm_oxide_b200.weights.random_init import random_weights
-    cfg = dict(architectures=["Qwen3ForCausalLM"], vocab_size=2048, rope_theta=1e6, rms_norm_eps=1e-6,
-               max_position_embeddings=max(4096, max_len), tie_word_embeddings=False, hidden_act="silu", torch_dtype="bfloat16",
-               **sizes)
+    cfg = config_of(sizes, max_len)
     config, plan = resolve(cfg, where="config")
     half = CausalLM(plan, torch.bfloat16, "cuda:0")
     weights = random_weights(half.tensor_specs(), seed, "fan_in", "cuda:0", torch.bfloat16)
     half.load(weights)
     full = CausalLM(plan, torch.float32, "cuda:0")
-    full.load({k: (v if v.dtype == torch.int32 else v.float()) for k, v in weights.items()})
-    del weights
+    as_float = {k: (v if v.dtype == torch.int32 else v.float()) for k, v in weights.items()}
+    full.load(as_float)
+    return cfg, config, half, full, (as_float if keep_weights else None)
+
+
+def engines(sizes, seed, max_len=2048, pages=12, budget=512, seqs=2):
+    from vllm_oxide_b200 import LLM, EngineOptions
+    _, config, half, full, _ = models(sizes, seed, max_len)
     out = []
     for model, dtype in ((half, "bfloat16"), (full, "float32")):
         opts = EngineOptions(max_model_len=max_len, block_size=256, num_kv_blocks=pages, max_num_seqs=seqs,
                              max_num_batched_tokens=budget, dtype=dtype)        # a 700-token prompt goes in two portions
         out.append(LLM("<random weights>", opts, device="cuda:0", _model=(config, model)))
     return out
+
+
+@pytest.mark.parametrize("name", list(SIZES))
+def test_real_layer_sizes_against_the_plain_implementation_in_every_cut(name):
+    """Both precisions at the layer sizes of Qwen3-8B (two layers) and Qwen3-32B (one layer), vocabulary 2,048, pages of
+    256 keys, against the PLAIN implementation over the same weights: every position of six requests, whole; with the
+    last 32 tokens one by one; in portions down to two tokens that start and end inside and on the edges of pages; and
+    mixed, up to four live requests on a pool of fewer pages than the requests need, so that pages are used again.  The plain
+    runs happen on the GPU in float64 (the truth) and in bfloat16 (what rounding at every operation costs), through
+    torch's generic operations; nothing of the engine is in them."""
+    import numpy as np
+    from plain import qwen3_plain as P
+    from test_gpu_replay import Both, check, mixed_schedule_of
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    assert not torch.backends.cuda.matmul.allow_tf32          # the plain float32 products are true float32
+    cfg, config, half, full, weights = models(SIZES[name], seed=21, keep_weights=True)
+    bs = 256
+    g = torch.Generator().manual_seed(31)
+    reqs = {f"r{i}": torch.randint(0, 2048, (n,), generator=g).tolist() for i, n in enumerate([700, 300, 515, 90, 260, 130])}
+    truth = {rid: P.forward_logits(cfg, weights, toks, torch.float64).cpu().numpy() for rid, toks in reqs.items()}
+    rounded = {rid: P.forward_logits(cfg, weights, toks, torch.bfloat16).double().cpu().numpy() for rid, toks in reqs.items()}
+    del weights
+    torch.cuda.empty_cache()
+    steps, _, peak = mixed_schedule_of(reqs, bs, seed=4, portions=[2, 3, 40, 130, bs - 1, bs, bs + 1])
+    assert peak // bs < sum((len(t) + bs - 1) // bs for t in reqs.values())       # fewer pages than the requests need
+    for dtype, model in (("float32", full), ("bfloat16", half)):
+        want = {rid: truth[rid] if dtype == "float32" else Both(truth[rid], rounded[rid]) for rid in reqs}
+        make = lambda pool: TraceRunner(None, dtype, pool, bs, _model=(config, model), max_live=4)
+        for rid, toks in reqs.items():
+            n = len(toks)
+            pool = (n + bs - 1) // bs * bs
+            whole = make(pool).step([dict(id=rid, tokens=toks, want=list(range(n)))], [rid])
+            check(whole, want[rid], dtype, f"{name} {dtype} {rid} whole")
+            r = make(pool)
+            cut = n - 32
+            rows = [r.step([dict(id=rid, tokens=toks[:cut], want=[cut - 1])], [])[0]]
+            for t in range(cut, n):
+                rows.append(r.step([dict(id=rid, tokens=[toks[t]], want=[0])], [])[0])
+            check(np.stack(rows), want[rid][cut - 1:], dtype, f"{name} {dtype} {rid} last 32 one by one")
+            r, got, pos = make(pool), [], 0
+            sizes = [2, bs - 2, 3, bs + 1, 2, 130, bs - 4, 2, 64]          # ends on a page's edge, starts on it, straddles it
+            while pos < n:
+                m = min(sizes[len(got) % len(sizes)], n - pos)
+                got.append(r.step([dict(id=rid, tokens=toks[pos:pos + m], want=list(range(m)))], []))
+                pos += m
+            check(np.concatenate(got), want[rid], dtype, f"{name} {dtype} {rid} portions")
+        r = make(peak)
+        got = {rid: [None] * len(t) for rid, t in reqs.items()}
+        for s in steps:
+            out = r.step([{k: v for k, v in e.items() if k != "_at"} for e in s["entries"]], s["end"])
+            row = 0
+            for e in s["entries"]:
+                for w in e["want"]:
+                    got[e["id"]][e["_at"] + w] = out[row]
+                    row += 1
+            assert r.manager.check_invariants() == ""
+        assert r.manager.num_free_blocks(0) == peak // bs
+        for rid in reqs:
+            check(np.stack(got[rid]), want[rid], dtype, f"{name} {dtype} {rid} mixed")
 
 
 @pytest.mark.parametrize("name", list(SIZES))
@@ -145,13 +215,13 @@ def test_a_mixed_workload_at_real_head_counts_repeats_bit_for_bit(name):
     head counts of real checkpoints (thousands of attention blocks a step): no kernel gives up a wait, and the second
     run of the same work gives the same tokens (the prefix cache is off, so it is the same work)."""
     import random
+    from test_gpu_generate import greedy_tokens_agree_with_32_bit_logits
     from vllm_oxide_b200 import LLM, EngineOptions, SamplingParams
-    cfg = dict(architectures=["Qwen3ForCausalLM"], vocab_size=2048, rope_theta=1e6, rms_norm_eps=1e-6,
-               max_position_embeddings=4096, tie_word_embeddings=False, hidden_act="silu", torch_dtype="bfloat16",
-               **SIZES[name])
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    _, config, half, full, _ = models(SIZES[name], seed=5)
     opts = EngineOptions(dtype="bfloat16", max_model_len=2048 + 64, block_size=256, max_num_seqs=24,
                          max_num_batched_tokens=2048, num_kv_blocks=70, enable_prefix_caching=False)
-    llm = LLM.from_config(cfg, opts, seed=5)
+    llm = LLM("<random weights>", opts, device="cuda:0", _model=(config, half))
     rng = random.Random(7)
     prompts = [[rng.randrange(2048) for _ in range(rng.randint(2, 2048))] for _ in range(32)]
     params = [SamplingParams(temperature=0.0 if i % 3 else 0.8, top_k=None if i % 2 else 40, top_p=None if i % 4 else 0.9,
@@ -161,6 +231,12 @@ def test_a_mixed_workload_at_real_head_counts_repeats_bit_for_bit(name):
     assert all(len(t) == p.max_tokens for t, p in zip(first, params))
     again = [o.token_ids for o in llm.generate(prompts, params)]
     assert again == first
+    # and they are the right tokens: the greedy requests against the 32-bit path over the same weights
+    runner = TraceRunner(None, "float32", 2304, 256, _model=(config, full), max_live=1)
+    sure = sum(greedy_tokens_agree_with_32_bit_logits(runner, prompts[i], first[i], f"{name} request {i}")
+               for i in range(32) if params[i].temperature == 0.0)
+    greedy_steps = sum(p.max_tokens for p in params if p.temperature == 0.0)
+    assert sure >= greedy_steps // 4, f"only {sure} of {greedy_steps} greedy steps had a clear winner"
 
 
 def test_the_residual_stream_inside_the_products_agrees_with_the_separate_norm_kernels():

@@ -77,6 +77,28 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     assert e.value.unexpected == ["model.layers.7.extra.weight"]
 
 
+def test_tensors_the_model_does_not_use_are_a_warning_not_an_error(tmp_path):
+    """A folder with tied output that also stores lm_head.weight and a rotary buffer loads (the reference never reads
+    them, crates/vllm-oxide/src/models/qwen3.rs:322-331); the names are kept for the caller; strict refuses them."""
+    from vllm_oxide_b200.weights.loader import UnexpectedTensorsWarning
+    folder = str(tmp_path / "m")
+    write_random_model_folder(folder, TINY["A"]["config"], 0, "fan_in", torch.float32)       # A: tied output
+    f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    tensors = {n: f.tensor(n).clone() for n in f.names()}
+    plain = load_checked(folder, specs_of("A"), torch.float32, "cpu")
+    tensors["lm_head.weight"] = torch.randn(256, 64)
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    seen = []
+    with pytest.warns(UnexpectedTensorsWarning, match="lm_head.weight"):
+        w = load_checked(folder, specs_of("A"), torch.float32, "cpu", unexpected=seen)
+    assert seen == ["lm_head.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
+    assert set(w) == set(plain) and all(torch.equal(w[k], plain[k]) for k in w)
+    with pytest.raises(WeightsError) as e:
+        load_checked(folder, specs_of("A"), torch.float32, "cpu", strict=True)
+    assert e.value.unexpected == seen and not e.value.missing and not e.value.wrong_shape
+
+
 def test_shard_resolution(tmp_path):
     d = tmp_path
     with pytest.raises(SafetensorsError, match="no weights found"):

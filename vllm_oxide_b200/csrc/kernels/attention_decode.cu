@@ -543,6 +543,8 @@ VOB_API int vob_attention_decode_box_slices(int block_size) { return block_size 
 
 // ------------------------------------------------------------------------------------------------
 // The same computation for callers that cannot allocate: see attention_decode_noalloc.h.
+#include <atomic>
+
 #include "attention_decode_noalloc.h"
 
 namespace vob {
@@ -550,7 +552,9 @@ namespace vob {
 // stand-in for the symbol, never a device address: the address is looked up below.
 static __device__ __align__(256) float g_decode_noalloc_scratch[VOB_DECODE_NOALLOC_MAX_FLOATS];
 constexpr int NOALLOC_MAX_DEVICES = 64;
-static float* g_decode_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+// The array's address per device.  Two host threads may both find an entry empty and both look the address up: they
+// store the same value, so the race is harmless; the atomic only keeps the read and the write whole.
+static std::atomic<float*> g_decode_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
 }  // namespace vob
 
 VOB_API long vob_attention_decode_noalloc_max_floats(void) { return VOB_DECODE_NOALLOC_MAX_FLOATS; }
@@ -571,20 +575,22 @@ VOB_API int vob_attention_decode_noalloc(const void* q, long q_stride, void* out
                                          int window, float scale, long num_pages, int num_splits, int* err,
                                          cudaStream_t stream) {
   if (num_requests <= 0) return 0;
-  if (num_splits < 1 || nh <= 0) return VOB_BAD_ARGUMENT;
+  // every argument is looked at before the device is: a call that is refused has touched nothing
+  if (num_splits < 1 || nh <= 0 || kvh <= 0 || nh % kvh || block_size <= 0 || !q || !out || !kcache || !vcache ||
+      !block_tables || !cu_q || !context_lens || !err)
+    return VOB_BAD_ARGUMENT;
   const long need = vob_attention_decode_scratch_floats(num_requests, nh, num_splits);
   if (need > VOB_DECODE_NOALLOC_MAX_FLOATS) return VOB_NOALLOC_TOO_LARGE;
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return VOB_NOALLOC_NO_DEVICE;
-  if (!g_decode_noalloc_ptr[dev]) {   // set-up, once per device, with that device current
-    float* ptr = nullptr;
+  float* ptr = g_decode_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (!ptr) {   // set-up, once per device, with that device current
     e = cudaGetSymbolAddress((void**)&ptr, g_decode_noalloc_scratch);
     if (e != cudaSuccess) return (int)e;
-    g_decode_noalloc_ptr[dev] = ptr;
+    g_decode_noalloc_ptr[dev].store(ptr, std::memory_order_release);
   }
   return vob_attention_decode(q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q, context_lens,
-                              num_requests, nh, kvh, block_size, window, scale, num_pages, num_splits,
-                              g_decode_noalloc_ptr[dev], err, stream);
+                              num_requests, nh, kvh, block_size, window, scale, num_pages, num_splits, ptr, err, stream);
 }

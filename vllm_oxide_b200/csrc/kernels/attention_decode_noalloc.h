@@ -20,6 +20,12 @@
 //     text for a code.
 //   * The first call on each device looks up the array's device address (once per device, with
 //     that device current).  Make that first call outside any stream capture.
+//   * At EVERY call the current device must be the one that owns `stream` and all the buffers:
+//     the array that is used is the current device's, whatever device the pointers belong to.
+//   * Host threads may call it at the same time (the look-up of the address may then happen twice,
+//     with the same result); what they launch is subject to the rule on overlapping calls below.
+//   * Arguments are checked before anything else: a call that is refused has looked up nothing
+//     and launched nothing.
 //   * The function calls no cudaMalloc, cudaFree or allocating library routine.
 //   * All calls share the one array, and it keeps what the previous call left in it.  The kernels
 //     overwrite every entry they later read, so nothing needs clearing between calls; but two calls

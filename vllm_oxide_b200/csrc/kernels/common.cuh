@@ -108,6 +108,19 @@ inline int launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block
   return (int)cudaGetLastError();
 }
 
+// The number of SMs of the current device (asked once; launch shapes are derived from it, never from a literal).
+inline int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      sms = n;
+    else
+      return 1;
+  }
+  return sms;
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return static_cast<int>(e);

@@ -330,8 +330,9 @@ __global__ void qk_norm_rope_kv_write_kernel(T* qkv, const T* __restrict__ bias,
       float ss = 0.f;
 #pragma unroll
       for (int j = 0; j < NV; ++j)
-        if (2 * lane + 64 * j < half)
-          ss += x1[h][j].x * x1[h][j].x + x1[h][j].y * x1[h][j].y + x2[h][j].x * x2[h][j].x + x2[h][j].y * x2[h][j].y;
+        if (2 * lane + 64 * j < half)   // one fixed chain of fused multiply-adds: see the note on the rotation below
+          ss = __fmaf_rn(x2[h][j].y, x2[h][j].y, __fmaf_rn(x2[h][j].x, x2[h][j].x,
+               __fmaf_rn(x1[h][j].y, x1[h][j].y, __fmaf_rn(x1[h][j].x, x1[h][j].x, ss))));
       ss = warp_sum(ss);
       const float denom = sqrtf(ss / (float)hd + eps);
 #pragma unroll
@@ -349,8 +350,13 @@ __global__ void qk_norm_rope_kv_write_kernel(T* qkv, const T* __restrict__ bias,
     for (int j = 0; j < NV; ++j) {
       const int i = 2 * lane + 64 * j;
       if (i < half) {
-        store2<T>(dst + i, make_float2(x1[h][j].x * c[j].x - x2[h][j].x * sn[j].x, x1[h][j].y * c[j].y - x2[h][j].y * sn[j].y));
-        store2<T>(dst + i + half, make_float2(x2[h][j].x * c[j].x + x1[h][j].x * sn[j].x, x2[h][j].y * c[j].y + x1[h][j].y * sn[j].y));
+        // Products and sums are spelled out (each rounded, none fused): this kernel exists in two shapes (one head or
+        // four a warp, chosen by the number of tokens), and left to itself the compiler may fuse a*b - c*d one way in
+        // one and another way in the other, which made a token's 32-bit logits depend on the size of its step.
+        store2<T>(dst + i, make_float2(__fsub_rn(__fmul_rn(x1[h][j].x, c[j].x), __fmul_rn(x2[h][j].x, sn[j].x)),
+                                       __fsub_rn(__fmul_rn(x1[h][j].y, c[j].y), __fmul_rn(x2[h][j].y, sn[j].y))));
+        store2<T>(dst + i + half, make_float2(__fadd_rn(__fmul_rn(x2[h][j].x, c[j].x), __fmul_rn(x1[h][j].x, sn[j].x)),
+                                              __fadd_rn(__fmul_rn(x2[h][j].y, c[j].y), __fmul_rn(x1[h][j].y, sn[j].y))));
       }
     }
   }
@@ -517,7 +523,8 @@ VOB_API int vob_silu_mul(const void* gu, void* out, int T, int I, int interleave
   const size_t total = (size_t)T * I;
   const bool vec = I % 8 == 0 && ((uintptr_t)gu | (uintptr_t)out) % 16 == 0;
   const size_t work = vec ? total / 8 : total;
-  const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
+  const size_t cap = (size_t)sm_count() * 16;
+  const int blocks = (int)((work + 255) / 256 < cap ? (work + 255) / 256 : cap);
   if (dtype == VOB_F32)
     return vec ? launch_kernel(silu_mul_kernel<float, true>, blocks, 256, 0, stream, (const float*)gu, (float*)out, I, total, interleaved)
                : launch_kernel(silu_mul_kernel<float, false>, blocks, 256, 0, stream, (const float*)gu, (float*)out, I, total, interleaved);
@@ -589,6 +596,9 @@ VOB_API int vob_copy_pages(void* cache, const int* pairs, int n_pairs, long page
 
 // Programmatic dependent launch on (default) or off, for every kernel of this library.
 VOB_API void vob_set_pdl(int on) { pdl_enabled() = on != 0; }
+
+// The number of SMs of the current device, as the launchers of this library see it.
+VOB_API int vob_sm_count() { return sm_count(); }
 
 VOB_API const char* vob_error_string(int code) {
   if (code == VOB_BAD_ARGUMENT) return "bad argument to a vllm_oxide_b200 kernel launcher";

@@ -79,6 +79,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_iters = (K + SK_KC - 1) / SK_KC;
+  const unsigned withheld = vob_test_withhold_copies;   // tests of the bounded waits only; read here, used after the set-up
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], SK_CONSUMERS); }
     *abort_flag = 0;
@@ -93,7 +94,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   pdl_launch_dependents();
   if (warp == SK_CONSUMERS) {
     // ------------------------------------------------ producer (one thread)
-    if (lane == 0) {
+    if (lane == 0 && !withheld) {
       const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
       const long total = (long)my_tiles * k_iters;
       // The weights do not depend on the kernel before this one: the first stages of W are on their way
@@ -298,7 +299,8 @@ static int skinny_launch(const CUtensorMap* tmW, const CUtensorMap* tmX, void* o
     configured = true;
   }
   const int num_tiles = (N + R - 1) / R;
-  const int grid = num_tiles < 2 * 148 ? num_tiles : 2 * 148;
+  const int resident = 2 * sm_count();   // two blocks of this kernel fit an SM
+  const int grid = num_tiles < resident ? num_tiles : resident;
   return launch_kernel(gemm_skinny_kernel<R, MT, EPI, NORM>, grid, SK_THREADS, smem, stream, *tmW, *tmX, out, ldo, M, N, K,
                        num_tiles, norm_w, eps, err);
 }
@@ -322,8 +324,16 @@ static int skinny_dispatch(int epilogue, const CUtensorMap* tw, const CUtensorMa
 
 using namespace vob;
 
+// For tests of the bounded waits: the number of tries after which a pipeline wait of this kernel gives up (0: the
+// default), and whether the producers withhold their copies.  With the copies withheld every block's first wait is for
+// something that never comes: after `tries` attempts the blocks set VOB_ERR_TIMEOUT | VOB_WHERE_GEMM_SKINNY in the error
+// word, write nothing and return (nothing is in flight).  Takes effect for launches made after it on the current device.
+VOB_API int vob_gemm_skinny_set_wait_limit(unsigned tries, int withhold_copies) {
+  return set_wait_limit(tries, withhold_copies ? 1u : 0u);
+}
+
 // Box rows the weight map must have for a matrix of N rows: 32, or 16 when 32-row tiles would leave SMs idle.
-VOB_API int vob_gemm_skinny_weight_box(long N) { return (N + 31) / 32 >= 148 ? 32 : 16; }
+VOB_API int vob_gemm_skinny_weight_box(long N) { return (N + 31) / 32 >= vob::sm_count() ? 32 : 16; }
 
 // Box rows the token map must have for a batch of M rows.
 VOB_API int vob_gemm_skinny_token_box(int M) { return M <= 8 ? 8 : 16; }

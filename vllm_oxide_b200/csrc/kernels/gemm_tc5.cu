@@ -305,15 +305,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   if (csize > 1) cluster_sync_all();
 }
 
-static int tc5_sm_count() {
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return sms;
-}
+static int tc5_sm_count() { return sm_count(); }
 
 // How many clusters of `csize` blocks of this kernel the device runs at once (0 if it cannot run one).
 template <int NT, int EPI>

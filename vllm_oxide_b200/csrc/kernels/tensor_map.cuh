@@ -30,6 +30,23 @@ namespace vob {
 
 constexpr unsigned MBAR_SPIN_LIMIT = 1u << 22;   // tries before a wait on an mbarrier gives up
 
+// The limit that the pipeline waits (mbar_wait) use: MBAR_SPIN_LIMIT, unless a test has shortened it through its source
+// file's setter to see a wait run out.  One copy per source file.  The drain at a kernel's end, which waits for copies
+// that are already on their way, always uses MBAR_SPIN_LIMIT itself: no block leaves with a copy in flight.
+static __device__ unsigned vob_wait_limit = MBAR_SPIN_LIMIT;
+// For the same tests: non-zero makes a kernel's producer issue none of its copies, so that what waits for them waits
+// for something that never comes (a try on an mbarrier may itself block for microseconds, long enough for a real copy
+// to land, so a short limit alone does not make a wait run out).  Nothing is then in flight when the block leaves.
+static __device__ unsigned vob_test_withhold_copies = 0;
+
+// Host side of a source file's setter: tries 0 restores the default limit.
+static inline int set_wait_limit(unsigned tries, unsigned withhold_copies) {
+  const unsigned v = tries ? tries : MBAR_SPIN_LIMIT;
+  cudaError_t e = cudaMemcpyToSymbol(vob_wait_limit, &v, sizeof(v));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(vob_test_withhold_copies, &withhold_copies, sizeof(withhold_copies));
+  return (int)e;
+}
+
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
@@ -49,9 +66,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
 }
 // False when the wait ran out (or another thread of the block gave up before).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int* err) {
-  for (unsigned i = 0; i < MBAR_SPIN_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;      // the common case costs no read of the limit
+  const unsigned limit = vob_wait_limit;
+  for (unsigned i = 1; i < limit; ++i) {
     if (*abort_flag) return false;
+    if (mbar_try_wait(bar, parity)) return true;
   }
   *abort_flag = 1;
   atomicOr(err, VOB_ERR_TIMEOUT_BITS);

@@ -87,7 +87,8 @@ class EngineCore:
         self._host_np = self._host_buf.numpy()
         self._dev_buf = torch.empty(cap, dtype=torch.int32, device=self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.ws = Workspace(min(self.max_tokens, 8192), self.device, model.dtype)
+        # activation buffers for the largest step the scheduler may form, so that no step re-allocates them
+        self.ws = Workspace(max(1, min(self.max_tokens, self.max_seqs * self.max_model_len)), self.device, model.dtype)
         model.bind(cache.planes, cache.states)
         self._copied = torch.cuda.Event() if torch.device(self.device).type == "cuda" else None
         self.h2d_bytes_last = 0

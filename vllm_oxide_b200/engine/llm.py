@@ -81,13 +81,15 @@ class LLM:
         self.sampler = Sampler(device, min(o.max_num_seqs, 512))
         self.tokenizer = self._load_tokenizer(source) if isinstance(source, str) else None
         self.last_stats = GenerateStats()
+        self.last_sampled_ids: List[int] = []
 
     @classmethod
     def from_config(cls, config_dict: dict, options: Optional[EngineOptions] = None, *, seed: int = 0,
-                    init_scheme: str = "fan_in", device: str = "cuda:0") -> "LLM":
-        """An engine over seeded random weights made on the device (no files)."""
+                    init_scheme: str = "fan_in", device: str = "cuda:0", draw_on: Optional[str] = None) -> "LLM":
+        """An engine over seeded random weights (no files): drawn on the device, or with `draw_on="cpu"` by the host's
+        generator, which gives the values a written random model folder holds for the same seed."""
         options = options or EngineOptions()
-        model = random_model(config_dict, seed, resolve_dtype(options.dtype), device, init_scheme)
+        model = random_model(config_dict, seed, resolve_dtype(options.dtype), device, init_scheme, draw_on)
         return cls("<random weights>", options, device=device, _model=model)
 
     # ---- construction helpers
@@ -107,7 +109,7 @@ class LLM:
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated(self.device)
         torch.cuda.reset_peak_memory_stats(self.device)
-        n_tok = min(o.max_num_batched_tokens, 8192)
+        n_tok = max(1, min(o.max_num_batched_tokens, o.max_num_seqs * o.max_model_len))   # the largest step there can be
         per_req = min(o.max_model_len, n_tok)
         n_req = max(1, min(n_tok // per_req, o.max_num_seqs))
         pages = n_req * ((per_req + o.block_size - 1) // o.block_size)
@@ -181,6 +183,7 @@ class LLM:
             return ([], None) if want_logits else []
         logits = self.core.run(entries)
         reqs = self.scheduler.sample_requests()
+        self.last_sampled_ids = [r[0] for r in reqs]     # the requests of the logits' rows, in row order
         sampled: List[int] = []
         if reqs:
             if any(r[6] for r in reqs):

@@ -8,8 +8,8 @@ import torch
 from ..config.model_config import read_config_json
 from ..models.causal_lm import CausalLM
 from ..models.registry import resolve
-from ..weights.loader import load_checked
-from ..weights.random_init import random_weights, write_model_folder
+from ..weights.loader import kept_dtype, load_checked
+from ..weights.random_init import random_tensor, random_weights, write_model_folder
 
 DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -26,15 +26,23 @@ def load_model(folder: str, dtype: torch.dtype, device) -> Tuple[object, CausalL
     config_dict = read_config_json(folder)
     cfg, plan = resolve(config_dict, where=f"{folder}/config.json")
     model = CausalLM(plan, dtype, device)
-    model.load(load_checked(folder, model.tensor_specs(), dtype, device))
+    model.unexpected_tensors = []      # names the folder holds and the model does not use (ignored, with a warning)
+    model.load(load_checked(folder, model.tensor_specs(), dtype, device, unexpected=model.unexpected_tensors))
     return cfg, model
 
 
-def random_model(config_dict: dict, seed: int, dtype: torch.dtype, device, scheme: str = "fan_in"):
-    """The model of `config_dict` with seeded random weights made directly on the device."""
+def random_model(config_dict: dict, seed: int, dtype: torch.dtype, device, scheme: str = "fan_in",
+                 draw_on: Optional[str] = None):
+    """The model of `config_dict` with seeded random weights.  They are drawn directly on the device (fast at any
+    size; the device's generator) unless `draw_on="cpu"`: then every tensor is drawn by the host's generator, which
+    gives the values that `write_random_model_folder` stores for the same seed, and moved to the device."""
     cfg, plan = resolve(config_dict, where="config")
     model = CausalLM(plan, dtype, device)
-    model.load(random_weights(model.tensor_specs(), seed, scheme, device, dtype))
+    if draw_on is None or torch.device(draw_on) == torch.device(device):
+        model.load(random_weights(model.tensor_specs(), seed, scheme, device, dtype))
+    else:
+        model.load({s.name: random_tensor(s, seed, scheme, draw_on, torch.float32).to(
+            device=device, dtype=kept_dtype(s.role, dtype)) for s in model.tensor_specs()})
     return cfg, model
 
 

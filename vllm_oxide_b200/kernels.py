@@ -62,6 +62,11 @@ def has_fast_attention(dtype, head_dim: int, group: int) -> bool:
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256 and group <= 16
 
 
+def sm_count() -> int:
+    """The number of SMs of the current device (the library asks the device once)."""
+    return int(lib().vob_sm_count())
+
+
 launch_count = 0   # launches of this package's own kernels since import (bench.py reports the difference)
 
 
@@ -319,6 +324,16 @@ def gemm_skinny(x, w, out, epilogue: int, err, norm_weight=None, eps: float = 0.
     map_x = tensor_map(x, 8 if M <= 8 else 16, 4)
     _check(lib().vob_gemm_skinny(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, _p(norm_weight),
                                  ctypes.c_float(eps), _p(err), _stream()), "gemm_skinny")
+
+
+def gemm_skinny_set_wait_limit(tries: int, withhold_copies: bool = False) -> None:
+    """For tests of the bounded waits: after `tries` attempts a pipeline wait of the weight-streaming product gives up
+    (0 restores the default); with `withhold_copies` its producers issue no copy, so the waits are for something that
+    never comes.  The kernel then sets the timeout bits of the error word and returns without writing."""
+    torch.cuda.synchronize()
+    code = lib().vob_gemm_skinny_set_wait_limit(ctypes.c_uint(tries), int(withhold_copies))
+    if code != 0:
+        raise KernelError(f"gemm_skinny_set_wait_limit: {lib().vob_error_string(code).decode()}")
 
 
 def sample(logits, temperature, top_k, top_p, keys, out, num_rows: int) -> None:

@@ -121,7 +121,7 @@ class Attention(Mixer):
         B = ctx.launch_requests
         if ctx.num_decode > 0:
             keys = ctx.max_context if self.window == 0 else min(ctx.max_context, self.window)
-            splits = decode_splits(B, self.kvh, keys)
+            splits = decode_splits(B, self.kvh, keys, kernels.sm_count())
             n = kernels.attention_decode_scratch_floats(self.hd, B, self.nh, splits)
             scratch = ctx.ws.get_flat("attention_decode_scratch", n, torch.float32) if n else None
             kernels.attention_decode(qkv, q_stride, out, cache.k, cache.v, tables, ctx.cu_q, ctx.context_lens, B, self.nh,
@@ -131,14 +131,17 @@ class Attention(Mixer):
                                       ctx.max_q, self.nh, self.kvh, self.hd, self.window, self.scale, ctx.err)
 
 
-def decode_splits(num_requests: int, kv_heads: int, max_keys: int) -> int:
+DECODE_BLOCKS_PER_SM = 2   # blocks of the decode attention kernel that fit an SM (its shared memory decides)
+
+
+def decode_splits(num_requests: int, kv_heads: int, max_keys: int, num_sms: int) -> int:
     """Splits of the key range per (request, kv head): as many as keep every block resident at once
-    (two blocks per SM on 148 SMs), but at least two 64-key tiles per split.  Up to 8 the blocks of a
+    (DECODE_BLOCKS_PER_SM blocks on each of the device's SMs), but at least two 64-key tiles per split.  Up to 8 the blocks of a
     (request, kv head) merge their results as a thread-block cluster, without a second kernel; beyond that a second
     kernel merges them, which pays only for few requests with long contexts (one request of 32,000 keys: 56 us with
     8 splits, 44 us with 16), so more than 8 are taken only from 8,192 keys on and only if at least 12 fit."""
     tiles = -(-max_keys // 64)
-    fit = (2 * 148) // max(1, num_requests * kv_heads)
+    fit = (DECODE_BLOCKS_PER_SM * num_sms) // max(1, num_requests * kv_heads)
     splits = max(1, min(fit, tiles // 2, 16 if tiles >= 128 else 8))
     return splits if splits <= 8 or splits >= 12 else 8
 

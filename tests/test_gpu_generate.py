@@ -201,6 +201,56 @@ def test_command_line(model_folders, plain_models):
     assert [int(t) for t in proc.stdout.split()] == P.greedy_generate(cfg, w, prompt, 6, torch.float32)
 
 
+def test_command_line_with_random_weights_and_no_model_folder(model_folders, plain_models, tmp_path):
+    """`--random-weights --config <config.json> --seed N` builds the model from the configuration and the seed alone and
+    generates the tokens that the plain implementation generates from the folder written with the same seed."""
+    name = "B"
+    cfg, w = plain_models[name]                         # the folder the fixtures wrote with TINY[name]["seed"]
+    prompt = tokens_for(name, 11, salt=4)
+    config = tmp_path / "config.json"
+    config.write_text(open(os.path.join(model_folders[name], "config.json")).read())
+    base = [sys.executable, os.path.join(ROOT, "bin", "vllm-oxide"), "--token-ids", "--max-tokens", "7", "--dtype", "float32",
+            "--max-model-len", "128", "--block-size", "32", "--num-kv-blocks", "8", "--ignore-eos"]
+    proc = subprocess.run(base + ["--random-weights", "--config", str(config), "--seed", str(TINY[name]["seed"]),
+                                  " ".join(map(str, prompt))], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [int(t) for t in proc.stdout.split()] == P.greedy_generate(cfg, w, prompt, 7, torch.float32)
+    other = subprocess.run(base + ["--random-weights", "--config", str(config), "--seed", "99", " ".join(map(str, prompt))],
+                           capture_output=True, text=True, timeout=600)
+    assert other.returncode == 0 and other.stdout != proc.stdout                 # another seed, another model
+    for bad in (["--random-weights"], ["--random-weights", "--config", str(config), "-m", model_folders[name]], []):
+        refused = subprocess.run(base + bad + ["1 2 3"], capture_output=True, text=True, timeout=600)
+        assert refused.returncode == 2 and "--" in refused.stderr
+
+
+def test_a_folder_with_tensors_the_model_does_not_use_loads_and_generates(model_folders, plain_models, tmp_path):
+    """A checkpoint with tied output that also stores lm_head.weight (as published small checkpoints do) and rotary
+    buffers: the extra tensors are reported and ignored, and the tokens are the plain implementation's."""
+    import shutil
+    import warnings
+    from vllm_oxide_b200 import LLM, EngineOptions, SamplingParams
+    from vllm_oxide_b200.weights import SafetensorsFile, write_safetensors
+    from vllm_oxide_b200.weights.loader import UnexpectedTensorsWarning
+    name = "A"                                          # tied output
+    cfg, w = plain_models[name]
+    folder = str(tmp_path / "m")
+    shutil.copytree(model_folders[name], folder)
+    f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    tensors = {n: f.tensor(n).clone() for n in f.names()}
+    tensors["lm_head.weight"] = torch.randn(256, 64)    # not the embedding: it must not be read
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    del f
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    with warnings.catch_warnings(record=True) as caught:
+        warnings.simplefilter("always")
+        llm = LLM(folder, EngineOptions(max_model_len=128, block_size=16, num_kv_blocks=16, dtype="float32"))
+    assert any(issubclass(c.category, UnexpectedTensorsWarning) for c in caught)
+    assert llm.model.unexpected_tensors == ["lm_head.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
+    prompt = tokens_for(name, 12, salt=9)
+    assert llm.generate([prompt], SamplingParams(max_tokens=8, ignore_eos=True))[0].token_ids == \
+        P.greedy_generate(cfg, w, prompt, 8, torch.float32)
+
+
 def greedy_tokens_agree_with_32_bit_logits(runner, prompt, tokens, what):
     """The tokens a bfloat16 engine chose greedily, fed to the 32-bit engine (`runner`, a float32 TraceRunner over the same
     weights): wherever the 32-bit logits have a clear winner (a gap of 5 % of the largest logit) it is the token that

@@ -97,6 +97,7 @@ def test_silu_mul(dtype):
 @pytest.mark.parametrize("norm,bias", [(True, False), (False, True)])
 def test_qk_norm_rope_kv_write(dtype, nh, kvh, hd, norm, bias):
     from vllm_oxide_b200 import kernels
+    from vllm_oxide_b200.parts import RotationRule
     T, bs, pages, eps, max_pos, theta = 9, 16, 6, 2e-6, 300, 12345.0
     width = (nh + 2 * kvh) * hd
     qkv = torch.randn(T, width, device=DEV).to(dtype)
@@ -110,7 +111,7 @@ def test_qk_norm_rope_kv_write(dtype, nh, kvh, hd, norm, bias):
     vc = torch.full((pages, kvh, bs, hd), 7.0, device=DEV).to(dtype)
     out = qkv.clone()
     err = err_word()
-    kernels.qk_norm_rope_kv_write(out, b, pos, slots, wq, wk, table.to(DEV), kc, vc, T, nh, kvh, hd, eps, True, err)
+    kernels.qk_norm_rope_kv_write(out, b, pos, slots, wq, wk, RotationRule(table.to(DEV), hd), kc, vc, T, nh, kvh, hd, eps, True, err)
     assert err.item() == 0
     x = qkv.cpu()
     if bias:
@@ -136,15 +137,15 @@ def test_qk_norm_rope_kv_write(dtype, nh, kvh, hd, norm, bias):
     assert (kflat[~written] == 7).all() and (vflat[~written] == 7).all()     # nothing else was touched
     # a reader of another layer's cache writes nothing
     kc2 = torch.zeros_like(kc)
-    kernels.qk_norm_rope_kv_write(qkv.clone(), b, pos, slots, wq, wk, table.to(DEV), kc2, kc2, T, nh, kvh, hd, eps, False, err)
+    kernels.qk_norm_rope_kv_write(qkv.clone(), b, pos, slots, wq, wk, RotationRule(table.to(DEV), hd), kc2, kc2, T, nh, kvh, hd, eps, False, err)
     assert kc2.abs().max() == 0
     # positions beyond the table and slots beyond the pool are refused, not read
     badpos = pos.clone(); badpos[0] = 300
-    kernels.qk_norm_rope_kv_write(qkv.clone(), b, badpos, slots, wq, wk, table.to(DEV), kc, vc, T, nh, kvh, hd, eps, True, err)
+    kernels.qk_norm_rope_kv_write(qkv.clone(), b, badpos, slots, wq, wk, RotationRule(table.to(DEV), hd), kc, vc, T, nh, kvh, hd, eps, True, err)
     assert err.item() & 2
     err.zero_()
     badslot = slots.clone(); badslot[1] = pages * bs
-    kernels.qk_norm_rope_kv_write(qkv.clone(), b, pos, badslot, wq, wk, table.to(DEV), kc, vc, T, nh, kvh, hd, eps, True, err)
+    kernels.qk_norm_rope_kv_write(qkv.clone(), b, pos, badslot, wq, wk, RotationRule(table.to(DEV), hd), kc, vc, T, nh, kvh, hd, eps, True, err)
     assert err.item() & 4
 
 
@@ -156,6 +157,7 @@ def test_qk_norm_rope_kv_write_many_tokens_and_head_sizes(dtype, nh, kvh, hd, T)
     """The rotation kernel picks its shape by head size and token count (16-byte accesses for head sizes that are a power
     of two, four heads a warp from 256 tokens on): each against the plain formulas, with norm and bias together."""
     from vllm_oxide_b200 import kernels
+    from vllm_oxide_b200.parts import RotationRule
     bs, eps, max_pos, theta = 32, 1e-5, 700, 1e6
     pages = -(-T // bs) + 2
     g = torch.Generator().manual_seed(T + hd)
@@ -173,7 +175,7 @@ def test_qk_norm_rope_kv_write_many_tokens_and_head_sizes(dtype, nh, kvh, hd, T)
     vc = torch.full((pages, kvh, bs, hd), 7.0, device=DEV).to(dtype)
     out = qkv.clone()
     err = err_word()
-    kernels.qk_norm_rope_kv_write(out, b, pos, slots, wq, wk, table.to(DEV), kc, vc, T, nh, kvh, hd, eps, True, err)
+    kernels.qk_norm_rope_kv_write(out, b, pos, slots, wq, wk, RotationRule(table.to(DEV), hd), kc, vc, T, nh, kvh, hd, eps, True, err)
     assert err.item() == 0
     q, k, v = P.split_qkv(qkv.cpu() + b.cpu(), nh, kvh, hd)
     q = P.apply_rope(P.head_rms_norm(q, wq.cpu().to(dtype), eps, dtype), pos.cpu(), table, dtype)
@@ -188,6 +190,62 @@ def test_qk_norm_rope_kv_write_many_tokens_and_head_sizes(dtype, nh, kvh, hd, T)
     untouched = torch.ones(pages * bs, dtype=torch.bool)
     untouched[idx] = False
     assert (kflat[untouched] == 7).all() and (vflat[untouched] == 7).all()
+
+def plain_rotation(x, positions, table, rot_dim, interleaved, dt):
+    """Rotation of the first rot_dim elements of every head, in halves or in neighbouring pairs, restated in plain torch:
+    the halves rule with rot_dim = head size is P.apply_rope (crates/vllm-oxide/src/layers/rope.rs:129-159)."""
+    if rot_dim == 0:
+        return x
+    it = torch.float64 if dt == torch.float64 else torch.float32
+    cs = table[positions.long()].to(it)
+    half = rot_dim // 2
+    c, s = cs[:, None, :half], cs[:, None, half:]
+    xf = x.to(it)
+    rot, rest = xf[..., :rot_dim], xf[..., rot_dim:]
+    if interleaved:
+        x1, x2 = rot[..., 0::2], rot[..., 1::2]
+        y = torch.stack([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).flatten(-2)
+    else:
+        x1, x2 = rot[..., :half], rot[..., half:]
+        y = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1)
+    return torch.cat([y, rest], dim=-1).to(dt)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,kvh,hd,rot,interleaved", [(4, 2, 64, 32, False), (4, 2, 64, 64, True), (6, 1, 48, 16, True),
+                                                        (3, 3, 80, 0, False), (8, 2, 128, 64, False), (2, 1, 16, 2, True)])
+def test_qk_norm_rope_kv_write_other_position_rules(dtype, nh, kvh, hd, rot, interleaved):
+    """The position rule is an argument of the kernel: a rotation of only the first elements of a head, neighbouring
+    pairs instead of halves, or no rotation at all; norm, bias and the cache write as with the stock rule."""
+    from vllm_oxide_b200 import kernels
+    from vllm_oxide_b200.parts import RotationRule
+    T, bs, eps, max_pos, theta = 37, 16, 1e-5, 200, 5e4
+    pages = -(-T // bs) + 1
+    g = torch.Generator().manual_seed(hd + rot)
+    width = (nh + 2 * kvh) * hd
+    qkv = torch.randn(T, width, generator=g).to(dtype).to(DEV)
+    b = (0.1 * torch.randn(width, generator=g)).to(dtype).to(DEV)
+    wq = (1 + 0.1 * torch.randn(hd, generator=g)).to(dtype).float().to(DEV)
+    wk = (1 + 0.1 * torch.randn(hd, generator=g)).to(dtype).float().to(DEV)
+    pos = torch.randint(0, max_pos, (T,), generator=g).int().to(DEV)
+    slots = torch.randperm(pages * bs, generator=g)[:T].int().to(DEV)
+    table = P.rope_table(rot, max_pos, theta) if rot else None
+    rule = RotationRule(table.to(DEV) if rot else None, rot, interleaved)
+    kc = torch.full((pages, kvh, bs, hd), 7.0, device=DEV).to(dtype)
+    vc = torch.full((pages, kvh, bs, hd), 7.0, device=DEV).to(dtype)
+    out = qkv.clone()
+    err = err_word()
+    kernels.qk_norm_rope_kv_write(out, b, pos, slots, wq, wk, rule, kc, vc, T, nh, kvh, hd, eps, True, err)
+    assert err.item() == 0
+    q, k, v = P.split_qkv(qkv.cpu() + b.cpu(), nh, kvh, hd)
+    q = plain_rotation(P.head_rms_norm(q, wq.cpu().to(dtype), eps, dtype), pos.cpu(), table, rot, interleaved, dtype)
+    k = plain_rotation(P.head_rms_norm(k, wk.cpu().to(dtype), eps, dtype), pos.cpu(), table, rot, interleaved, dtype)
+    assert torch.allclose(out[:, :nh * hd].reshape(T, nh, hd).cpu().float(), q.float(), **tol(dtype))
+    kflat = kc.permute(0, 2, 1, 3).reshape(pages * bs, kvh, hd).cpu()
+    vflat = vc.permute(0, 2, 1, 3).reshape(pages * bs, kvh, hd).cpu()
+    idx = slots.cpu().long()
+    assert torch.allclose(kflat[idx].float(), k.float(), **tol(dtype))
+    assert torch.equal(vflat[idx], v.to(dtype))
 
 
 def paged_setup(dtype, kvh, hd, bs, ctx_lens, g):

@@ -198,10 +198,14 @@ def register_routed_toy():
     from vllm_oxide_b200.weights import TensorSpec
 
     class LinearAngles(PositionEncoding):
-        """Another table for the attention part's rotation: the interface is the `cos_sin` attribute."""
+        """Another table for the attention part's rotation: the interface is `rotation_rule()`."""
 
         def __init__(self, device=None, **_):
             self.cos_sin = toy_angles().contiguous().to(device)
+
+        def rotation_rule(self):
+            from vllm_oxide_b200.parts import RotationRule
+            return RotationRule(self.cos_sin, HD, False)
 
     class Top1Experts(FeedForward):
         """Each token goes to the expert with the largest router logit (float, ties to the lowest index):
@@ -346,3 +350,283 @@ def test_unknown_parts_and_bad_orders_are_refused():
     plan.order = [ExecStep(0, 0), ExecStep(0, 0)]
     with pytest.raises(ValueError, match="written by two runs"):
         plan.validate()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Another position rule for the STOCK attention part: the first half of every head rotated in neighbouring pairs in one
+# layer, no rotation at all in the next.  Only a plan is defined here; parts and kernels are the framework's.
+ROT = HD // 2
+
+
+def register_partial_rotary_toy():
+    from vllm_oxide_b200.models import ExecStep, ModelPlan, register_architecture
+    from vllm_oxide_b200.parts import PartSpec
+
+    @dataclass
+    class ToyConfig:
+        raw: dict
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+    def norm(name):
+        return PartSpec("rmsnorm", dict(size=H, eps=EPS, weight_name=name))
+
+    def plan(cfg):
+        def layer(i, position):
+            p = f"toy.layers.{i}."
+            return PartSpec("pre_norm", dict(
+                mixer=PartSpec("attention", dict(hidden_size=H, num_heads=NH, num_kv_heads=KVH, head_dim=HD, eps=EPS,
+                                                 qkv_bias=False, qk_norm=True, window=None, position=position,
+                                                 prefix=p + "self_attn.")),
+                feed_forward=PartSpec("swiglu", dict(hidden_size=H, intermediate_size=I, prefix=p + "mlp.")),
+                input_norm=norm(p + "input_layernorm.weight"), post_mixer_norm=norm(p + "post_attention_layernorm.weight")))
+        return ModelPlan(
+            architecture="ToyPartialRotaryForCausalLM", hidden_size=H, vocab_size=V, max_position=MAXPOS,
+            embedding_name="toy.embed.weight", lm_head_name=None, final_norm=norm("toy.norm.weight"),
+            positions={"front_pairs": PartSpec("rope", dict(head_dim=HD, max_position=MAXPOS, theta=THETA, rotary_dim=ROT,
+                                                            interleaved=True))},
+            layers=[layer(0, "front_pairs"), layer(1, None)],
+            order=[ExecStep(0, 0), ExecStep(1, 1)])
+
+    register_architecture("ToyPartialRotaryForCausalLM", ToyConfig.from_dict, plan)
+
+
+def plain_partial_rotary(weights, tokens, dt):
+    """The same model from the plain parts; the rotation is restated here: elements 2i and 2i + 1 (i < ROT / 2) of a head
+    turn by angle i of the position, the rest of the head passes through."""
+    ids = torch.as_tensor(tokens)
+    pos = torch.arange(len(tokens))
+    table = P.rope_table(ROT, MAXPOS, THETA)           # [max_pos, ROT]: cos of ROT/2 angles, then sin
+
+    def rotate_front_pairs(x):
+        it = torch.float64 if dt == torch.float64 else torch.float32
+        cs = table[pos].to(it)
+        c, s = cs[:, None, :ROT // 2], cs[:, None, ROT // 2:]
+        xf = x.to(it)
+        x1, x2 = xf[..., 0:ROT:2], xf[..., 1:ROT:2]
+        y = torch.stack([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).flatten(-2)
+        return torch.cat([y, xf[..., ROT:]], dim=-1).to(dt)
+
+    hidden, residual = P.embedding(weights["toy.embed.weight"], ids, dt), None
+    for i, rotate in ((0, rotate_front_pairs), (1, lambda x: x)):
+        p = f"toy.layers.{i}."
+        normed, residual = P.add_rms_norm(hidden, residual, weights[p + "input_layernorm.weight"], EPS, dt)
+        q = P.linear(normed, weights[p + "self_attn.q_proj.weight"], dt)
+        k = P.linear(normed, weights[p + "self_attn.k_proj.weight"], dt)
+        v = P.linear(normed, weights[p + "self_attn.v_proj.weight"], dt)
+        q, k, v = P.split_qkv(torch.cat([q, k, v], -1), NH, KVH, HD)
+        q = rotate(P.head_rms_norm(q, weights[p + "self_attn.q_norm.weight"], EPS, dt))
+        k = rotate(P.head_rms_norm(k, weights[p + "self_attn.k_norm.weight"], EPS, dt))
+        a = P.linear(P.attention(q, k, v, pos, None, dt), weights[p + "self_attn.o_proj.weight"], dt)
+        normed, residual = P.add_rms_norm(a, residual, weights[p + "post_attention_layernorm.weight"], EPS, dt)
+        hidden = P.swiglu(normed, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"],
+                          weights[p + "mlp.down_proj.weight"], dt)
+    hf, _ = P.add_rms_norm(hidden, residual, weights["toy.norm.weight"], EPS, dt)
+    return P.linear(hf, weights["toy.embed.weight"], dt).double().numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_another_position_rule_needs_only_a_plan(tmp_path, dtype):
+    """Partial rotation in neighbouring pairs in one layer and no rotation in the other, with the stock attention part
+    and its kernels: whole, and decoded token by token after a portion, against the plain form above."""
+    from vllm_oxide_b200.engine.loading import write_random_model_folder
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    register_partial_rotary_toy()
+    folder = str(tmp_path / "partial")
+    write_random_model_folder(folder, dict(architectures=["ToyPartialRotaryForCausalLM"]), 21, "fan_in", torch.float32)
+    _, weights = P.read_folder(folder)
+    g = torch.Generator().manual_seed(6)
+    toks = torch.randint(0, V, (70,), generator=g).tolist()
+    dt = torch.float64 if dtype == "float32" else torch.bfloat16
+    want = plain_partial_rotary(weights, toks, dt)
+    scale = np.abs(want).max()
+    bound = 2e-5 if dtype == "float32" else 0.04
+    r = TraceRunner(folder, dtype, 80, 16)
+    whole = r.step([dict(id="w", tokens=toks, want=list(range(70)))], ["w"])
+    assert np.abs(whole.astype(np.float64) - want).max() / scale < bound
+    rows = [r.step([dict(id="d", tokens=toks[:37], want=list(range(37)))], [])]
+    rows += [r.step([dict(id="d", tokens=[t], want=[0])], []) for t in toks[37:]]
+    assert np.abs(np.concatenate(rows).astype(np.float64) - want).max() / scale < bound
+    # and the rule matters: the stock rule on the same weights gives other logits
+    assert np.abs(want - plain_toy_stock_rule(weights, toks, dt)).max() / scale > 3 * bound
+
+
+def plain_toy_stock_rule(weights, tokens, dt):
+    """The two layers with the reference's rule (the whole head in halves, both layers), to show that the test above
+    would see a rule that was not applied."""
+    ids = torch.as_tensor(tokens)
+    pos = torch.arange(len(tokens))
+    table = P.rope_table(HD, MAXPOS, THETA)
+    hidden, residual = P.embedding(weights["toy.embed.weight"], ids, dt), None
+    for i in (0, 1):
+        p = f"toy.layers.{i}."
+        normed, residual = P.add_rms_norm(hidden, residual, weights[p + "input_layernorm.weight"], EPS, dt)
+        q = P.linear(normed, weights[p + "self_attn.q_proj.weight"], dt)
+        k = P.linear(normed, weights[p + "self_attn.k_proj.weight"], dt)
+        v = P.linear(normed, weights[p + "self_attn.v_proj.weight"], dt)
+        q, k, v = P.split_qkv(torch.cat([q, k, v], -1), NH, KVH, HD)
+        q = P.apply_rope(P.head_rms_norm(q, weights[p + "self_attn.q_norm.weight"], EPS, dt), pos, table, dt)
+        k = P.apply_rope(P.head_rms_norm(k, weights[p + "self_attn.k_norm.weight"], EPS, dt), pos, table, dt)
+        a = P.linear(P.attention(q, k, v, pos, None, dt), weights[p + "self_attn.o_proj.weight"], dt)
+        normed, residual = P.add_rms_norm(a, residual, weights[p + "post_attention_layernorm.weight"], EPS, dt)
+        hidden = P.swiglu(normed, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"],
+                          weights[p + "mlp.down_proj.weight"], dt)
+    hf, _ = P.add_rms_norm(hidden, residual, weights["toy.norm.weight"], EPS, dt)
+    return P.linear(hf, weights["toy.embed.weight"], dt).double().numpy()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# A mixer that keeps ONE tensor a token in pages (a latent), in pages of its own size and in float32, beside a stock
+# attention layer that keeps keys and values in the engine's pages: two cache groups, two block tables per request.
+LW, LATENT_PAGE = 24, 8
+
+
+def register_latent_toy():
+    from vllm_oxide_b200.models import ExecStep, ModelPlan, register_architecture
+    from vllm_oxide_b200.parts import CacheSpec, Mixer, PartSpec, register_part
+    from vllm_oxide_b200.weights import TensorSpec
+
+    class LatentMeanMixer(Mixer):
+        """c_t = x_t Wc^T is written to the pages (one float32 tensor of LW elements a token); y_t = mean(c_0..c_t) Wo^T
+        is computed from the pages through the block table, so it sees earlier portions and nothing of other requests."""
+
+        def __init__(self, hidden_size, latent, prefix, **_):
+            self.H, self.L, self.prefix = hidden_size, latent, prefix
+
+        def tensor_specs(self):
+            return [TensorSpec(self.prefix + "compress.weight", (self.L, self.H), "matrix", self.H),
+                    TensorSpec(self.prefix + "expand.weight", (self.H, self.L), "matrix", self.L)]
+
+        def load(self, tensors):
+            self.wc, self.wo = tensors[self.prefix + "compress.weight"], tensors[self.prefix + "expand.weight"]
+
+        def cache_spec(self):
+            return CacheSpec(kv_heads=1, head_dim=self.L, tensors=1, block_size=LATENT_PAGE, dtype=torch.float32)
+
+        def forward(self, x, ctx, cache, state, write_cache=True):
+            assert cache.v is None and cache.k.dtype == torch.float32 and cache.block_size == LATENT_PAGE
+            T = ctx.num_tokens
+            c = x[:T].float() @ self.wc.float().t()
+            flat = cache.k.view(-1, self.L)                                  # [pages * page size, L]: one row a slot
+            flat[ctx.slot_mapping[cache.group][:T].long()] = c
+            cu, lens = ctx.host_view("cu_q"), ctx.host_view("context_lens")
+            out = torch.zeros_like(x)
+            for r in range(ctx.num_requests):
+                n, end = int(cu[r + 1] - cu[r]), int(lens[r])
+                pages = ctx.block_tables[cache.group][r, :(end + LATENT_PAGE - 1) // LATENT_PAGE].long()
+                seen = cache.k[pages].reshape(-1, self.L)[:end]              # the latents of positions 0 .. end-1
+                means = seen.cumsum(0)[end - n:] / torch.arange(end - n + 1, end + 1, device=x.device)[:, None]
+                out[int(cu[r]):int(cu[r + 1])] = (means @ self.wo.float().t()).to(x.dtype)
+            return out
+
+    register_part("mixer", "toy_latent_mean", LatentMeanMixer)
+
+    @dataclass
+    class ToyConfig:
+        raw: dict
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+    def norm(name):
+        return PartSpec("rmsnorm", dict(size=H, eps=EPS, weight_name=name))
+
+    def plan(cfg):
+        def layer(i, mixer):
+            p = f"toy.layers.{i}."
+            return PartSpec("pre_norm", dict(
+                mixer=mixer(p), feed_forward=PartSpec("swiglu", dict(hidden_size=H, intermediate_size=I, prefix=p + "mlp.")),
+                input_norm=norm(p + "input_layernorm.weight"), post_mixer_norm=norm(p + "post_attention_layernorm.weight")))
+        attention = lambda p: PartSpec("attention", dict(hidden_size=H, num_heads=NH, num_kv_heads=KVH, head_dim=HD, eps=EPS,
+                                                        qkv_bias=False, qk_norm=True, window=None, position="rope",
+                                                        prefix=p + "self_attn."))
+        latent = lambda p: PartSpec("toy_latent_mean", dict(hidden_size=H, latent=LW, prefix=p + "latent."))
+        return ModelPlan(
+            architecture="ToyLatentForCausalLM", hidden_size=H, vocab_size=V, max_position=MAXPOS,
+            embedding_name="toy.embed.weight", lm_head_name=None, final_norm=norm("toy.norm.weight"),
+            positions={"rope": PartSpec("rope", dict(head_dim=HD, max_position=MAXPOS, theta=THETA))},
+            layers=[layer(0, attention), layer(1, latent)], order=[ExecStep(0, 0), ExecStep(1, 1)])
+
+    register_architecture("ToyLatentForCausalLM", ToyConfig.from_dict, plan)
+
+
+def plain_latent_toy(weights, tokens, dt):
+    ids = torch.as_tensor(tokens)
+    pos = torch.arange(len(tokens))
+    table = P.rope_table(HD, MAXPOS, THETA)
+    hidden, residual = P.embedding(weights["toy.embed.weight"], ids, dt), None
+    p = "toy.layers.0."
+    normed, residual = P.add_rms_norm(hidden, residual, weights[p + "input_layernorm.weight"], EPS, dt)
+    q = P.linear(normed, weights[p + "self_attn.q_proj.weight"], dt)
+    k = P.linear(normed, weights[p + "self_attn.k_proj.weight"], dt)
+    v = P.linear(normed, weights[p + "self_attn.v_proj.weight"], dt)
+    q, k, v = P.split_qkv(torch.cat([q, k, v], -1), NH, KVH, HD)
+    q = P.apply_rope(P.head_rms_norm(q, weights[p + "self_attn.q_norm.weight"], EPS, dt), pos, table, dt)
+    k = P.apply_rope(P.head_rms_norm(k, weights[p + "self_attn.k_norm.weight"], EPS, dt), pos, table, dt)
+    a = P.linear(P.attention(q, k, v, pos, None, dt), weights[p + "self_attn.o_proj.weight"], dt)
+    normed, residual = P.add_rms_norm(a, residual, weights[p + "post_attention_layernorm.weight"], EPS, dt)
+    hidden = P.swiglu(normed, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"],
+                      weights[p + "mlp.down_proj.weight"], dt)
+    p = "toy.layers.1."
+    normed, residual = P.add_rms_norm(hidden, residual, weights[p + "input_layernorm.weight"], EPS, dt)
+    it = torch.float64 if dt == torch.float64 else torch.float32
+    c = normed.to(it) @ weights[p + "latent.compress.weight"].to(dt).to(it).t()
+    means = c.cumsum(0) / torch.arange(1, len(tokens) + 1)[:, None]
+    mixed = (means @ weights[p + "latent.expand.weight"].to(dt).to(it).t()).to(dt)
+    normed, residual = P.add_rms_norm(mixed, residual, weights[p + "post_attention_layernorm.weight"], EPS, dt)
+    hidden = P.swiglu(normed, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"],
+                      weights[p + "mlp.down_proj.weight"], dt)
+    hf, _ = P.add_rms_norm(hidden, residual, weights["toy.norm.weight"], EPS, dt)
+    return P.linear(hf, weights["toy.embed.weight"], dt).double().numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_mixer_with_one_tensor_a_token_in_pages_of_its_own_size(tmp_path, dtype):
+    """The cache allocates what each plane's spec states: keys and values in the engine's pages for the attention layer,
+    ONE float32 tensor a token in pages of 8 for the toy mixer; each group has its own pool and block tables, pages of
+    both are given back and used again, and the logits are the plain form's, whole and cut and mixed."""
+    from vllm_oxide_b200.engine.loading import write_random_model_folder
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    register_latent_toy()
+    folder = str(tmp_path / "latent")
+    write_random_model_folder(folder, dict(architectures=["ToyLatentForCausalLM"]), 31, "fan_in", torch.float32)
+    _, weights = P.read_folder(folder)
+    g = torch.Generator().manual_seed(8)
+    reqs = {name: torch.randint(0, V, (n,), generator=g).tolist() for name, n in (("a", 61), ("b", 30), ("c", 45))}
+    dt = torch.float64 if dtype == "float32" else torch.bfloat16
+    want = {name: plain_latent_toy(weights, toks, dt) for name, toks in reqs.items()}
+
+    def close(got, w, what):
+        worst = np.abs(np.asarray(got, np.float64) - w).max() / np.abs(w).max()
+        assert worst < (2e-5 if dtype == "float32" else 0.04), f"{what}: {worst:.3e}"
+
+    r = TraceRunner(folder, dtype, 96, 16)                       # 6 pages of 16, and 12 pages of 8 for the latents
+    kv, latent = r.cache.planes
+    assert len(r.cache.groups) == 2 and {(g.block_size, g.num_blocks) for g in r.cache.groups} == {(16, 6), (8, 12)}
+    assert latent.v is None and latent.data.shape == (1, 12, 1, 8, LW) and latent.data.dtype == torch.float32
+    assert kv.v is not None and kv.data.shape == (2, 6, KVH, 16, HD) and kv.group != latent.group
+    assert not r.manager.prefix_caching
+    close(r.step([dict(id="a", tokens=reqs["a"], want=list(range(61)))], ["a"]), want["a"], "whole")
+    # a in portions beside b; then c on the pages both gave back
+    got = {name: [] for name in reqs}
+    out = r.step([dict(id="a", tokens=reqs["a"][:19], want=list(range(19)))], [])
+    got["a"].append(out)
+    out = r.step([dict(id="a", tokens=reqs["a"][19:21], want=[0, 1]), dict(id="b", tokens=reqs["b"][:9], want=list(range(9)))], [])
+    got["a"].append(out[:2]); got["b"].append(out[2:])
+    for t in range(21, 61):
+        entries = [dict(id="a", tokens=[reqs["a"][t]], want=[0])]
+        if t - 12 < 30:
+            entries.append(dict(id="b", tokens=[reqs["b"][t - 12]], want=[0]))
+        out = r.step(entries, [e["id"] for e in entries if (e["id"] == "a" and t == 60) or (e["id"] == "b" and t - 12 == 29)])
+        got["a"].append(out[:1])
+        if len(entries) > 1:
+            got["b"].append(out[1:])
+        assert r.manager.check_invariants() == ""
+    got["c"].append(r.step([dict(id="c", tokens=reqs["c"][:40], want=list(range(40)))], []))
+    got["c"].append(r.step([dict(id="c", tokens=reqs["c"][40:], want=list(range(5)))], ["c"]))
+    for name in reqs:
+        close(np.concatenate(got[name]), want[name], f"cut and mixed {name}")
+    assert r.manager.num_free_blocks(0) + r.manager.num_free_blocks(1) == 18

@@ -458,6 +458,78 @@ __global__ void qk_norm_rope_kv_write_wide_kernel(__nv_bfloat16* qkv, const __nv
   store16<T>(dst + i + HALF, o2);
 }
 
+// The same for any position rule, one head a warp: the first `rot_dim` elements of a head are rotated (rot_dim even, at
+// most hd; 0: no rotation at all), in pairs (i, i + rot_dim/2) or, `interleaved`, in pairs (2i, 2i + 1), by the angle i of
+// the token's position; cos_sin is [max_pos, rot_dim]: cos of rot_dim/2 angles, then sin.  The elements from rot_dim on
+// pass through (after bias and norm).  The head goes through shared memory, so that a lane finds its partner whatever the
+// pairing; the two kernels above are the fast path of the rule "rotate the whole head in halves".
+template <typename T>
+__global__ void qk_norm_rope_kv_write_general_kernel(T* qkv, const T* __restrict__ bias, const int* __restrict__ positions,
+                                                     const int* __restrict__ slots, const float* __restrict__ wq,
+                                                     const float* __restrict__ wk, const float* __restrict__ cos_sin,
+                                                     T* __restrict__ kcache, T* __restrict__ vcache, int nh, int kvh, int hd,
+                                                     int rot_dim, int interleaved, float eps, int max_pos, long num_slots,
+                                                     int block_size, int write_kv, int* err) {
+  extern __shared__ float head_rows[];   // [warps][hd]
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  const int total_heads = nh + 2 * kvh;
+  const int pos = positions[t];
+  const int slot = slots ? slots[t] : -1;
+  const bool pos_ok = pos >= 0 && pos < max_pos;
+  pdl_wait();
+  if (head >= total_heads) return;
+  const bool is_q = head < nh, is_k = !is_q && head < nh + kvh;
+  if (!is_q && (!write_kv || slot < 0)) return;
+  if (!is_q && slot >= num_slots) {
+    if (lane == 0) atomicOr(err, VOB_ERR_SLOT);
+    return;
+  }
+  float* x = head_rows + (size_t)warp * hd;
+  T* row = qkv + ((size_t)t * total_heads + head) * hd;
+  const T* brow = bias ? bias + (size_t)head * hd : nullptr;
+  float ss = 0.f;
+  for (int d = lane; d < hd; d += 32) {
+    float v = to_f<T>(row[d]);
+    if (brow) v = round_to<T>(v + to_f<T>(brow[d]));
+    x[d] = v;
+    ss = __fmaf_rn(v, v, ss);
+  }
+  if (!is_q && !is_k) {   // value head: copy
+    T* dst = vcache + (((size_t)(slot / block_size) * kvh + (head - nh - kvh)) * block_size + slot % block_size) * hd;
+    for (int d = lane; d < hd; d += 32) dst[d] = from_f<T>(x[d]);
+    return;
+  }
+  if (rot_dim > 0 && !pos_ok) {
+    if (lane == 0) atomicOr(err, VOB_ERR_POSITION);
+    return;
+  }
+  const float* w = is_q ? wq : wk;
+  if (w) {
+    ss = warp_sum(ss);
+    const float denom = sqrtf(ss / (float)hd + eps);
+    for (int d = lane; d < hd; d += 32) x[d] = round_to<T>(round_to<T>(x[d] / denom) * w[d]);
+  }
+  __syncwarp();
+  T* dst = is_q ? row : kcache + (((size_t)(slot / block_size) * kvh + (head - nh)) * block_size + slot % block_size) * hd;
+  const int half = rot_dim >> 1;
+  const float* cs = cos_sin + (size_t)pos * rot_dim;
+  for (int d = lane; d < hd; d += 32) {
+    float y = x[d];
+    if (d < rot_dim) {
+      const bool first = interleaved ? !(d & 1) : d < half;
+      const int i = interleaved ? d >> 1 : (first ? d : d - half);
+      const int partner = interleaved ? d ^ 1 : (first ? d + half : d - half);
+      const float c = cs[i], sn = cs[half + i];
+      y = first ? __fsub_rn(__fmul_rn(x[d], c), __fmul_rn(x[partner], sn)) : __fadd_rn(__fmul_rn(x[d], c), __fmul_rn(x[partner], sn));
+    }
+    dst[d] = from_f<T>(y);
+  }
+}
+
+
 // ---------------------------------------------------------------- page copy (utility)
 template <typename T>
 __global__ void copy_pages_kernel(T* cache, const int* __restrict__ pairs, size_t page_elems) {
@@ -536,13 +608,32 @@ VOB_API int vob_silu_mul(const void* gu, void* out, int T, int I, int interleave
   return VOB_BAD_ARGUMENT;
 }
 
+// The position rule: the first rot_dim elements of every q and k head are rotated (rot_dim even, <= hd; 0: none, cos_sin
+// may then be null), in halves or, `interleaved`, in neighbouring pairs; cos_sin is float [max_pos, rot_dim].
 VOB_API int vob_qk_norm_rope_kv_write(void* qkv, const void* bias, const int* positions, const int* slots,
                                       const float* wq, const float* wk, const float* cos_sin, void* kcache, void* vcache,
-                                      int T, int nh, int kvh, int hd, float eps, int max_pos, long num_slots,
-                                      int block_size, int write_kv, int dtype, int* err, cudaStream_t stream) {
+                                      int T, int nh, int kvh, int hd, int rot_dim, int interleaved, float eps, int max_pos,
+                                      long num_slots, int block_size, int write_kv, int dtype, int* err,
+                                      cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd <= 0 || hd % 2 || hd > 512 || block_size <= 0) return VOB_UNSUPPORTED;
   if ((wq == nullptr) != (wk == nullptr)) return VOB_BAD_ARGUMENT;
+  if (rot_dim < 0 || rot_dim > hd || rot_dim % 2 || (rot_dim > 0 && !cos_sin)) return VOB_BAD_ARGUMENT;
+  if (rot_dim != hd || interleaved) {
+    const int warps = 4;
+    dim3 grid(T, (nh + 2 * kvh + warps - 1) / warps);
+    const size_t smem = (size_t)warps * hd * sizeof(float);
+    if (dtype == VOB_F32)
+      return launch_kernel(qk_norm_rope_kv_write_general_kernel<float>, grid, warps * 32, smem, stream, (float*)qkv,
+                           (const float*)bias, positions, slots, wq, wk, cos_sin, (float*)kcache, (float*)vcache, nh, kvh, hd,
+                           rot_dim, interleaved, eps, max_pos, num_slots, block_size, write_kv, err);
+    if (dtype == VOB_BF16)
+      return launch_kernel(qk_norm_rope_kv_write_general_kernel<__nv_bfloat16>, grid, warps * 32, smem, stream,
+                           (__nv_bfloat16*)qkv, (const __nv_bfloat16*)bias, positions, slots, wq, wk, cos_sin,
+                           (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nh, kvh, hd, rot_dim, interleaved, eps, max_pos,
+                           num_slots, block_size, write_kv, err);
+    return VOB_BAD_ARGUMENT;
+  }
   if (dtype == VOB_BF16 && hd >= 16 && (hd & (hd - 1)) == 0 &&
       (((uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)cos_sin | (uintptr_t)wq | (uintptr_t)wk) % 16) == 0) {
     // head sizes that are a power of two: 16-byte accesses, hd / 16 lanes a head

@@ -77,7 +77,8 @@ class EngineCore:
         self.manager = cache.manager
         self.max_tokens, self.max_seqs, self.max_model_len = max_num_batched_tokens, max_num_seqs, max_model_len
         self.num_groups = len(cache.groups)
-        self.max_pages = (max_model_len + cache.block_size - 1) // cache.block_size
+        # width of the block tables: the pages of a request of max_model_len in the group with the smallest pages
+        self.max_pages = max((max_model_len + g.block_size - 1) // g.block_size for g in cache.groups)
         cap = host.BatchLayout(self.max_tokens, self.max_seqs, self.max_tokens, self.num_groups, self.max_pages).total
         # a decode step replayed from a graph is padded to the next batch size that has one, which may be more
         # requests (and tokens) than a step may hold: the staging buffers take that layout too

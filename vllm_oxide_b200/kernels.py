@@ -131,15 +131,23 @@ def silu_mul(gate_up, out, num_tokens: int, interleaved: bool = False) -> None:
            "silu_mul")
 
 
-def qk_norm_rope_kv_write(qkv, bias, positions, slots, wq, wk, cos_sin, kcache, vcache, num_tokens, nh, kvh, hd,
+def qk_norm_rope_kv_write(qkv, bias, positions, slots, wq, wk, rule, kcache, vcache, num_tokens, nh, kvh, hd,
                           eps, write_kv: bool, err) -> None:
-    _cuda(qkv, positions, slots, cos_sin, kcache, vcache)
+    """Bias, per-head norm, rotation and cache write of a merged q|k|v row.  `rule` is the position encoding's
+    `RotationRule` (table [max_pos, rotary_dim] float32, rotary_dim, interleaved); a rule with rotary_dim 0 rotates
+    nothing."""
+    table = rule.table if rule.rotary_dim > 0 else None
+    _cuda(qkv, positions, slots, table, kcache, vcache)
+    if table is not None and (table.dtype != torch.float32 or table.shape[1] != rule.rotary_dim or not table.is_contiguous()):
+        raise KernelError(f"the table of angles must be contiguous float32 [max_pos, {rule.rotary_dim}]")
     num_slots = kcache.shape[0] * kcache.shape[2] if kcache is not None else 0
     block_size = kcache.shape[2] if kcache is not None else 1
-    _check(lib().vob_qk_norm_rope_kv_write(_p(qkv), _p(bias), _p(positions), _p(slots), _p(wq), _p(wk), _p(cos_sin),
-                                           _p(kcache), _p(vcache), num_tokens, nh, kvh, hd, ctypes.c_float(eps),
-                                           cos_sin.shape[0], ctypes.c_long(num_slots), block_size, int(write_kv),
-                                           _code(qkv.dtype), _p(err), _stream()), "qk_norm_rope_kv_write")
+    max_pos = table.shape[0] if table is not None else 0
+    _check(lib().vob_qk_norm_rope_kv_write(_p(qkv), _p(bias), _p(positions), _p(slots), _p(wq), _p(wk), _p(table),
+                                           _p(kcache), _p(vcache), num_tokens, nh, kvh, hd, rule.rotary_dim,
+                                           int(rule.interleaved), ctypes.c_float(eps), max_pos, ctypes.c_long(num_slots),
+                                           block_size, int(write_kv), _code(qkv.dtype), _p(err), _stream()),
+           "qk_norm_rope_kv_write")
 
 
 def paged_attention_generic(q, q_stride, out, kcache, vcache, block_tables, token_req, positions, num_tokens, nh, kvh,

@@ -16,7 +16,7 @@ import torch
 
 from .. import kernels
 from ..weights.loader import TensorSpec
-from .base import CacheSpec, Mixer, register_part
+from .base import NO_ROTATION, CacheSpec, Mixer, register_part
 from .linear import linear
 
 
@@ -24,7 +24,7 @@ class Attention(Mixer):
     graph_safe = True
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, eps: float,
-                 qkv_bias: bool, qk_norm: bool, window: Optional[int], position: str, prefix: str,
+                 qkv_bias: bool, qk_norm: bool, window: Optional[int], position: Optional[str], prefix: str,
                  positions: dict, dtype, device, **_):
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
@@ -34,7 +34,11 @@ class Attention(Mixer):
         self.H, self.nh, self.kvh, self.hd = hidden_size, num_heads, num_kv_heads, head_dim
         self.eps, self.qkv_bias, self.qk_norm = float(eps), qkv_bias, qk_norm
         self.window = int(window or 0)
-        self.rope = positions[position]
+        # the position encoding is named by the plan; None (or a part that rotates nothing) leaves q and k as they are
+        if position is not None and position not in positions:
+            raise KeyError(f"the plan names position encoding {position!r}, but has only {sorted(positions)}")
+        encoding = positions[position] if position is not None else None
+        self.rotation = encoding.rotation_rule() if encoding is not None else NO_ROTATION
         self.prefix, self.dtype, self.device = prefix, dtype, device
         self.scale = 1.0 / math.sqrt(head_dim)   # qwen3.rs:204
         self.wqkv = self.wo = self.bqkv = self.wq_norm = self.wk_norm = None
@@ -82,7 +86,7 @@ class Attention(Mixer):
         qkv = linear(x, self.wqkv, ctx.ws.get("qkv", T, width, x.dtype), ctx)
         g = cache.group
         kernels.qk_norm_rope_kv_write(qkv, self.bqkv, ctx.positions, ctx.slot_mapping[g], self.wq_norm, self.wk_norm,
-                                      self.rope.cos_sin, cache.k, cache.v, T, self.nh, self.kvh, self.hd, self.eps,
+                                      self.rotation, cache.k, cache.v, T, self.nh, self.kvh, self.hd, self.eps,
                                       write_cache, ctx.err)
         attn = ctx.ws.get("attn_out", T, self.nh * self.hd, x.dtype)
         self.attend(qkv, width, attn, cache, ctx, T)
@@ -103,7 +107,7 @@ class Attention(Mixer):
         kernels.gemm_skinny(stream, self.wqkv, qkv, kernels.EPI_BF16, ctx.err, norm_weight=norm.weight, eps=norm.eps)
         g = cache.group
         kernels.qk_norm_rope_kv_write(qkv, self.bqkv, ctx.positions, ctx.slot_mapping[g], self.wq_norm, self.wk_norm,
-                                      self.rope.cos_sin, cache.k, cache.v, T, self.nh, self.kvh, self.hd, self.eps,
+                                      self.rotation, cache.k, cache.v, T, self.nh, self.kvh, self.hd, self.eps,
                                       write_cache, ctx.err)
         attn = ctx.ws.get("attn_out", T, self.nh * self.hd, stream.dtype)
         self.attend(qkv, width, attn, cache, ctx, T)

@@ -38,12 +38,20 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class CacheSpec:
-    """What a mixer needs of the paged cache: keys and values of `kv_heads * head_dim` elements per
-    token, all positions (window 0) or the last `window`.  Planes with equal specs share a group:
-    one page pool and one block table per request."""
+    """What a mixer keeps in pages, a token: `tensors` tensors (2: keys and values; 1: a single tensor, e.g. a latent that
+    stands for both) of `kv_heads * head_dim` elements each, for all positions (window 0) or the last `window`; in pages
+    of `block_size` tokens (None: the engine's page size) and in `dtype` (None: the model's).  A plane is stored as
+    [tensors, pages, kv_heads, block_size, head_dim].  Planes with equal windows and page sizes share a group: one page
+    pool and one block table per request, whatever their widths, tensors and dtypes."""
     kv_heads: int
     head_dim: int
     window: int = 0
+    tensors: int = 2
+    block_size: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
+
+    def elements_per_token(self) -> int:
+        return self.tensors * self.kv_heads * self.head_dim
 
 
 @dataclass(frozen=True)
@@ -55,11 +63,13 @@ class StateSpec:
 
 @dataclass
 class CachePlane:
-    """One layer's keys and values: [num_pages, kv_heads, block_size, head_dim] each."""
+    """One layer's pages: `k` (the first, or only, tensor) and `v` (the second, None for a one-tensor plane), each
+    [num_pages, kv_heads, block_size, head_dim]; `data` is both as one tensor [tensors, num_pages, ...]."""
     k: torch.Tensor
-    v: torch.Tensor
+    v: Optional[torch.Tensor]
     group: int
     block_size: int
+    data: Optional[torch.Tensor] = None
 
 
 class Workspace:
@@ -124,8 +134,24 @@ class Norm(Part):
         raise NotImplementedError
 
 
+@dataclass(frozen=True)
+class RotationRule:
+    """What a mixer's kernel needs of a rotary position encoding: the first `rotary_dim` elements of every query and key
+    head are rotated (0: none), in pairs (i, i + rotary_dim/2) or, `interleaved`, in pairs (2i, 2i + 1), by the angles of
+    the token's position in `table`: float32 [max_position, rotary_dim], cos of rotary_dim/2 angles, then their sin."""
+    table: Optional[torch.Tensor]
+    rotary_dim: int
+    interleaved: bool = False
+
+
+NO_ROTATION = RotationRule(None, 0, False)
+
+
 class PositionEncoding(Part):
-    pass
+    def rotation_rule(self) -> RotationRule:
+        """The rule a mixer hands to its rotation kernel; a position encoding that rotates nothing (absolute positions
+        added elsewhere, or none at all) keeps this default."""
+        return NO_ROTATION
 
 
 class Mixer(Part):

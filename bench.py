@@ -10,8 +10,12 @@ of 8 requests whose context starts at 2,048 tokens, and prints ONE JSON line:
   prefill   one 2,048-token prompt in one step; frac = flops / time / peak;
   roofline  the decode step's bytes (every weight once + the cache of the live requests) / time
             against the measured copy bandwidth;
-  points    decode at batch 1 and 64.
-Every timed step reads 15 GB of weights, far more than the 126 MB L2, so nothing stays cached
+  points    decode at batch 1, 16, 32 and 64 with their fractions of the copy bandwidth; the end-to-end rate at batch 1
+            and 64 and the host's time per step (end-to-end minus device) at batch 1, 8 and 64; decode at contexts of
+            8,192 and 32,768 tokens (batch 1 and 8);
+  workloads serving_0_6b: 256 whole requests at Qwen3-0.6B sizes through LLM.generate (continuous batching), with the
+            bytes its steps had to move against the copy bandwidth.
+The cache that the decode steps read was written by a real prefill of random prompts.  Every timed step reads 15 GB of weights, far more than the 126 MB L2, so nothing stays cached
 between iterations.  Peaks come from MEASURED_PEAKS.json beside this file when present.
 
     python bench.py --workload serving-0.6b | mixed-32b
@@ -123,15 +127,31 @@ def prefill_flops(c, T):
     return linear + attention
 
 
+def fill_cache(llm, ids, ctx_len, seed):
+    """Prompts of `ctx_len` random tokens for the requests `ids`, run through the step function in steps of at most the
+    token budget, so that the pages the decode steps will read hold real keys and values."""
+    import torch
+    from vllm_oxide_b200 import host
+    mgr, core = llm.cache.manager, llm.core
+    g = torch.Generator().manual_seed(seed)
+    budget = llm.options.max_num_batched_tokens
+    for rid in ids:
+        toks = torch.randint(0, llm.model.vocab_size, (ctx_len,), generator=g).tolist()
+        for start in range(0, ctx_len, budget):
+            core.run([host.BatchEntry(rid, start, toks[start:start + budget], [])])
+    torch.cuda.synchronize()
+    core.check_errors()
+
+
 def decode_run(llm, batch, steps, warmup, start_ctx):
-    """K decode steps of `batch` requests whose context starts at `start_ctx`, timed on the device.
-    The cache content does not matter for the time: pages are taken without a prefill."""
+    """K decode steps of `batch` requests whose context starts at `start_ctx` (prefilled), timed on the device."""
     import torch
     from vllm_oxide_b200 import host, kernels
     mgr, core, sampler = llm.cache.manager, llm.core, llm.sampler
     ids = list(range(10_000, 10_000 + batch))
     for rid in ids:
         assert mgr.add_request(rid) and mgr.ensure(rid, 0, start_ctx)
+    fill_cache(llm, ids, start_ctx, seed=batch)
     g = torch.Generator().manual_seed(0)
     toks = torch.randint(0, llm.model.vocab_size, (batch, steps + warmup), generator=g).tolist()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -162,15 +182,19 @@ def decode_run(llm, batch, steps, warmup, start_ctx):
 
 
 def e2e_run(llm, batch, steps, warmup):
-    """The same metric through the public calls: prompts of 2,048 host token ids in, tokens out each step."""
+    """The same metric through the public calls: prompts of 2,048 host token ids in, tokens out each step.
+    Returns (tokens a second, host-to-device bytes a step, device-to-host bytes a step, milliseconds a step)."""
     import torch
     from vllm_oxide_b200 import SamplingParams
-    g = torch.Generator().manual_seed(1)
+    g = torch.Generator().manual_seed(100 + batch)       # other prompts in every run: nothing comes from the prefix cache
     prompts = torch.randint(0, llm.model.vocab_size, (batch, PROMPT_LEN), generator=g).tolist()
-    before = llm.scheduler.stats.prefill_tokens
+    entered = lambda: llm.scheduler.stats.prefill_tokens + llm.scheduler.stats.prefix_hit_tokens
+    before = entered()
+    # the first requests decode while the later prompts are still being computed: room for those tokens too
+    room = steps + warmup + 16 + batch * PROMPT_LEN // llm.options.max_num_batched_tokens
     for p in prompts:
-        llm.add_request(p, SamplingParams(temperature=0.0, max_tokens=steps + warmup + 16, ignore_eos=True))
-    while llm.scheduler.stats.prefill_tokens - before < batch * PROMPT_LEN:
+        llm.add_request(p, SamplingParams(temperature=0.0, max_tokens=room, ignore_eos=True))
+    while llm.is_running() and entered() - before < batch * PROMPT_LEN:
         llm.step()                            # prompts, in portions under the token budget
     for _ in range(warmup):
         llm.step()
@@ -186,7 +210,7 @@ def e2e_run(llm, batch, steps, warmup):
     assert llm.scheduler.num_running == batch, "a request finished inside the timed region"
     while llm.is_running():
         llm.step()
-    return batch * steps / dt, h2d // steps, d2h // steps
+    return batch * steps / dt, h2d // steps, d2h // steps, dt / steps * 1e3
 
 
 def prefill_run(llm, T, reps=3, warmup=2):
@@ -228,12 +252,16 @@ WORKLOADS = {
 }
 
 
-def workload_run(name: str) -> int:
-    """Whole requests through the public entry point; prints one JSON line."""
+def workload_run(name: str, pk=None) -> dict:
+    """Whole requests through the public entry point (LLM.generate, wall clock).  Returns the record of the run: rates,
+    steps, mean number of requests in a step, and the bytes its steps had to move (every weight once a step, the cache
+    of every scheduled request's context, and the float logits of every sampled row written by the output product and
+    read by the sampler) against the copy bandwidth."""
     import random
     import torch
     from vllm_oxide_b200 import LLM, EngineOptions, SamplingParams
     w = WORKLOADS[name]
+    pk = pk or peaks()
     cfg = dict(QWEN3_8B)
     cfg.update(w["config"])
     llm = LLM.from_config(cfg, EngineOptions(dtype="bfloat16", **w["options"]), seed=w["seed"], init_scheme="0.02")
@@ -247,23 +275,35 @@ def workload_run(name: str) -> int:
     warm = [[wrng.randrange(cfg["vocab_size"]) for _ in range(len(p))] for p in prompts]
     llm.generate(warm, [sp] * len(warm))
     torch.cuda.synchronize()
+    s0 = llm.scheduler.stats
+    before = (s0.steps, s0.scheduled_requests, s0.context_tokens, s0.sampled_rows)
     t0 = time.perf_counter()
     outs = llm.generate(prompts, [sp] * len(prompts))
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     assert all(o.finished and len(o.token_ids) == w["new"] for o in outs)
-    st = llm.last_stats
-    print(json.dumps({
+    st, s1 = llm.last_stats, llm.scheduler.stats
+    steps, scheduled, context, rows = (b - a for a, b in zip(before, (s1.steps, s1.scheduled_requests, s1.context_tokens,
+                                                                      s1.sampled_rows)))
+    n = model_numbers(cfg)
+    weight_bytes = n["weight_bytes"]       # the layers and the output matrix (tied or not, it is read once a step)
+    moved = steps * weight_bytes + context * n["kv_bytes_per_token"] + rows * cfg["vocab_size"] * 8
+    achieved = moved / dt / 1e9
+    flops = 2 * st.total_tokens * n["linear_params"] + 2 * rows * n["lm_head_params"]
+    return {
         "metric": f"tokens/s over whole requests ({name})", "value": round(st.total_tokens / dt, 1), "unit": "tokens/s",
-        "generated_tokens_per_s": round(w["requests"] * w["new"] / dt, 1), "seconds": round(dt, 3), "steps": st.steps,
-        "preemptions": st.preemptions, "n_gpus": 1, "dtype": "bf16", "impl": "ours",
-        "data": "synthetic token ids, seeded random weights",
+        "generated_tokens_per_s": round(w["requests"] * w["new"] / dt, 1), "seconds": round(dt, 3), "steps": steps,
+        "mean_requests_per_step": round(scheduled / max(steps, 1), 1), "preemptions": st.preemptions,
+        "bytes_per_step_gb": round(moved / max(steps, 1) / 1e9, 3),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "linear_tflops": round(flops / dt / 1e12, 1),
+        "n_gpus": 1, "dtype": "bf16", "impl": "ours", "data": "synthetic token ids, seeded random weights",
         "config": {"model": name, "layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "requests": w["requests"],
                    "prompt_min": lo, "prompt_max": hi, "new_tokens": w["new"], "step_budget": w["options"]["max_num_batched_tokens"],
-                   "pool_pages": w["options"]["num_kv_blocks"], "block_size": w["options"]["block_size"]}}))
-    return 0
+                   "pool_pages": w["options"]["num_kv_blocks"], "block_size": w["options"]["block_size"]}}
 
 
 def main() -> int:
@@ -287,7 +327,8 @@ def main() -> int:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (use --gpus 1)")
         return 2
     if args.workload:
-        return workload_run(args.workload)
+        print(json.dumps(workload_run(args.workload)))
+        return 0
     import torch
     from vllm_oxide_b200 import LLM, EngineOptions
 
@@ -315,14 +356,42 @@ def main() -> int:
     with ClockSampler() as clocks:
         ms, launches, mean_ctx = decode_run(llm, args.batch, steps, warmup, PROMPT_LEN)
     value = args.batch * 1000.0 / ms
-    step_bytes = n["weight_bytes"] + args.batch * mean_ctx * n["kv_bytes_per_token"]
-    achieved = step_bytes / (ms * 1e-3) / 1e9
-    e2e, h2d, d2h = e2e_run(llm, args.batch, steps, warmup)
-    points = {}
+
+    def hbm_frac(batch, ctx, step_ms):
+        return (n["weight_bytes"] + batch * ctx * n["kv_bytes_per_token"]) / (step_ms * 1e-3) / 1e9 / pk["hbm_gbs"]
+    achieved = hbm_frac(args.batch, mean_ctx, ms) * pk["hbm_gbs"]
+    e2e, h2d, d2h, e2e_ms = e2e_run(llm, args.batch, steps, warmup)
+    points, workloads = {}, {}
     if not args.skip_points:
-        for b in (1, 64):
-            pms, _, _ = decode_run(llm, b, min(steps, 32), warmup, PROMPT_LEN)
+        short = min(steps, 32)
+        points[f"host_ms_b{args.batch}"] = round(e2e_ms - ms, 4)
+        for b in (1, 16, 32, 64):
+            pms, _, ctx = decode_run(llm, b, short, warmup, PROMPT_LEN)
             points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+            points[f"frac_b{b}"] = round(hbm_frac(b, ctx, pms), 4)
+            if b in (1, 64):
+                rate, _, _, step_ms = e2e_run(llm, b, short, warmup)
+                points[f"e2e_b{b}"] = round(rate, 1)
+                points[f"host_ms_b{b}"] = round(step_ms - pms, 4)
+        # longer contexts: another engine over the same model (its decode steps are shaped for up to 32,768 keys)
+        config, model = llm.config, llm.model
+        del llm
+        torch.cuda.empty_cache()
+        long_ctx = 32768
+        pages = 8 * (long_ctx // BLOCK + 2) + 8
+        opts = EngineOptions(max_model_len=long_ctx + 2 * BLOCK, block_size=BLOCK, num_kv_blocks=pages, max_num_seqs=8,
+                             max_num_batched_tokens=8192, dtype="bfloat16")
+        llm = LLM("<random weights>", opts, _model=(config, model))
+        for ctx0 in (8192, long_ctx):
+            for b in (1, 8):
+                pms, _, ctx = decode_run(llm, b, 16, warmup, ctx0)
+                points[f"decode_b{b}_ctx{ctx0}"] = round(b * 1000.0 / pms, 1)
+                points[f"frac_b{b}_ctx{ctx0}"] = round(hbm_frac(b, ctx, pms), 4)
+        del llm, model
+        torch.cuda.empty_cache()
+        w = workload_run("serving-0.6b", pk)
+        workloads["serving_0_6b"] = {k: w[k] for k in ("value", "generated_tokens_per_s", "seconds", "steps",
+                                                       "mean_requests_per_step", "bytes_per_step_gb", "roofline")}
     flops = prefill_flops(cfg, PROMPT_LEN)
     line = {
         "metric": "decode tok/s (Qwen3-8B sizes, bf16, batch 8, context 2048+)", "value": round(value, 1), "unit": "tokens/s",
@@ -342,6 +411,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "workloads": workloads,
     }
     print(json.dumps(line))
     return 0

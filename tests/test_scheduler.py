@@ -170,3 +170,46 @@ def test_many_requests_tiny_pool_all_finish_with_their_own_tokens():
     out = run(s, token=lambda rid, k: rid * 100 + k)
     assert {k: v[0] for k, v in out.items()} == want
     assert m.num_free_blocks(0) == 10 and m.num_requests == 0 and m.check_invariants() == ""
+
+
+def test_the_step_written_straight_from_the_sequences_equals_the_step_built_from_entries():
+    """fill_batch (the scheduler writes the step's arrays from its sequences) against fill_step_batch over
+    batch_entries(), array for array, over a run with portions, decodes and a preemption; the summary says what the
+    step holds; the sampling settings and keys of the sampled rows are the ones sample_requests() reports."""
+    import numpy as np
+    from vllm_oxide_b200.sampling import row_key
+    m, s = make(pages=10, bs=4, budget=9, max_seqs=4)
+    for i, n in enumerate([13, 3, 7, 6]):
+        p = params(6, temperature=0.5 * i)
+        p.top_k, p.top_p, p.seed, p.own_seed = i, 1.0 - 0.1 * i, 1000 + i, i % 2 == 1
+        s.add_request(list(range(10 * i, 10 * i + n)), p)
+    steps = 0
+    while s.has_unfinished():
+        assert s.schedule_step() == len(s.last_entries())
+        entries = s.batch_entries()
+        summ = s.summary()
+        assert summ.num_requests == len(entries) and summ.num_tokens == sum(len(e.tokens) for e in entries)
+        assert summ.num_rows == sum(len(e.want) for e in entries) and summ.all_single == all(len(e.tokens) == 1 for e in entries)
+        assert summ.max_pages == max(len(m.block_table(e.id, 0)) for e in entries)
+        L = host.BatchLayout(summ.num_tokens + 3, summ.num_requests + 1, summ.num_rows + 2, 1, summ.max_pages)
+        a, b = np.full(L.total, 77, np.int32), np.full(L.total, 88, np.int32)
+        ca = s.fill_batch(L, a)
+        cb = host.fill_step_batch(m, entries, L, b)
+        fresh = slice(L.state_fresh, L.state_fresh + L.B)          # "fresh" is taken by whoever asks first
+        a[fresh] = b[fresh] = 0
+        assert np.array_equal(a, b)
+        assert (ca.num_tokens, ca.num_requests, ca.num_rows, ca.num_decode, ca.max_q, ca.max_context) == \
+               (cb.num_tokens, cb.num_requests, cb.num_rows, cb.num_decode, cb.max_q, cb.max_context)
+        reqs = s.sample_requests()
+        t, p_, k, keys = np.zeros(8, np.float32), np.zeros(8, np.float32), np.zeros(8, np.int32), np.zeros(8, np.uint64)
+        rows, penalties = s.fill_sampling(t, p_, k, keys)
+        assert rows == len(reqs) and not penalties
+        for r, (rid, generated, temp, top_k, top_p, seed, _, key_id) in enumerate(reqs):
+            assert (t[r], k[r]) == (np.float32(temp), top_k) and p_[r] == np.float32(top_p)
+            assert int(keys[r]) == row_key(seed, key_id, generated) == s.row_key(seed, key_id, generated)
+        s.postprocess([5] * rows)
+        steps += 1
+    assert s.stats.preemptions > 0 and s.stats.steps == steps
+    assert s.stats.scheduled_requests >= steps and s.stats.sampled_rows == 4 * 6 and s.stats.context_tokens > 0
+    with pytest.raises(RuntimeError, match="no request"):
+        s.sequence(0)                                              # finished requests are forgotten

@@ -128,7 +128,17 @@ PYBIND11_MODULE(_host, m) {
       .def_readonly("decode_tokens", &SchedulerStats::decode_tokens)
       .def_readonly("preemptions", &SchedulerStats::preemptions)
       .def_readonly("prefix_hit_tokens", &SchedulerStats::prefix_hit_tokens)
-      .def_readonly("finished", &SchedulerStats::finished);
+      .def_readonly("finished", &SchedulerStats::finished)
+      .def_readonly("scheduled_requests", &SchedulerStats::scheduled_requests)
+      .def_readonly("context_tokens", &SchedulerStats::context_tokens)
+      .def_readonly("sampled_rows", &SchedulerStats::sampled_rows);
+
+  py::class_<StepSummary>(m, "StepSummary")
+      .def_readonly("num_requests", &StepSummary::num_requests)
+      .def_readonly("num_tokens", &StepSummary::num_tokens)
+      .def_readonly("num_rows", &StepSummary::num_rows)
+      .def_readonly("max_pages", &StepSummary::max_pages)
+      .def_readonly("all_single", &StepSummary::all_single);
 
   py::class_<Scheduler>(m, "Scheduler")
       .def(py::init<std::shared_ptr<KvCacheManager>, int, int, int, int>(), py::arg("manager"),
@@ -143,8 +153,29 @@ PYBIND11_MODULE(_host, m) {
       .def("running_ids", &Scheduler::running_ids)
       .def("waiting_ids", &Scheduler::waiting_ids)
       .def("schedule", &Scheduler::schedule)
+      // schedule() for callers that go on with summary() / fill_batch(): returns the number of requests in the step
+      .def("schedule_step", [](Scheduler& s) { return static_cast<int>(s.schedule().size()); })
+      .def("row_key", [](const Scheduler&, uint64_t seed, uint64_t request, uint64_t index) {
+        return sample_row_key(seed, request, index);
+      })
       .def("postprocess", &Scheduler::postprocess)
       .def("last_entries", &Scheduler::last_entries)
+      .def("summary", &Scheduler::summary)
+      // The scheduled step's arrays into `out` (as fill_step_batch, without building entries).
+      .def("fill_batch", [](Scheduler& s, const BatchLayout& L, py::array_t<int32_t, py::array::c_style> out) {
+        if (out.size() < L.total) throw PoolError("fill_batch: the output buffer is smaller than the layout");
+        return s.fill_batch(L, out.mutable_data());
+      })
+      // Sampling settings of the sampled rows into the caller's arrays; returns (rows, any row with penalties).
+      .def("fill_sampling", [](const Scheduler& s, py::array_t<float, py::array::c_style> temperature,
+                               py::array_t<float, py::array::c_style> top_p, py::array_t<int32_t, py::array::c_style> top_k,
+                               py::array_t<uint64_t, py::array::c_style> keys) {
+        const long cap = std::min(std::min(temperature.size(), top_p.size()), std::min(top_k.size(), keys.size()));
+        bool any = false;
+        int r = s.fill_sampling(temperature.mutable_data(), top_p.mutable_data(), top_k.mutable_data(), keys.mutable_data(),
+                                static_cast<int>(cap), &any);
+        return std::make_pair(r, any);
+      })
       // For every scheduled request that wants logits, in entry order:
       // (id, generated so far, temperature, top_k, top_p, seed, has penalties).
       .def("sample_requests", [](const Scheduler& s) {

@@ -23,8 +23,10 @@
 #pragma once
 #include <deque>
 #include <memory>
+#include <unordered_map>
 
 #include "kv_cache_manager.hpp"
+#include "step_batch.hpp"
 
 namespace vob {
 
@@ -66,7 +68,26 @@ struct RequestOutput {
 
 struct SchedulerStats {
   int64_t steps = 0, prefill_tokens = 0, decode_tokens = 0, preemptions = 0, prefix_hit_tokens = 0, finished = 0;
+  // sums over the steps booked so far: requests in a step, keys their queries could read (the context of every request
+  // after its portion), rows that a token was sampled from.  They give a step's mean occupancy and its cache traffic.
+  int64_t scheduled_requests = 0, context_tokens = 0, sampled_rows = 0;
 };
+
+// What the next step holds, for the engine to choose its buffers by: all single tokens -> a captured decode step.
+struct StepSummary {
+  int num_requests = 0, num_tokens = 0, num_rows = 0, max_pages = 0;
+  bool all_single = true;
+};
+
+// The key of one sampled token's random numbers: a splitmix64 finaliser over (seed, request, index of the token in the
+// request's output).  The same function as vllm_oxide_b200.sampling.sampler.row_key.
+inline uint64_t sample_row_key(uint64_t seed, uint64_t request, uint64_t index) {
+  uint64_t z = seed * 0x9E3779B97F4A7C15ull + request * 0xBF58476D1CE4E5B9ull + index * 0x94D049BB133111EBull +
+               0x2545F4914F6CDD1Dull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
 
 class Scheduler {
  public:
@@ -97,6 +118,7 @@ class Scheduler {
     seq->num_prompt = static_cast<int>(prompt.size());
     seq->params = params;
     int64_t id = seq->id;
+    by_id_[id] = seq.get();
     waiting_.push_back(std::move(seq));
     return id;
   }
@@ -107,9 +129,9 @@ class Scheduler {
   const SchedulerStats& stats() const { return stats_; }
 
   const Sequence& sequence(int64_t id) const {
-    for (const auto& s : running_) if (s->id == id) return *s;
-    for (const auto& s : waiting_) if (s->id == id) return *s;
-    throw PoolError("Scheduler: no request " + std::to_string(id));
+    auto it = by_id_.find(id);
+    if (it == by_id_.end()) throw PoolError("Scheduler: no request " + std::to_string(id));
+    return *it->second;
   }
 
   std::vector<int64_t> running_ids() const {
@@ -181,6 +203,9 @@ class Scheduler {
       if (!seq) throw PoolError("postprocess: request " + std::to_string(e.id) + " is not running");
       seq->num_computed += e.n;
       (e.n == 1 && e.start >= seq->num_prompt ? stats_.decode_tokens : stats_.prefill_tokens) += e.n;
+      ++stats_.scheduled_requests;
+      stats_.context_tokens += e.start + e.n;
+      stats_.sampled_rows += e.wants_logits;
       bool finished = false;
       std::string reason;
       if (e.wants_logits) {
@@ -198,6 +223,7 @@ class Scheduler {
                            true, reason});
         mgr_->free_request(seq->id);
         ++stats_.finished;
+        by_id_.erase(seq->id);
         for (auto it = running_.begin(); it != running_.end(); ++it)
           if (it->get() == seq) { running_.erase(it); break; }
       } else {
@@ -211,10 +237,58 @@ class Scheduler {
 
   const std::vector<ScheduledEntry>& last_entries() const { return last_; }
 
+  // ---- the scheduled step without a detour through per-request objects of the caller's language
+  StepSummary summary() const {
+    StepSummary s;
+    for (const auto& e : last_) {
+      ++s.num_requests;
+      s.num_tokens += e.n;
+      s.num_rows += e.wants_logits;
+      s.all_single = s.all_single && e.n == 1;
+      for (int g = 0; g < mgr_->num_groups(); ++g)
+        s.max_pages = std::max(s.max_pages, static_cast<int>(mgr_->block_table(e.id, g).size()));
+    }
+    return s;
+  }
+
+  // The step's arrays straight from the sequences (see fill_step_batch): a request that wants logits asks for its
+  // last place.
+  BatchCounts fill_batch(const BatchLayout& L, int32_t* out) {
+    views_.clear();
+    last_place_.resize(last_.size());
+    for (size_t i = 0; i < last_.size(); ++i) {
+      const auto& e = last_[i];
+      const Sequence& q = sequence(e.id);
+      last_place_[i] = e.n - 1;
+      views_.push_back({e.id, e.start, q.tokens.data() + e.start, e.n, &last_place_[i], e.wants_logits ? 1 : 0});
+    }
+    return fill_step_views(*mgr_, views_, L, out);
+  }
+
+  // Sampling settings of the rows that a token is sampled from, in row order, into the caller's arrays (each of
+  // `capacity` elements).  Returns the number of rows; *any_penalties says whether a row asks for penalties.
+  int fill_sampling(float* temperature, float* top_p, int32_t* top_k, uint64_t* keys, int capacity, bool* any_penalties) const {
+    int r = 0;
+    *any_penalties = false;
+    for (const auto& e : last_) {
+      if (!e.wants_logits) continue;
+      if (r >= capacity) throw PoolError("fill_sampling: more sampled rows than the arrays hold");
+      const Sequence& q = sequence(e.id);
+      const SamplingParams& p = q.params;
+      temperature[r] = p.temperature;
+      top_p[r] = p.top_p;
+      top_k[r] = p.top_k;
+      keys[r] = sample_row_key(p.seed, p.own_seed ? 0ull : static_cast<uint64_t>(q.id), static_cast<uint64_t>(q.num_generated()));
+      *any_penalties = *any_penalties || p.presence_penalty != 0.f || p.frequency_penalty != 0.f || p.repetition_penalty != 0.f;
+      ++r;
+    }
+    return r;
+  }
+
  private:
   Sequence* find_running(int64_t id) {
-    for (auto& s : running_) if (s->id == id) return s.get();
-    return nullptr;
+    auto it = by_id_.find(id);
+    return it == by_id_.end() ? nullptr : it->second;
   }
   void preempt_last() {
     std::unique_ptr<Sequence> v = std::move(running_.back());
@@ -230,7 +304,10 @@ class Scheduler {
   int budget_, max_seqs_, max_len_, eos_;
   int64_t next_id_ = 0;
   std::deque<std::unique_ptr<Sequence>> waiting_, running_;
+  std::unordered_map<int64_t, Sequence*> by_id_;   // every unfinished request, waiting or running
   std::vector<ScheduledEntry> last_;
+  std::vector<EntryView> views_;
+  std::vector<int32_t> last_place_;
   SchedulerStats stats_;
 };
 

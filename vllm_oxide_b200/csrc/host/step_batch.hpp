@@ -46,11 +46,21 @@ struct BatchCounts {
   int num_tokens = 0, num_requests = 0, num_rows = 0, num_decode = 0, max_q = 0, max_context = 0;
 };
 
-inline BatchCounts fill_step_batch(KvCacheManager& mgr, const std::vector<BatchEntry>& entries,
-                                   const BatchLayout& L, int32_t* out) {
+// One request's part of a step, by reference: the tokens and wanted places live in the caller's entry or sequence.
+struct EntryView {
+  int64_t id;
+  int start;
+  const int32_t* tokens;
+  int n;
+  const int32_t* want;
+  int n_want;
+};
+
+inline BatchCounts fill_step_views(KvCacheManager& mgr, const std::vector<EntryView>& entries, const BatchLayout& L,
+                                   int32_t* out) {
   BatchCounts c;
   long T = 0, R = 0;
-  for (const auto& e : entries) { T += static_cast<long>(e.tokens.size()); R += static_cast<long>(e.want.size()); }
+  for (const auto& e : entries) { T += e.n; R += e.n_want; }
   if (T > L.T || static_cast<int>(entries.size()) > L.B || R > L.R)
     throw PoolError("fill_step_batch: the step (" + std::to_string(T) + " tokens, " + std::to_string(entries.size()) +
                     " requests, " + std::to_string(R) + " rows) exceeds the buffer's capacity");
@@ -61,7 +71,7 @@ inline BatchCounts fill_step_batch(KvCacheManager& mgr, const std::vector<BatchE
   std::fill(out + L.block_tables, out + L.block_tables + static_cast<long>(L.G) * L.B * L.P, -1);
   int t = 0, r = 0, b = 0;
   for (const auto& e : entries) {
-    const int n = static_cast<int>(e.tokens.size());
+    const int n = e.n;
     if (n <= 0) throw PoolError("fill_step_batch: an entry without tokens");
     if (e.start < 0) throw PoolError("fill_step_batch: negative start");
     out[L.cu_q + b] = t;
@@ -85,7 +95,8 @@ inline BatchCounts fill_step_batch(KvCacheManager& mgr, const std::vector<BatchE
                         " pages exceeds the buffer's width " + std::to_string(L.P));
       std::copy(table.begin(), table.end(), out + L.block_tables + (static_cast<long>(g) * L.B + b) * L.P);
     }
-    for (int w : e.want) {
+    for (int j = 0; j < e.n_want; ++j) {
+      const int w = e.want[j];
       if (w < 0 || w >= n) throw PoolError("fill_step_batch: wanted place " + std::to_string(w) + " outside the portion");
       out[L.logit_rows + r++] = t + w;
     }
@@ -98,6 +109,16 @@ inline BatchCounts fill_step_batch(KvCacheManager& mgr, const std::vector<BatchE
   for (int i = b; i <= L.B; ++i) out[L.cu_q + i] = t;
   c.num_tokens = t; c.num_requests = b; c.num_rows = r;
   return c;
+}
+
+inline BatchCounts fill_step_batch(KvCacheManager& mgr, const std::vector<BatchEntry>& entries,
+                                   const BatchLayout& L, int32_t* out) {
+  std::vector<EntryView> views;
+  views.reserve(entries.size());
+  for (const auto& e : entries)
+    views.push_back({e.id, e.start, e.tokens.data(), static_cast<int>(e.tokens.size()), e.want.data(),
+                     static_cast<int>(e.want.size())});
+  return fill_step_views(mgr, views, L, out);
 }
 
 }  // namespace vob

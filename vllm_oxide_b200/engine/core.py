@@ -103,15 +103,21 @@ class EngineCore:
     def build_context(self, entries: Sequence["host.BatchEntry"]) -> StepContext:
         n_tok = sum(len(e.tokens) for e in entries)
         n_rows = sum(len(e.want) for e in entries)
+        pages = max((len(self.manager.block_table(e.id, g)) for e in entries for g in range(self.num_groups)), default=1)
+        entries = list(entries)
+        return self._build_context(len(entries), n_tok, n_rows, pages,
+                                   lambda layout: host.fill_step_batch(self.manager, entries, layout, self._host_np))
+
+    def _build_context(self, n_req: int, n_tok: int, n_rows: int, pages: int, fill) -> StepContext:
+        """`fill(layout)` writes the step's arrays into the pinned buffer and returns its counts."""
         if n_tok > self.max_tokens:
             raise ValueError(f"a step of {n_tok} tokens exceeds max_num_batched_tokens {self.max_tokens}")
-        if len(entries) > self.max_seqs:
-            raise ValueError(f"a step of {len(entries)} requests exceeds max_num_seqs {self.max_seqs}")
-        pages = max((len(self.manager.block_table(e.id, g)) for e in entries for g in range(self.num_groups)), default=1)
-        layout = host.BatchLayout(max(n_tok, 1), max(len(entries), 1), max(n_rows, 1), self.num_groups, max(pages, 1))
+        if n_req > self.max_seqs:
+            raise ValueError(f"a step of {n_req} requests exceeds max_num_seqs {self.max_seqs}")
+        layout = host.BatchLayout(max(n_tok, 1), max(n_req, 1), max(n_rows, 1), self.num_groups, max(pages, 1))
         if self._copied is not None:
             self._copied.synchronize()   # the previous step's copy has left the pinned buffer
-        counts = host.fill_step_batch(self.manager, list(entries), layout, self._host_np)
+        counts = fill(layout)
         fresh = [int(s) for s, f in zip(self._host_np[layout.state_slots:layout.state_slots + counts.num_requests],
                                         self._host_np[layout.state_fresh:layout.state_fresh + counts.num_requests]) if f]
         self.cache.zero_states(fresh)
@@ -125,16 +131,18 @@ class EngineCore:
     def _graph_bucket(self, entries) -> Optional[int]:
         if not self.use_graphs or any(len(e.tokens) != 1 for e in entries):
             return None
+        return self._bucket_for(len(entries))
+
+    def _bucket_for(self, num_requests: int) -> Optional[int]:
         for b in GRAPH_BUCKETS:
-            if b >= len(entries):
+            if b >= num_requests:
                 return b if b <= max(self.max_seqs, 1) * 2 else None
         return None
 
-    def _fill_fixed(self, g: _DecodeGraph, entries) -> "host.BatchCounts":
+    def _fill_fixed(self, g: _DecodeGraph, fill) -> "host.BatchCounts":
         if self._copied is not None:
             self._copied.synchronize()
-        counts = host.fill_step_batch(self.manager, entries if isinstance(entries, list) else list(entries), g.layout,
-                                      self._host_np)
+        counts = fill(g.layout)
         L = g.layout
         if self.cache.has_states:
             fresh = [int(s) for s, f in zip(self._host_np[L.state_slots:L.state_slots + counts.num_requests],
@@ -154,13 +162,13 @@ class EngineCore:
         ctx.max_q, ctx.max_context = 1, self.max_model_len
         return ctx
 
-    def _run_graph(self, bucket: int, entries) -> torch.Tensor:
+    def _run_graph(self, bucket: int, fill) -> torch.Tensor:
         g = self._graphs.get(bucket)
         if g is None:
             layout = host.BatchLayout(bucket, bucket, bucket, self.num_groups, self.max_pages)
             g = _DecodeGraph(layout, Workspace(bucket, self.device, self.model.dtype),
                              torch.empty(layout.total, dtype=torch.int32, device=self.device))
-            counts = self._fill_fixed(g, entries)
+            counts = self._fill_fixed(g, fill)
             ctx = self._graph_context(g, counts)
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
@@ -177,7 +185,7 @@ class EngineCore:
             g.launches = kernels.launch_count - before
             self._graphs[bucket] = g
         else:
-            counts = self._fill_fixed(g, entries)
+            counts = self._fill_fixed(g, fill)
         g.graph.replay()
         if self._copied is not None:
             self._copied.record()     # after the launch: it guards the pinned buffer, and recording it is not free
@@ -192,8 +200,24 @@ class EngineCore:
             return torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
         bucket = self._graph_bucket(entries)
         if bucket is not None:
-            return self._run_graph(bucket, entries)
-        ctx = self.build_context(entries)
+            entries = entries if isinstance(entries, list) else list(entries)
+            return self._run_graph(bucket, lambda layout: host.fill_step_batch(self.manager, entries, layout, self._host_np))
+        return self._forward(self.build_context(entries))
+
+    def run_scheduled(self, scheduler: "host.Scheduler") -> torch.Tensor:
+        """The step that `scheduler.schedule()` has just decided, without building entries on the way: the scheduler
+        writes the step's arrays from its sequences straight into the pinned buffer.  Same logits as
+        `run(scheduler.batch_entries())`."""
+        s = scheduler.summary()
+        if s.num_requests == 0:
+            return torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
+        fill = lambda layout: scheduler.fill_batch(layout, self._host_np)
+        bucket = self._bucket_for(s.num_requests) if self.use_graphs and s.all_single else None
+        if bucket is not None:
+            return self._run_graph(bucket, fill)
+        return self._forward(self._build_context(s.num_requests, s.num_tokens, s.num_rows, s.max_pages, fill))
+
+    def _forward(self, ctx: StepContext) -> torch.Tensor:
         hidden, residual = self.model.forward(ctx)
         if ctx.num_rows == 0:
             return torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)

@@ -23,7 +23,7 @@ from .. import host
 from ..cache.paged_cache import PagedCache
 from ..config.engine_options import EngineOptions
 from ..sampling.params import SamplingParams
-from ..sampling.sampler import Sampler, row_key
+from ..sampling.sampler import Sampler
 from .core import EngineCore
 from .loading import load_model, random_model, resolve_dtype
 
@@ -175,28 +175,30 @@ class LLM:
     def step(self, want_logits: bool = False):
         """One engine step: schedule, run, sample, book.  Returns the finished requests' outputs
         (and, with `want_logits`, the float32 logits of the rows that were sampled from)."""
-        self.scheduler.schedule()
-        entries = self.scheduler.batch_entries()
-        if not entries:
-            if self.scheduler.has_unfinished():
+        sched, sampler = self.scheduler, self.sampler
+        if not sched.schedule_step():
+            if sched.has_unfinished():
                 raise RuntimeError("the scheduler produced an empty step while requests are unfinished")
             return ([], None) if want_logits else []
-        logits = self.core.run(entries)
-        reqs = self.scheduler.sample_requests()
-        self.last_sampled_ids = [r[0] for r in reqs]     # the requests of the logits' rows, in row order
+        logits = self.core.run_scheduled(sched)        # the step's arrays go from the sequences into the pinned buffer
+        sampler.reserve(logits.shape[0])
+        rows, penalties = sched.fill_sampling(sampler.host_temperature, sampler.host_top_p, sampler.host_top_k,
+                                              sampler.host_keys)
         sampled: List[int] = []
-        if reqs:
-            if any(r[6] for r in reqs):
-                self._penalties(logits, reqs)
-            keys = [row_key(r[5], r[7], r[1]) for r in reqs]
-            toks = self.sampler.forward(logits, [r[2] for r in reqs], [r[3] for r in reqs], [r[4] for r in reqs], keys)
-            sampled = self._read_back(toks)
+        if rows:
+            if penalties or want_logits:
+                reqs = sched.sample_requests()
+                self.last_sampled_ids = [r[0] for r in reqs]     # the requests of the logits' rows, in row order
+                if penalties:
+                    self._penalties(logits, reqs)
+            sampled = self._read_back(sampler.forward_staged(logits, rows))
         else:
+            self.last_sampled_ids = []
             self.core.check_errors()
         outs = [RequestOutput(o.id, list(o.token_ids), "", o.finished, o.finish_reason)
-                for o in self.scheduler.postprocess(sampled)]
+                for o in sched.postprocess(sampled)]
         if want_logits:
-            return outs, (logits.float().cpu().numpy().copy() if reqs else None)
+            return outs, (logits.float().cpu().numpy().copy() if rows else None)
         return outs
 
     def _read_back(self, toks: torch.Tensor) -> List[int]:

@@ -37,12 +37,30 @@ class Sampler:
     def _grow(self, rows: int) -> None:
         if rows <= self._cap:
             return
+        rows = (rows + 1) // 2 * 2          # the 64-bit keys start on an 8-byte boundary of the staging block
         self._cap = rows
         pin = torch.device(self.device).type == "cuda"
         # one pinned staging block: temperature f32 | top_p f32 | top_k i32 | keys u64 (as 2 x i32)
         self._host = torch.empty(5 * rows, dtype=torch.int32, pin_memory=pin)
         self._dev = torch.empty(5 * rows, dtype=torch.int32, device=self.device)
         self._out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        h, n = self._host.numpy(), rows
+        # the four arrays of the staging block, for callers that fill them in place (the scheduler does, in C++)
+        self.host_temperature, self.host_top_p = h[0:n].view(np.float32), h[n:2 * n].view(np.float32)
+        self.host_top_k, self.host_keys = h[2 * n:3 * n], h[3 * n:5 * n].view(np.uint64)
+
+    def reserve(self, rows: int) -> None:
+        """Makes room for `rows` rows (the staging arrays are replaced when it has to grow)."""
+        self._grow(rows)
+
+    def forward_staged(self, logits: torch.Tensor, rows: int) -> torch.Tensor:
+        """As forward(), with the settings of the first `rows` rows already written to the host_* arrays."""
+        n = self._cap
+        self._dev.copy_(self._host, non_blocking=True)
+        d = self._dev
+        kernels.sample(logits, d[0:n].view(torch.float32), d[2 * n:3 * n], d[n:2 * n].view(torch.float32),
+                       d[3 * n:5 * n], self._out, rows)
+        return self._out[:rows]
 
     def forward(self, logits: torch.Tensor, temperature: Sequence[float], top_k: Sequence[int],
                 top_p: Sequence[float], keys: Sequence[int]) -> torch.Tensor:

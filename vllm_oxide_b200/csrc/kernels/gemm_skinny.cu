@@ -55,7 +55,10 @@ __device__ __forceinline__ void sk_mma(float (&d)[4], const uint32_t (&a)[4], ui
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 // stages of the ring: about 100 KB of shared memory per block, two blocks per SM
-template <int R, int MT> struct SkStages { static constexpr int N = (96 * 1024) / (SK_SLICES * (R + MT) * 128); };
+#ifndef VOB_SK_RING_KB
+#define VOB_SK_RING_KB 96
+#endif
+template <int R, int MT> struct SkStages { static constexpr int N = (VOB_SK_RING_KB * 1024) / (SK_SLICES * (R + MT) * 128); };
 
 // tmW: W [N, K] with box [R, 64]; tmX: x [M, K] with box [MT, 64].  EPI_BF16 / EPI_F32: out [M, N] (row
 // stride ldo).  EPI_SWIGLU: the rows of W alternate in groups of eight between gate and up (gate rows

@@ -239,27 +239,29 @@ def test_a_mixed_workload_at_real_head_counts_repeats_bit_for_bit(name):
     assert sure >= greedy_steps // 4, f"only {sure} of {greedy_steps} greedy steps had a clear winner"
 
 
-def test_the_residual_stream_inside_the_products_agrees_with_the_separate_norm_kernels():
+def test_the_residual_stream_inside_the_products_is_as_close_to_the_32_bit_path_as_the_separate_norm_kernels():
     """Decode steps of up to 8 tokens run two kernels less a layer: the norm inside the product that follows it, the
-    residual sum made by the product before it.  Same logits as with the add+norm kernels up to bfloat16 rounding,
-    at real layer sizes, and the kernels are really gone."""
+    residual sum made by the product before it.  That path rounds at other places than the separate add+norm kernels (the
+    norm is taken of the stream as it was rounded to bfloat16, x * w is rounded before the scale by 1/rms, the new stream
+    is rounded once), so the two agree only beyond rounding; what must hold is that it is no further from the 32-bit
+    path over the same weights than the separate kernels are (measured: 0.0062 against 0.0060 of the logits' scale,
+    root mean square; 0.0075 from each other), at real layer sizes, and that the kernels are really gone."""
     import vllm_oxide_b200.parts.block as block
     from vllm_oxide_b200 import host, kernels
-    half, _ = engines(SIZES["8b"], seed=14, seqs=8, pages=24)
-    del _
+    half, full = engines(SIZES["8b"], seed=14, seqs=8, pages=24)
     g = torch.Generator().manual_seed(9)
     prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (300, 5, 129)]
     feed = torch.randint(0, 2048, (3, 4), generator=g).tolist()
 
-    def run(on, first_id):
+    def run(llm, on, first_id):
         block.STREAM_IN_PRODUCTS = on
-        half.core._graphs.clear()
-        mgr = half.cache.manager
+        llm.core._graphs.clear()
+        mgr = llm.cache.manager
         ids = [first_id + i for i in range(3)]
         for r, p in zip(ids, prompts):
             mgr.add_request(r)
             mgr.ensure(r, 0, len(p))
-            half.core.run([host.BatchEntry(r, 0, p, [])])
+            llm.core.run([host.BatchEntry(r, 0, p, [])])
             mgr.advance(r, len(p))
         rows, launches = [], []
         for step in range(4):
@@ -268,22 +270,26 @@ def test_the_residual_stream_inside_the_products_agrees_with_the_separate_norm_k
                 mgr.ensure(r, len(p) + step, 1)
                 entries.append(host.BatchEntry(r, len(p) + step, [feed[i][step]], [0]))
             before = kernels.launch_count
-            rows.append(half.core.run(entries).double().cpu())
+            rows.append(llm.core.run(entries).double().cpu())
             launches.append(kernels.launch_count - before)
             for r, p in zip(ids, prompts):
                 mgr.advance(r, len(p) + step + 1)
-        half.core.check_errors()
+        llm.core.check_errors()
         for r in ids:
             mgr.free_request(r)
         return torch.stack(rows), launches[-1]
 
     try:
-        separate, n_separate = run(False, 100)
-        inside, n_inside = run(True, 200)
+        separate, n_separate = run(half, False, 100)
+        inside, n_inside = run(half, True, 200)
+        truth, _ = run(full, False, 300)
     finally:
         block.STREAM_IN_PRODUCTS = True
     layers = SIZES["8b"]["num_hidden_layers"]
     assert n_separate - n_inside == 2 * layers
-    scale = separate.pow(2).mean().sqrt()
-    err = inside - separate
-    assert err.pow(2).mean().sqrt() < 8e-3 * scale and err.abs().max() < 6e-2 * scale
+    scale = truth.pow(2).mean().sqrt()
+    rms = lambda d: float(d.pow(2).mean().sqrt() / scale)
+    worst = lambda d: float(d.abs().max() / scale)
+    assert rms(separate - truth) < 0.01 and rms(inside - truth) < 0.01
+    assert rms(inside - truth) <= 1.25 * rms(separate - truth), (rms(inside - truth), rms(separate - truth))
+    assert worst(inside - truth) <= 1.5 * worst(separate - truth), (worst(inside - truth), worst(separate - truth))

@@ -302,3 +302,31 @@ def test_a_decode_graph_padded_beyond_the_step_limits(model_folders):
     llm = make_llm(model_folders, name, max_num_seqs=5, max_num_batched_tokens=6)
     assert [o.token_ids for o in llm.generate(prompts, sp)] == want
     assert llm.core.graph_replays > 0 and 8 in llm.core._graphs
+
+
+def test_kernel_class_timers_behind_a_flag(model_folders):
+    """With the timers on, every launch of the package's kernels is bracketed by events and the report adds the device
+    time up by entry point; off (the default), nothing is recorded."""
+    import time
+    from vllm_oxide_b200 import SamplingParams, kernels
+    llm = make_llm(model_folders, "D", "bfloat16", enforce_eager=True)
+    prompt = tokens_for("D", 70, salt=11)
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    want = llm.generate([prompt], sp)[0].token_ids
+    with pytest.raises(kernels.KernelError, match="timers are off"):
+        kernels.kernel_timer_report()
+    kernels.enable_kernel_timers()
+    try:
+        before = kernels.launch_count
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        assert llm.generate([prompt], sp)[0].token_ids == want          # timing changes no result
+        torch.cuda.synchronize()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        report = kernels.kernel_timer_report()
+    finally:
+        kernels.enable_kernel_timers(False)
+    assert sum(n for n, _ in report.values()) == kernels.launch_count - before
+    for name in ("embedding", "gemm_skinny", "qk_norm_rope_kv_write", "attention_decode_tma", "attention_prefill_tc5", "sample"):
+        assert report[name][0] > 0 and report[name][1] > 0.0, (name, report)
+    assert 0.0 < sum(ms for _, ms in report.values()) < wall_ms

@@ -51,24 +51,27 @@ class Both:
 
 
 def check(got, want, dtype, what):
-    """32-bit: within 2e-5 of the logits' scale of the float64 run.
-    bfloat16: the engine must be as close to the float64 run as the plain bfloat16 run is: at most 1.5 times
-    its root-mean-square error and 2.5 times its worst error (two runs that round at every operation, in
-    different orders, differ from each other by about 1.4 times that error)."""
+    """Against the float64 run alone (32-bit path, small models): within 2e-5 of the logits' scale.
+    Against a `Both` (the float64 run and a plain run in the engine's own precision over the same weights): the engine
+    must be as close to the float64 run as that plain run is: at most 1.5 times its root-mean-square error and 2.5
+    times its worst error (two runs that round at every operation, in different orders, differ from each other by
+    about 1.4 times that error).  That is the bound for bfloat16 everywhere, and for the 32-bit path of a model of
+    many layers, where rounding alone exceeds any fixed small bound."""
     got = np.asarray(got, np.float64)
-    if dtype == "float32":
+    if not isinstance(want, Both):
+        assert dtype == "float32", what
         want = np.asarray(want, np.float64)
         assert got.shape == want.shape, what
         worst = np.abs(got - want).max() / np.abs(want).max()
         assert worst < 2e-5, f"{what}: {worst:.3e} of scale"
         return
-    truth, rounded = want.truth, want.rounded
+    truth, rounded = np.asarray(want.truth, np.float64), np.asarray(want.rounded, np.float64)
     assert got.shape == truth.shape, what
     rms = lambda d: np.sqrt((d ** 2).mean())
     floor_rms, floor_worst = rms(rounded - truth), np.abs(rounded - truth).max()
     got_rms, got_worst = rms(got - truth), np.abs(got - truth).max()
     assert got_rms <= 1.5 * floor_rms and got_worst <= 2.5 * floor_worst, \
-        f"{what}: rms {got_rms:.3e} vs plain bfloat16 {floor_rms:.3e}; worst {got_worst:.3e} vs {floor_worst:.3e}"
+        f"{what}: rms {got_rms:.3e} vs the plain run in {dtype} {floor_rms:.3e}; worst {got_worst:.3e} vs {floor_worst:.3e}"
 
 
 def check_same(a, b, dtype, what):

@@ -109,6 +109,64 @@ def test_real_layer_sizes_against_the_plain_implementation_in_every_cut(name):
             check(np.stack(got[rid]), want[rid], dtype, f"{name} {dtype} {rid} mixed")
 
 
+def test_the_whole_qwen3_8b_against_the_plain_implementation():
+    """All 36 layers and the whole vocabulary of 151,936 at Qwen3-8B sizes (random weights of bfloat16 values): the
+    32-bit path and the bfloat16 path against the plain implementation over the same weights (float64 and bfloat16 runs
+    on the GPU), every position of two requests, whole; the last 32 tokens one by one; in portions that cross the
+    256-key pages; and both requests mixed in the same steps on a pool of three pages that the second run uses again."""
+    import numpy as np
+    from plain import qwen3_plain as P
+    from test_gpu_replay import Both, check
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    cfg = dict(config_of(dict(SIZES["8b"], num_hidden_layers=36)), vocab_size=151936)
+    from vllm_oxide_b200.engine.loading import resolve
+    from vllm_oxide_b200.models.causal_lm import CausalLM
+    from vllm_oxide_b200.weights.random_init import random_weights
+    config, plan = resolve(cfg, where="config")
+    half = CausalLM(plan, torch.bfloat16, "cuda:0")
+    weights = random_weights(half.tensor_specs(), 7, "0.02", "cuda:0", torch.bfloat16)
+    half.load(weights)
+    full = CausalLM(plan, torch.float32, "cuda:0")
+    full.load({k: (v if v.dtype == torch.int32 else v.float()) for k, v in weights.items()})
+    bs = 256
+    g = torch.Generator().manual_seed(41)
+    reqs = {"a": torch.randint(0, 151936, (300,), generator=g).tolist(), "b": torch.randint(0, 151936, (70,), generator=g).tolist()}
+    # the plain runs read the bfloat16 tensors themselves (they widen what they use, layer by layer)
+    truth = {r: P.forward_logits(cfg, weights, t, torch.float64).cpu().numpy() for r, t in reqs.items()}
+    # what rounding at every operation costs over 36 layers, in each precision: the plain run in float32 and in bfloat16.
+    # (Over 36 layers float32 rounding alone passes the fixed bound that the small models are held to: the 32-bit path
+    # measured 2.3e-5 of the logits' scale from the float64 run; so it is held to the plain float32 run's distance.)
+    plain = {dt: {r: P.forward_logits(cfg, weights, t, dt).double().cpu().numpy() for r, t in reqs.items()}
+             for dt in (torch.float32, torch.bfloat16)}
+    del weights
+    torch.cuda.empty_cache()
+    for dtype, model in (("float32", full), ("bfloat16", half)):
+        floor = plain[torch.float32 if dtype == "float32" else torch.bfloat16]
+        want = {r: Both(truth[r], floor[r]) for r in reqs}
+        make = lambda pool: TraceRunner(None, dtype, pool, bs, _model=(config, model), max_live=2)
+        a, n = reqs["a"], len(reqs["a"])
+        check(make(512).step([dict(id="a", tokens=a, want=list(range(n)))], ["a"]), want["a"], dtype, f"8B {dtype} whole")
+        r = make(512)
+        rows = [r.step([dict(id="a", tokens=a[:n - 32], want=[n - 33])], [])[0]]
+        rows += [r.step([dict(id="a", tokens=[t], want=[0])], [])[0] for t in a[n - 32:]]
+        check(np.stack(rows), want["a"][n - 33:], dtype, f"8B {dtype} last 32 one by one")
+        r, got, pos = make(512), [], 0
+        for m in (2, 250, 6, 3, 39):                      # 252 | 258: a portion ends before the page's edge, the next crosses it
+            got.append(r.step([dict(id="a", tokens=a[pos:pos + m], want=list(range(m)))], []))
+            pos += m
+        check(np.concatenate(got), want["a"], dtype, f"8B {dtype} portions")
+        # both requests in the same steps; then the first again on the pages they gave back
+        r = make(768)
+        b = reqs["b"]
+        o1 = r.step([dict(id="a", tokens=a[:200], want=[]), dict(id="b", tokens=b[:69], want=list(range(69)))], [])
+        o2 = r.step([dict(id="a", tokens=a[200:], want=list(range(100))), dict(id="b", tokens=b[69:], want=[0])], ["a", "b"])
+        check(np.concatenate([o1, o2[100:]]), want["b"], dtype, f"8B {dtype} mixed b")
+        check(o2[:100], want["a"][200:], dtype, f"8B {dtype} mixed a")
+        again = r.step([dict(id="a2", tokens=a, want=[n - 1])], ["a2"])
+        check(again, want["a"][n - 1:], dtype, f"8B {dtype} pages used again")
+        assert r.manager.num_free_blocks(0) == 3 and r.manager.check_invariants() == ""
+
+
 @pytest.mark.parametrize("name", list(SIZES))
 def test_real_layer_sizes_agree_with_the_32_bit_path(name):
     half, full = engines(SIZES[name], seed=11)

@@ -100,8 +100,19 @@ def kernel_sources(per_head_dim: bool = False):
     return [os.path.join(d, f) for f in names]
 
 
+SANITIZE_FLAGS = ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer", "-g", "-O1"]
+
+
+def host_sanitized() -> bool:
+    """VOB_HOST_SANITIZE=1: the host runtime is built with AddressSanitizer and UndefinedBehaviorSanitizer into a folder
+    of its own and loaded from there (the process must have the sanitizer's runtime preloaded: see
+    tests/test_host_sanitizers.py)."""
+    return os.environ.get("VOB_HOST_SANITIZE", "") not in ("", "0")
+
+
 def host_library_path() -> str:
-    return os.path.join(_PKG, "_host" + sysconfig.get_config_var("EXT_SUFFIX"))
+    name = "_host" + sysconfig.get_config_var("EXT_SUFFIX")
+    return os.path.join(_BUILD, "sanitized", name) if host_sanitized() else os.path.join(_PKG, name)
 
 
 def kernel_library_path() -> str:
@@ -117,8 +128,10 @@ def build_host(force: bool = False) -> str:
     with _LOCK:
         os.makedirs(_BUILD, exist_ok=True)
         out = host_library_path()
-        stamp_path = os.path.join(_BUILD, "host.stamp")
-        stamp = _hash_files(host_sources(), " ".join(CXX_FLAGS))
+        os.makedirs(os.path.dirname(out), exist_ok=True)
+        flags = CXX_FLAGS + (SANITIZE_FLAGS if host_sanitized() else [])
+        stamp_path = os.path.join(_BUILD, "host_sanitized.stamp" if host_sanitized() else "host.stamp")
+        stamp = _hash_files(host_sources(), " ".join(flags))
         if not force and os.path.isfile(out) and _read(stamp_path) == stamp:
             return out
         cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
@@ -126,7 +139,7 @@ def build_host(force: bool = False) -> str:
             raise BuildError("no C++ compiler found for the host runtime (set CXX)")
         _log("compiling the host runtime (block pool, cache manager, scheduler) ...")
         tmp = out + f".tmp{os.getpid()}"
-        cmd = [cxx, *CXX_FLAGS, f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}",
+        cmd = [cxx, *flags, f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}",
                os.path.join(_HERE, "host", "bindings.cpp"), "-o", tmp]
         _run(cmd, "host runtime")
         os.replace(tmp, out)

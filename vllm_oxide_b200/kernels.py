@@ -19,6 +19,8 @@ class KernelError(RuntimeError):
     pass
 
 
+import os as _os
+
 _lib = None
 DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -69,10 +71,43 @@ def sm_count() -> int:
 
 launch_count = 0   # launches of this package's own kernels since import (bench.py reports the difference)
 
+# Per-kernel-class device timers, off unless asked for (VOB_KERNEL_TIMERS=1 or enable_kernel_timers()): every launch
+# of this package's kernels is then bracketed by two CUDA events on its stream, and kernel_timer_report() adds them up
+# by entry point.  It serialises nothing, but events cannot be recorded into a CUDA graph: time with
+# EngineOptions(enforce_eager=True).  The event before a launch is recorded where the launch asks for its stream,
+# which every binding does as the last thing before it calls the library.
+_timers = None          # None: off; else a list of (entry point, start event, end event)
+_timer_start = None
+
+
+def enable_kernel_timers(on: bool = True) -> None:
+    global _timers, _timer_start
+    _timers, _timer_start = ([] if on else None), None
+
+
+def kernel_timer_report(reset: bool = True):
+    """{entry point: (launches, milliseconds on the device)} since the timers were enabled or last reset."""
+    global _timers
+    if _timers is None:
+        raise KernelError("the kernel timers are off: enable_kernel_timers() or VOB_KERNEL_TIMERS=1")
+    torch.cuda.synchronize()
+    out = {}
+    for what, e0, e1 in _timers:
+        n, ms = out.get(what, (0, 0.0))
+        out[what] = (n + 1, ms + e0.elapsed_time(e1))
+    if reset:
+        _timers = []
+    return out
+
 
 def _check(code: int, what: str) -> None:
-    global launch_count
+    global launch_count, _timer_start
     launch_count += 1
+    if _timers is not None and _timer_start is not None:
+        end = torch.cuda.Event(enable_timing=True)
+        end.record(torch.cuda.current_stream(torch.cuda.current_device()))
+        _timers.append((what, _timer_start, end))
+        _timer_start = None
     if code != 0:
         raise KernelError(f"{what}: {lib().vob_error_string(code).decode()} (code {code})")
 
@@ -84,7 +119,12 @@ def _p(t: Optional[torch.Tensor]):
 def _stream():
     """The current stream's handle.  torch.cuda.current_stream() without a device spends 15 us looking the device up;
     with the index given it is a plain call."""
-    return ctypes.c_void_p(torch.cuda.current_stream(torch.cuda.current_device()).cuda_stream)
+    global _timer_start
+    stream = torch.cuda.current_stream(torch.cuda.current_device())
+    if _timers is not None and not torch.cuda.is_current_stream_capturing():
+        _timer_start = torch.cuda.Event(enable_timing=True)
+        _timer_start.record(stream)
+    return ctypes.c_void_p(stream.cuda_stream)
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -363,3 +403,7 @@ def copy_pages(cache_plane, pairs, n_pairs: int) -> None:
     page_elems = cache_plane[0].numel()
     _check(lib().vob_copy_pages(_p(cache_plane), _p(pairs), n_pairs, ctypes.c_long(page_elems),
                                 _code(cache_plane.dtype), _stream()), "copy_pages")
+
+
+if _os.environ.get("VOB_KERNEL_TIMERS", "") not in ("", "0"):
+    enable_kernel_timers()

@@ -78,19 +78,15 @@ class CausalLM:
         self.planes, self.states = list(planes), list(states)
 
     def weight_bytes(self) -> int:
+        """Bytes of every distinct weight tensor (a tied output matrix counts once)."""
         seen, total = set(), 0
-        def add(t):
-            nonlocal total
+        tensors = [self.embedding, self.lm_head] + self.final_norm.device_tensors()
+        for b in self.blocks:
+            tensors += b.device_tensors()
+        for t in tensors:
             if t is not None and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
-        add(self.embedding)
-        add(self.lm_head)
-        for b in self.blocks:
-            for part in getattr(b, "_parts", []):
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor):
-                        add(v)
         return total
 
     # ---- one step

@@ -126,6 +126,18 @@ class Part:
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         pass
 
+    def parts(self) -> List["Part"]:
+        """The parts this part is made of (a block: its norms, mixer and feed-forward)."""
+        return []
+
+    def device_tensors(self) -> List[torch.Tensor]:
+        """Every tensor this part and its parts hold (weights as loaded or merged, tables): what a step may read."""
+        own = [v for v in vars(self).values() if isinstance(v, torch.Tensor)]
+        for v in vars(self).values():
+            if isinstance(v, (list, tuple)):
+                own += [t for t in v if isinstance(t, torch.Tensor)]
+        return own + [t for p in self.parts() for t in p.device_tensors()]
+
 
 class Norm(Part):
     def forward(self, x, residual, ctx, rows=None, n_rows=None):

@@ -32,6 +32,9 @@ class PreNormBlock(Block):
         self._parts = [self.input_norm, self.mixer, self.post_mixer_norm, self.feed_forward]
         self.graph_safe = all(p.graph_safe for p in self._parts)
 
+    def parts(self):
+        return list(self._parts)
+
     def tensor_specs(self) -> List[TensorSpec]:
         return [s for p in self._parts for s in p.tensor_specs()]
 

@@ -630,3 +630,118 @@ def test_a_mixer_with_one_tensor_a_token_in_pages_of_its_own_size(tmp_path, dtyp
     for name in reqs:
         close(np.concatenate(got[name]), want[name], f"cut and mixed {name}")
     assert r.manager.num_free_blocks(0) + r.manager.num_free_blocks(1) == 18
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# What a plan may say beyond its layers: a scale on the embedded tokens, a soft cap on the logits, and a position part
+# that adds learned absolute positions to the embedding (its table is a tensor of the checkpoint) while the attention
+# layers rotate nothing.
+EMB_SCALE, SOFTCAP = math.sqrt(H), 7.5
+
+
+def register_absolute_toy():
+    from vllm_oxide_b200.models import ExecStep, ModelPlan, register_architecture
+    from vllm_oxide_b200.parts import PartSpec, PositionEncoding, register_part
+    from vllm_oxide_b200.weights import TensorSpec
+
+    class LearnedPositions(PositionEncoding):
+        """hidden[t] += table[position[t]]: one row of a learned table per token, added right after the embedding."""
+        graph_safe = True       # the same operations whatever the batch holds (rows beyond the batch get row 0)
+
+        def __init__(self, size, max_position, name, **_):
+            self.size, self.max_position, self.name = size, max_position, name
+
+        def tensor_specs(self):
+            return [TensorSpec(self.name, (self.max_position, self.size), "embedding")]
+
+        def load(self, tensors):
+            self.table = tensors[self.name]
+
+        def embed(self, hidden, ctx):
+            pos = ctx.positions[:hidden.shape[0]].clamp(0, self.max_position - 1).long()
+            hidden += self.table[pos]
+
+    register_part("position", "toy_learned", LearnedPositions)
+
+    @dataclass
+    class ToyConfig:
+        raw: dict
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+    def norm(name):
+        return PartSpec("rmsnorm", dict(size=H, eps=EPS, weight_name=name))
+
+    def plan(cfg):
+        def layer(i):
+            p = f"toy.layers.{i}."
+            return PartSpec("pre_norm", dict(
+                mixer=PartSpec("attention", dict(hidden_size=H, num_heads=NH, num_kv_heads=KVH, head_dim=HD, eps=EPS,
+                                                 qkv_bias=False, qk_norm=True, window=None, position=None,
+                                                 prefix=p + "self_attn.")),
+                feed_forward=PartSpec("swiglu", dict(hidden_size=H, intermediate_size=I, prefix=p + "mlp.")),
+                input_norm=norm(p + "input_layernorm.weight"), post_mixer_norm=norm(p + "post_attention_layernorm.weight")))
+        return ModelPlan(
+            architecture="ToyAbsoluteForCausalLM", hidden_size=H, vocab_size=V, max_position=MAXPOS,
+            embedding_name="toy.embed.weight", lm_head_name=None, final_norm=norm("toy.norm.weight"),
+            positions={"learned": PartSpec("toy_learned", dict(size=H, max_position=MAXPOS, name="toy.positions.weight"))},
+            layers=[layer(0), layer(1)], order=[ExecStep(0, 0), ExecStep(1, 1)],
+            embedding_scale=EMB_SCALE, logit_softcap=SOFTCAP)
+
+    register_architecture("ToyAbsoluteForCausalLM", ToyConfig.from_dict, plan)
+
+
+def plain_absolute_toy(weights, tokens, dt):
+    ids = torch.as_tensor(tokens)
+    pos = torch.arange(len(tokens))
+    it = torch.float64 if dt == torch.float64 else torch.float32
+    emb = (P.embedding(weights["toy.embed.weight"], ids, dt).to(it) * EMB_SCALE).to(dt)
+    hidden = (emb.to(it) + weights["toy.positions.weight"].to(dt)[pos].to(it)).to(dt)
+    residual = None
+    for i in (0, 1):
+        p = f"toy.layers.{i}."
+        normed, residual = P.add_rms_norm(hidden, residual, weights[p + "input_layernorm.weight"], EPS, dt)
+        q = P.linear(normed, weights[p + "self_attn.q_proj.weight"], dt)
+        k = P.linear(normed, weights[p + "self_attn.k_proj.weight"], dt)
+        v = P.linear(normed, weights[p + "self_attn.v_proj.weight"], dt)
+        q, k, v = P.split_qkv(torch.cat([q, k, v], -1), NH, KVH, HD)
+        q = P.head_rms_norm(q, weights[p + "self_attn.q_norm.weight"], EPS, dt)
+        k = P.head_rms_norm(k, weights[p + "self_attn.k_norm.weight"], EPS, dt)
+        a = P.linear(P.attention(q, k, v, pos, None, dt), weights[p + "self_attn.o_proj.weight"], dt)
+        normed, residual = P.add_rms_norm(a, residual, weights[p + "post_attention_layernorm.weight"], EPS, dt)
+        hidden = P.swiglu(normed, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"],
+                          weights[p + "mlp.down_proj.weight"], dt)
+    hf, _ = P.add_rms_norm(hidden, residual, weights["toy.norm.weight"], EPS, dt)
+    logits = P.linear(hf, weights["toy.embed.weight"], dt).double()
+    return (SOFTCAP * torch.tanh(logits / SOFTCAP)).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_plan_with_an_embedding_scale_a_soft_cap_and_learned_positions(tmp_path, dtype):
+    """Nothing of the model walk is edited for it: the plan carries the two constants, the position part brings its
+    table with the checkpoint and adds it after the embedding.  Whole, and decoded token by token (from CUDA graphs)."""
+    from vllm_oxide_b200.engine.loading import write_random_model_folder
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    register_absolute_toy()
+    folder = str(tmp_path / "absolute")
+    write_random_model_folder(folder, dict(architectures=["ToyAbsoluteForCausalLM"]), 41, "fan_in", torch.float32)
+    _, weights = P.read_folder(folder)
+    assert weights["toy.positions.weight"].shape == (MAXPOS, H)
+    g = torch.Generator().manual_seed(10)
+    toks = torch.randint(0, V, (60,), generator=g).tolist()
+    dt = torch.float64 if dtype == "float32" else torch.bfloat16
+    want = plain_absolute_toy(weights, toks, dt)
+    assert np.abs(want).max() < SOFTCAP and np.abs(want).max() > 0.8 * SOFTCAP        # the cap is at work
+    bound = 2e-5 if dtype == "float32" else 0.04
+    r = TraceRunner(folder, dtype, 64, 16)
+    whole = r.step([dict(id="w", tokens=toks, want=list(range(60)))], ["w"])
+    assert np.abs(whole.astype(np.float64) - want).max() / SOFTCAP < bound
+    rows = [r.step([dict(id="d", tokens=toks[:21], want=list(range(21)))], [])]
+    rows += [r.step([dict(id="d", tokens=[t], want=[0])], ["d"] if n == 59 else []) for n, t in enumerate(toks) if n >= 21]
+    assert np.abs(np.concatenate(rows).astype(np.float64) - want).max() / SOFTCAP < bound
+    assert r.core.graph_replays > 0
+    # the positions matter: the same tokens at other positions give other logits
+    shifted = r.step([dict(id="s", tokens=toks[5:25], want=list(range(20)))], ["s"])
+    assert np.abs(shifted.astype(np.float64) - want[5:25]).max() / SOFTCAP > 3 * bound

@@ -12,9 +12,10 @@
 namespace vob {
 
 // ---------------------------------------------------------------- embedding gather
+// out[t] = table[ids[t]] * scale (scale 1: a copy; otherwise the product is rounded to T once).
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, T* __restrict__ out,
-                                 int H, int V, int* err) {
+                                 int H, int V, float scale, int* err) {
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
@@ -26,7 +27,9 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
   }
   const T* src = table + (size_t)id * H;
   T* dst = out + (size_t)t * H;
-  if ((H * sizeof(T)) % 16 == 0) {
+  if (scale != 1.f) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = from_f<T>(to_f<T>(src[i]) * scale);
+  } else if ((H * sizeof(T)) % 16 == 0) {
     const int4* s4 = reinterpret_cast<const int4*>(src);
     int4* d4 = reinterpret_cast<int4*>(dst);
     const int n = H * sizeof(T) / 16;
@@ -542,15 +545,34 @@ __global__ void copy_pages_kernel(T* cache, const int* __restrict__ pairs, size_
 
 using namespace vob;
 
-VOB_API int vob_embedding(const void* table, const int* ids, void* out, int T, int H, int V, int dtype, int* err,
-                          cudaStream_t stream) {
+VOB_API int vob_embedding(const void* table, const int* ids, void* out, int T, int H, int V, float scale, int dtype,
+                          int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (dtype == VOB_F32)
-    return launch_kernel(embedding_kernel<float>, T, 128, 0, stream, (const float*)table, ids, (float*)out, H, V, err);
+    return launch_kernel(embedding_kernel<float>, T, 128, 0, stream, (const float*)table, ids, (float*)out, H, V, scale, err);
   if (dtype == VOB_BF16)
     return launch_kernel(embedding_kernel<__nv_bfloat16>, T, 128, 0, stream, (const __nv_bfloat16*)table, ids,
-                         (__nv_bfloat16*)out, H, V, err);
+                         (__nv_bfloat16*)out, H, V, scale, err);
   return VOB_BAD_ARGUMENT;
+}
+
+// logits = cap * tanh(logits / cap), in place, over rows of V floats with row stride ld.
+__global__ void softcap_kernel(float* logits, long ld, int V, long total, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const float inv = 1.f / cap;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    float* p = logits + (i / V) * ld + i % V;
+    *p = cap * tanhf(*p * inv);
+  }
+}
+
+VOB_API int vob_softcap(float* logits, long ld, int R, int V, float cap, cudaStream_t stream) {
+  if (R <= 0 || V <= 0) return 0;
+  if (!(cap > 0.f)) return VOB_BAD_ARGUMENT;
+  const long total = (long)R * V;
+  const long want = (total + 255) / 256, most = (long)sm_count() * 16;
+  return launch_kernel(softcap_kernel, (int)(want < most ? want : most), 256, 0, stream, logits, ld, V, total, cap);
 }
 
 template <typename T>

@@ -144,11 +144,20 @@ def describe_error_word(word: int) -> str:
     return "; ".join(msg for bit, msg in ERR_BITS.items() if word & bit) or f"unknown error bits {word}"
 
 
-def embedding(table, ids, out, num_tokens: int, err) -> None:
+def embedding(table, ids, out, num_tokens: int, err, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale."""
     _cuda(table, ids, out)
     V, H = table.shape
-    _check(lib().vob_embedding(_p(table), _p(ids), _p(out), num_tokens, H, V, _code(table.dtype), _p(err), _stream()),
-           "embedding")
+    _check(lib().vob_embedding(_p(table), _p(ids), _p(out), num_tokens, H, V, ctypes.c_float(scale), _code(table.dtype),
+                               _p(err), _stream()), "embedding")
+
+
+def softcap(logits, num_rows: int, cap: float) -> None:
+    """logits = cap * tanh(logits / cap), in place (float32 rows)."""
+    _cuda(logits)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    _check(lib().vob_softcap(_p(logits), ctypes.c_long(logits.stride(0)), num_rows, logits.shape[1], ctypes.c_float(cap),
+                             _stream()), "softcap")
 
 
 def add_rmsnorm(x, residual, weight, y, eps: float, has_residual: bool, err, rows=None, n_out: Optional[int] = None):

@@ -7,6 +7,9 @@ compute_logits(hidden) -> logits), with the step's batch descriptor as an explic
 instead of a shared mutex (crates/vllm-oxide/src/attention/mod.rs:34-38): `forward(ctx)` returns
 the residual stream before the last norm, `compute_logits(hidden, residual, ctx)` applies the last
 norm and the output product on the wanted rows only and returns float32 logits.
+
+What surrounds the blocks is data of the plan too: a scale on the embedded tokens, position parts that add
+to the embedding (`PositionEncoding.embed`), a soft cap on the logits.  Qwen3 uses none of the three.
 """
 from __future__ import annotations
 
@@ -29,7 +32,8 @@ class CausalLM:
         common = dict(positions=self.positions, dtype=dtype, device=device)
         self.blocks = [build_part("block", spec, **common) for spec in plan.layers]
         self.final_norm = build_part("norm", plan.final_norm, **common)
-        self.graph_safe = all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+        self.graph_safe = (all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+                           and all(p.graph_safe for p in self.positions.values()))
         self.embedding = None
         self.lm_head = None
         self.planes: List[Optional[CachePlane]] = [None] * plan.num_planes()
@@ -45,6 +49,8 @@ class CausalLM:
         specs = [TensorSpec(p.embedding_name, (p.vocab_size, p.hidden_size), "embedding")]
         if p.lm_head_name:
             specs.append(TensorSpec(p.lm_head_name, (p.vocab_size, p.hidden_size), "matrix", p.hidden_size))
+        for part in self.positions.values():
+            specs += part.tensor_specs()
         for b in self.blocks:
             specs += b.tensor_specs()
         specs += self.final_norm.tensor_specs()
@@ -54,6 +60,8 @@ class CausalLM:
         p = self.plan
         self.embedding = tensors[p.embedding_name].contiguous()
         self.lm_head = tensors[p.lm_head_name].contiguous() if p.lm_head_name else self.embedding
+        for part in self.positions.values():
+            part.load({s.name: tensors[s.name] for s in part.tensor_specs()})
         for b in self.blocks:
             b.load({s.name: tensors[s.name] for s in b.tensor_specs()})
         self.final_norm.load({s.name: tensors[s.name] for s in self.final_norm.tensor_specs()})
@@ -81,6 +89,8 @@ class CausalLM:
         """Bytes of every distinct weight tensor (a tied output matrix counts once)."""
         seen, total = set(), 0
         tensors = [self.embedding, self.lm_head] + self.final_norm.device_tensors()
+        for part in self.positions.values():
+            tensors += part.device_tensors()
         for b in self.blocks:
             tensors += b.device_tensors()
         for t in tensors:
@@ -93,7 +103,9 @@ class CausalLM:
     def forward(self, ctx):
         T = ctx.launch_tokens
         hidden = ctx.ws.get("embedded", T, self.plan.hidden_size, self.dtype)
-        kernels.embedding(self.embedding, ctx.token_ids, hidden, T, ctx.err)
+        kernels.embedding(self.embedding, ctx.token_ids, hidden, T, ctx.err, self.plan.embedding_scale)
+        for part in self.positions.values():
+            part.embed(hidden, ctx)
         residual = None
         for s in self.plan.order:
             plane = self.planes[s.plane] if s.plane is not None else None
@@ -104,6 +116,12 @@ class CausalLM:
     def compute_logits(self, hidden, residual, ctx) -> torch.Tensor:
         R = ctx.launch_rows
         normed, _ = self.final_norm.forward(hidden, residual, ctx, rows=ctx.logit_rows, n_rows=R, name="final_normed")
+        out = self._logits(normed, R, ctx)
+        if self.plan.logit_softcap > 0.0:
+            kernels.softcap(out, R, self.plan.logit_softcap)
+        return out
+
+    def _logits(self, normed, R: int, ctx) -> torch.Tensor:
         V = self.plan.vocab_size
         if self.dtype == torch.float32:
             return linear(normed, self.lm_head, ctx.ws.get_rows("logits", R, V, self.dtype), ctx)

@@ -36,6 +36,8 @@ class ModelPlan:
     order: List[ExecStep]
     eos_token_id: Optional[int] = None
     default_dtype: str = "bfloat16"
+    embedding_scale: float = 1.0           # the embedded tokens are multiplied by it
+    logit_softcap: float = 0.0             # > 0: logits = cap * tanh(logits / cap)
 
     def num_planes(self) -> int:
         return 1 + max((s.plane for s in self.order if s.plane is not None), default=-1)

@@ -160,6 +160,12 @@ NO_ROTATION = RotationRule(None, 0, False)
 
 
 class PositionEncoding(Part):
+    graph_safe = True      # the default embed() launches nothing
+
+    def embed(self, hidden: torch.Tensor, ctx) -> None:
+        """Adds what this encoding contributes to the embedded tokens, in place (absolute or learned positions: a table
+        row per `ctx.positions`); the default adds nothing.  Called once a step, after the embedding."""
+
     def rotation_rule(self) -> RotationRule:
         """The rule a mixer hands to its rotation kernel; a position encoding that rotates nothing (absolute positions
         added elsewhere, or none at all) keeps this default."""

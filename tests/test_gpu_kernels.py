@@ -817,6 +817,30 @@ def test_gemm_skinny_with_the_norm_in_front_and_the_residual_behind(M, N, K):
     kernels.gemm_skinny(x.to(DEV), w.to(DEV), acc, kernels.EPI_ADD, err)
     plain = (P.linear(x, w, torch.bfloat16).float() + before.float()).bfloat16()
     assert torch.allclose(acc.cpu().float(), plain.float(), rtol=2e-2, atol=2e-2) and err.item() == 0
+    # the norm in two halves: the adding product leaves stream * weight and the sums of squares behind, the product
+    # after it takes them instead of doing the norm's arithmetic itself; against the norm applied on the way, and plain
+    if N % 64 == 0:
+        wn2 = (1 + 0.2 * torch.randn(N, generator=g)).bfloat16()
+        w2 = (torch.randn(72, N, generator=g) / math.sqrt(N)).bfloat16().to(DEV)
+        acc2 = before.clone().to(DEV)
+        scaled = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        parts = torch.full((kernels.gemm_skinny_weight_tiles(N) * 16,), float("nan"), device=DEV)
+        kernels.gemm_skinny(x.to(DEV), w.to(DEV), acc2, kernels.EPI_ADD, err, emit=(wn2.float().to(DEV), scaled, parts))
+        assert torch.equal(acc2, acc)                                       # the stream itself is what it was
+        assert torch.equal(scaled.cpu(), (acc.cpu().float() * wn2.float()).bfloat16())
+        box = 8 if M <= 8 else 16
+        sums = parts[:kernels.gemm_skinny_weight_tiles(N) * box].view(-1, box).sum(0)[:M].cpu()
+        assert torch.allclose(sums, acc.cpu().float().pow(2).sum(-1), rtol=1e-5)
+        on_the_way = torch.empty(M, 72, dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_skinny(acc, w2, on_the_way, kernels.EPI_BF16, err, norm_weight=wn2.float().to(DEV), eps=eps)
+        ahead = torch.empty(M, 72, dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_skinny(scaled, w2, ahead, kernels.EPI_BF16, err, eps=eps, prenormed=parts)
+        normed2, _ = P.add_rms_norm(acc.cpu(), None, wn2, eps, torch.bfloat16)
+        want2 = P.linear(normed2, w2.cpu(), torch.bfloat16)
+        assert torch.allclose(ahead.cpu().float(), want2.float(), rtol=2e-2, atol=2e-2) and err.item() == 0
+        # the two ways differ only in the order the squares are added: a unit of bfloat16 here and there, no more
+        assert (ahead.float() - on_the_way.float()).abs().max() <= 2 ** -7 * on_the_way.float().abs().max()
+        assert (ahead != on_the_way).float().mean() < 0.01
     # norm in front of the fused activation
     if N % 16 == 0:
         I = N // 2

@@ -20,10 +20,16 @@
 //     add+norm kernel, and every kernel less in the chain of a layer saves about 4 us):
 //       - EPI_ADD rounds the product to bfloat16 and adds it to `out` in place: out is the residual stream,
 //         so the output product of the attention and the down product leave residual' = x + residual behind;
-//       - NORM reads that stream as its tokens and applies RMSNorm on the fly: the consumer warps multiply the
+//       - NORM 1 reads that stream as its tokens and applies RMSNorm on the fly: the consumer warps multiply the
 //         token fragments by the norm's weight in registers and sum their squares on the way (a block reads
 //         all of K for its tile anyway), and the epilogue scales every sum by 1/sqrt(mean square + eps) of its
-//         token, which is the same product up to the place where bfloat16 rounds.
+//         token, which is the same product up to the place where bfloat16 rounds;
+//       - that arithmetic on every fragment of every block costs a product about 2 us, so the product BEFORE can do
+//         it once instead: EPI_ADD, given the weight of the norm that follows, also writes bfloat16(stream * weight)
+//         to a second buffer and, per tile and token, the sum of the squares of the stream values it wrote;
+//         NORM 2 then takes that buffer as its tokens, runs the plain loop, adds the tiles' sums in a fixed order
+//         at its start and scales by 1/rms in the epilogue: the same values as NORM 1 up to the order in which
+//         the squares are added.
 //
 // Every wait on an mbarrier is bounded: a wait that runs out sets an error bit and a block-wide
 // abort flag; the block then waits (bounded again) for the copies it still has in flight and returns.
@@ -67,7 +73,9 @@ template <int R, int MT> struct SkStages { static constexpr int N = (VOB_SK_RING
 template <int R, int MT, int EPI, int NORM>
 __global__ void __launch_bounds__(SK_THREADS, 2)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, void* out,
-                   long ldo, int M, int N, int K, int num_tiles, const float* __restrict__ norm_w, float eps, int* err) {
+                   long ldo, int M, int N, int K, int num_tiles, const float* __restrict__ norm_w, float eps,
+                   const float* ss_parts, int ss_count, const float* __restrict__ emit_w, __nv_bfloat16* emit_xn,
+                   float* emit_ss, int* err) {
   constexpr int S = SkStages<R, MT>::N;
   constexpr int RT = R / 16, NT = MT / 8;
   constexpr int W_SLICE = R * 128, X_SLICE = MT * 128;
@@ -134,6 +142,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   } else {
     // ------------------------------------------------ consumers
     pdl_wait();   // they write `out`, which the kernel before this one may still read
+    if (NORM == 2) {
+      // 1/rms of every token from the sums of squares that the product before left per tile: a fixed order of additions
+      // (thread t adds the parts t / MT, t / MT + 128 / MT, ... of token t % MT, then one thread a token adds those)
+      constexpr int STEP = SK_CONSUMERS * 32 / MT;
+      float part = 0.f;
+      for (int p = (int)threadIdx.x / MT; p < ss_count; p += STEP) part += ss_parts[(long)p * MT + (int)threadIdx.x % MT];
+      red[threadIdx.x] = part;
+      asm volatile("bar.sync 1, %0;\n" ::"n"(SK_CONSUMERS * 32) : "memory");
+      if ((int)threadIdx.x < MT) {
+        float total = 0.f;
+#pragma unroll
+        for (int q = 0; q < STEP; ++q) total += red[q * MT + threadIdx.x];
+        sumsq[threadIdx.x] = 1.f / sqrtf(total / (float)K + eps);
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(SK_CONSUMERS * 32) : "memory");
+    }
     const int g = lane >> 2, tq = lane & 3;
     const int mi = lane >> 3, r8 = lane & 7;
     const int a_row = (mi & 1) * 8 + r8, a_chunk = mi >> 1;                       // W rows, ldmatrix x4
@@ -164,7 +188,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         // NORM: the norm's weights for this thread's columns of the stage, asked for before the wait for the stage
         // (they come from L2 and would otherwise stand between every ldmatrix and its mma)
         float2 nw[SK_KC / 16 / SK_CONSUMERS][2];
-        if (NORM) {
+        if (NORM == 1) {
 #pragma unroll
           for (int jj = 0; jj < SK_KC / 16 / SK_CONSUMERS; ++jj) {
             const int k0 = kc * SK_KC + (warp + jj * SK_CONSUMERS) * 16 + tq * 2;
@@ -192,7 +216,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             sk_ldmatrix_x2(b2, xt + c * X_SLICE + swizzled_offset(b_row, ch + b_chunk));
             b[0] = b2[0]; b[1] = b2[1]; b[2] = b[3] = 0;
           }
-          if (NORM) {
+          if (NORM == 1) {
             // b[0], b[1]: token g at columns k, k+1 and k+8, k+9 of this 16-column step; b[2], b[3]: token g + 8
             const float2 w0 = nw[jj][0], w1 = nw[jj][1];
 #pragma unroll
@@ -219,7 +243,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
       }
-      if (NORM) {
+      if (NORM == 1) {
         // the four lanes of a token hold different columns: add them, then one lane writes the warp's share
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -253,7 +277,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
           for (int w = 0; w < SK_CONSUMERS; ++w) { gate += red[(w * R + gr) * MT + tok]; up += red[(w * R + gr + 8) * MT + tok]; }
           if (NORM) {
-            const float inv = 1.f / sqrtf((sumsq[tok] + sumsq[16 + tok] + sumsq[32 + tok] + sumsq[48 + tok]) / (float)K + eps);
+            const float inv = NORM == 2 ? sumsq[tok]
+                                        : 1.f / sqrtf((sumsq[tok] + sumsq[16 + tok] + sumsq[32 + tok] + sumsq[48 + tok]) / (float)K + eps);
             gate *= inv;
             up *= inv;
           }
@@ -266,20 +291,33 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
         for (int i = 0; i < ADD_PER_THREAD; ++i) {
           const int idx = tid + i * SK_CONSUMERS * 32;
-          if (idx >= R * m_rows) break;
           const int tok = idx / R, r = idx % R;
           const long n = (long)tile * R + r;
-          if (n >= N) continue;
-          float v = 0.f;
+          float sq = 0.f;                                  // EPI_ADD with emit: the square of the stream value written here
+          if (idx < R * m_rows && n < N) {
+            float v = 0.f;
 #pragma unroll
-          for (int w = 0; w < SK_CONSUMERS; ++w) v += red[(w * R + r) * MT + tok];
-          if (NORM) v *= 1.f / sqrtf((sumsq[tok] + sumsq[16 + tok] + sumsq[32 + tok] + sumsq[48 + tok]) / (float)K + eps);
-          if (EPI == EPI_F32) {
-            reinterpret_cast<float*>(out)[(long)tok * ldo + n] = bf16_round(v);
-          } else if (EPI == EPI_ADD) {
-            reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(bf16_round(v) + prev[i]);
-          } else {
-            reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(v);
+            for (int w = 0; w < SK_CONSUMERS; ++w) v += red[(w * R + r) * MT + tok];
+            if (NORM == 1) v *= 1.f / sqrtf((sumsq[tok] + sumsq[16 + tok] + sumsq[32 + tok] + sumsq[48 + tok]) / (float)K + eps);
+            if (NORM == 2) v *= sumsq[tok];
+            if (EPI == EPI_F32) {
+              reinterpret_cast<float*>(out)[(long)tok * ldo + n] = bf16_round(v);
+            } else if (EPI == EPI_ADD) {
+              const float sv = bf16_round(bf16_round(v) + prev[i]);
+              reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(sv);
+              if (emit_xn) {
+                emit_xn[(long)tok * N + n] = __float2bfloat16_rn(sv * __ldg(emit_w + n));
+                sq = sv * sv;
+              }
+            } else {
+              reinterpret_cast<__nv_bfloat16*>(out)[(long)tok * ldo + n] = __float2bfloat16_rn(v);
+            }
+          }
+          if (EPI == EPI_ADD && emit_ss) {                  // the same for every thread of the block
+            // the R lanes that hold a token's rows of this tile add their squares; tokens beyond the batch give 0
+#pragma unroll
+            for (int o = R / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (r == 0 && tok < MT) emit_ss[(long)tile * MT + tok] = sq;
           }
         }
       }
@@ -290,9 +328,17 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
 }
 
+struct SkExtra {        // what only some products use
+  const float* ss_parts = nullptr;   // NORM 2: [ss_count][MT] sums of squares of the tokens, per tile of the product before
+  int ss_count = 0;
+  const float* emit_w = nullptr;     // EPI_ADD: weight [N] of the norm that follows,
+  __nv_bfloat16* emit_xn = nullptr;  //          where bfloat16(stream * weight) goes, [M, N],
+  float* emit_ss = nullptr;          //          and the sums of squares, [tiles][MT]
+};
+
 template <int R, int MT, int EPI, int NORM>
 static int skinny_launch(const CUtensorMap* tmW, const CUtensorMap* tmX, void* out, long ldo, int M, int N, int K,
-                         const float* norm_w, float eps, int* err, cudaStream_t stream) {
+                         const float* norm_w, float eps, const SkExtra& x, int* err, cudaStream_t stream) {
   constexpr int S = SkStages<R, MT>::N;
   const int smem = 1024 + S * SK_SLICES * (R + MT) * 128 + SK_CONSUMERS * (R * MT + 16) * (int)sizeof(float) + 2 * S * 8 + 16;
   static bool configured = false;
@@ -305,21 +351,26 @@ static int skinny_launch(const CUtensorMap* tmW, const CUtensorMap* tmX, void* o
   const int resident = 2 * sm_count();   // two blocks of this kernel fit an SM
   const int grid = num_tiles < resident ? num_tiles : resident;
   return launch_kernel(gemm_skinny_kernel<R, MT, EPI, NORM>, grid, SK_THREADS, smem, stream, *tmW, *tmX, out, ldo, M, N, K,
-                       num_tiles, norm_w, eps, err);
+                       num_tiles, norm_w, eps, x.ss_parts, x.ss_count, x.emit_w, x.emit_xn, x.emit_ss, err);
 }
 
 template <int R, int MT>
 static int skinny_dispatch(int epilogue, const CUtensorMap* tw, const CUtensorMap* tx, void* out, long ldo, int M, int N,
-                           int K, const float* norm_w, float eps, int* err, cudaStream_t stream) {
-  if (norm_w) {   // the norm in front is instantiated for the two products that follow a norm in a layer
-    if (epilogue == EPI_BF16) return skinny_launch<R, MT, EPI_BF16, 1>(tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream);
-    if (epilogue == EPI_SWIGLU) return skinny_launch<R, MT, EPI_SWIGLU, 1>(tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream);
+                           int K, const float* norm_w, float eps, const SkExtra& x, int* err, cudaStream_t stream) {
+  if (x.ss_parts) {   // the tokens come already multiplied by the norm's weight; 1/rms from the sums the product before left
+    if (epilogue == EPI_BF16) return skinny_launch<R, MT, EPI_BF16, 2>(tw, tx, out, ldo, M, N, K, nullptr, eps, x, err, stream);
+    if (epilogue == EPI_SWIGLU) return skinny_launch<R, MT, EPI_SWIGLU, 2>(tw, tx, out, ldo, M, N, K, nullptr, eps, x, err, stream);
     return VOB_UNSUPPORTED;
   }
-  if (epilogue == EPI_BF16) return skinny_launch<R, MT, EPI_BF16, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, err, stream);
-  if (epilogue == EPI_F32) return skinny_launch<R, MT, EPI_F32, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, err, stream);
-  if (epilogue == EPI_SWIGLU) return skinny_launch<R, MT, EPI_SWIGLU, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, err, stream);
-  if (epilogue == EPI_ADD) return skinny_launch<R, MT, EPI_ADD, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, err, stream);
+  if (norm_w) {   // the norm in front is instantiated for the two products that follow a norm in a layer
+    if (epilogue == EPI_BF16) return skinny_launch<R, MT, EPI_BF16, 1>(tw, tx, out, ldo, M, N, K, norm_w, eps, x, err, stream);
+    if (epilogue == EPI_SWIGLU) return skinny_launch<R, MT, EPI_SWIGLU, 1>(tw, tx, out, ldo, M, N, K, norm_w, eps, x, err, stream);
+    return VOB_UNSUPPORTED;
+  }
+  if (epilogue == EPI_BF16) return skinny_launch<R, MT, EPI_BF16, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, x, err, stream);
+  if (epilogue == EPI_F32) return skinny_launch<R, MT, EPI_F32, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, x, err, stream);
+  if (epilogue == EPI_SWIGLU) return skinny_launch<R, MT, EPI_SWIGLU, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, x, err, stream);
+  if (epilogue == EPI_ADD) return skinny_launch<R, MT, EPI_ADD, 0>(tw, tx, out, ldo, M, N, K, nullptr, 0.f, x, err, stream);
   return VOB_BAD_ARGUMENT;
 }
 
@@ -347,18 +398,29 @@ VOB_API int vob_gemm_skinny_token_box(int M) { return M <= 8 ? 8 : 16; }
 // epilogue: 0 bfloat16 out [M,N]; 1 float out [M,N] (rounded to bfloat16 first); 2 SiLU(gate)*up over rows that
 // alternate in groups of eight between gate and up, out [M,N/2] bfloat16; 3 out [M,N] bfloat16 += the product rounded to
 // bfloat16 (the residual stream).  norm_w (may be null; epilogues 0 and 2): float [K], the weight of an RMSNorm with
-// `eps` that is applied to x on the way.  Needs M <= 16.
+// `eps` that is applied to x on the way.  ss_parts (may be null; instead of norm_w): x is already the tokens times the
+// norm's weight, and ss_parts [ss_count][8 or 16] (the token rows of a box for this M) holds sums of squares of the
+// unscaled tokens that add up to each token's; the product is scaled by 1/rms.  emit_w / emit_xn / emit_ss (all or none;
+// epilogue 3): beside the sum into `out`, bfloat16(out * emit_w) goes to emit_xn [M, N] and, per tile of
+// vob_gemm_skinny_weight_box(N) rows and token, the sum of the squares of the new values of `out` to emit_ss.  Needs M <= 16.
 VOB_API int vob_gemm_skinny(const void* map_w, const void* map_x, void* out, long ldo, int M, int N, int K, int epilogue,
-                            const float* norm_w, float eps, int* err, cudaStream_t stream) {
+                            const float* norm_w, float eps, const float* ss_parts, int ss_count, const float* emit_w,
+                            void* emit_xn, float* emit_ss, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 16 || K <= 0 || K % 64 || !map_w || !map_x) return VOB_UNSUPPORTED;
   if (epilogue == EPI_SWIGLU && N % 16) return VOB_BAD_ARGUMENT;
   if (norm_w && (uintptr_t)norm_w % 8) return VOB_BAD_ARGUMENT;
+  if (ss_parts && (norm_w || ss_count <= 0)) return VOB_BAD_ARGUMENT;
+  if ((emit_w != nullptr) != (emit_xn != nullptr) || (emit_w != nullptr) != (emit_ss != nullptr)) return VOB_BAD_ARGUMENT;
+  if (emit_w && epilogue != EPI_ADD) return VOB_BAD_ARGUMENT;
+  SkExtra x;
+  x.ss_parts = ss_parts; x.ss_count = ss_count;
+  x.emit_w = emit_w; x.emit_xn = (__nv_bfloat16*)emit_xn; x.emit_ss = emit_ss;
   const CUtensorMap* tw = (const CUtensorMap*)map_w;
   const CUtensorMap* tx = (const CUtensorMap*)map_x;
   const bool tall = vob_gemm_skinny_weight_box(N) == 32;
-  if (M <= 8) return tall ? skinny_dispatch<32, 8>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream)
-                          : skinny_dispatch<16, 8>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream);
-  return tall ? skinny_dispatch<32, 16>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream)
-              : skinny_dispatch<16, 16>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, err, stream);
+  if (M <= 8) return tall ? skinny_dispatch<32, 8>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, x, err, stream)
+                          : skinny_dispatch<16, 8>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, x, err, stream);
+  return tall ? skinny_dispatch<32, 16>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, x, err, stream)
+              : skinny_dispatch<16, 16>(epilogue, tw, tx, out, ldo, M, N, K, norm_w, eps, x, err, stream);
 }

@@ -34,6 +34,8 @@ class StepContext:
         self.launch_tokens = self.num_tokens if launch_tokens is None else launch_tokens
         self.launch_rows = self.num_rows if launch_rows is None else launch_rows
         self.launch_requests = L.B
+        self.next_norm = None      # hints between blocks within a step (models/causal_lm.py sets them, parts/block.py reads them)
+        self.prenormed = None
         self.token_ids = dev[L.token_ids:L.token_ids + L.T]
         self.positions = dev[L.positions:L.positions + L.T]
         self.token_req = dev[L.token_req:L.token_req + L.T]

@@ -361,12 +361,23 @@ def gemm_skinny_supported(x, w) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_skinny(x, w, out, epilogue: int, err, norm_weight=None, eps: float = 0.0) -> None:
+def gemm_skinny_weight_tiles(n_rows: int) -> int:
+    """The number of row tiles the weight-streaming product cuts a matrix of `n_rows` rows into."""
+    box = int(lib().vob_gemm_skinny_weight_box(ctypes.c_long(n_rows)))
+    return (n_rows + box - 1) // box
+
+
+def gemm_skinny(x, w, out, epilogue: int, err, norm_weight=None, eps: float = 0.0, emit=None, prenormed=None) -> None:
     """out = x @ w^T for at most 16 rows of x (see gemm_skinny_supported); epilogue EPI_BF16 (out bfloat16 [M,N]),
     EPI_F32 (out float32 [M,N], rounded to bfloat16 first), EPI_SWIGLU (the rows of w alternate in groups of
     eight between gate and up; out bfloat16 [M,N/2] = SiLU(gate) * up) or EPI_ADD (out bfloat16 [M,N] += the
     product rounded to bfloat16: out is the residual stream).  With `norm_weight` (float [K]; EPI_BF16 and EPI_SWIGLU)
-    the product is that of RMSNorm(x) * norm_weight, the norm computed on the way."""
+    the product is that of RMSNorm(x) * norm_weight, the norm computed on the way.
+
+    The same norm in two halves, for a chain of products: `emit=(weight, scaled, parts)` (EPI_ADD) makes the product
+    leave bfloat16(out * weight) in `scaled` [M,N] and per-tile sums of the squares of the new `out` in `parts`
+    (float, gemm_skinny_weight_tiles(N) * 16 entries are enough) for the norm that follows; `prenormed=parts` (EPI_BF16
+    and EPI_SWIGLU, with `eps`) takes x to be such a `scaled` buffer and scales the product by 1/rms from the parts."""
     _cuda(x, w, out, norm_weight)
     if not gemm_skinny_supported(x, w):
         raise KernelError("gemm_skinny: this product is not supported (bfloat16, at most 16 rows, K a multiple of 64, 16-byte aligned rows)")
@@ -377,10 +388,24 @@ def gemm_skinny(x, w, out, epilogue: int, err, norm_weight=None, eps: float = 0.
     assert out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16)
     if norm_weight is not None:
         assert epilogue in (EPI_BF16, EPI_SWIGLU) and norm_weight.dtype == torch.float32 and norm_weight.numel() == K
+    box_m = 8 if M <= 8 else 16
+    ss_parts, ss_count = None, 0
+    if prenormed is not None:
+        assert norm_weight is None and epilogue in (EPI_BF16, EPI_SWIGLU) and prenormed.dtype == torch.float32
+        ss_parts, ss_count = prenormed, gemm_skinny_weight_tiles(K)      # the product before wrote K outputs a token
+        assert prenormed.numel() >= ss_count * box_m
+    emit_w = emit_xn = emit_ss = None
+    if emit is not None:
+        emit_w, emit_xn, emit_ss = emit
+        _cuda(emit_w, emit_xn, emit_ss)
+        assert epilogue == EPI_ADD and emit_w.dtype == torch.float32 and emit_w.numel() == N
+        assert emit_xn.dtype == torch.bfloat16 and emit_xn.is_contiguous() and emit_xn.shape == (M, N)
+        assert emit_ss.dtype == torch.float32 and emit_ss.numel() >= gemm_skinny_weight_tiles(N) * box_m
     map_w = tensor_map(w, int(lib().vob_gemm_skinny_weight_box(ctypes.c_long(N))), 4)
-    map_x = tensor_map(x, 8 if M <= 8 else 16, 4)
+    map_x = tensor_map(x, box_m, 4)
     _check(lib().vob_gemm_skinny(map_w, map_x, _p(out), ctypes.c_long(out.stride(0)), M, N, K, epilogue, _p(norm_weight),
-                                 ctypes.c_float(eps), _p(err), _stream()), "gemm_skinny")
+                                 ctypes.c_float(eps), _p(ss_parts), ss_count, _p(emit_w), _p(emit_xn), _p(emit_ss),
+                                 _p(err), _stream()), "gemm_skinny")
 
 
 def gemm_skinny_set_wait_limit(tries: int, withhold_copies: bool = False) -> None:

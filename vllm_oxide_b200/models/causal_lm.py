@@ -107,10 +107,16 @@ class CausalLM:
         for part in self.positions.values():
             part.embed(hidden, ctx)
         residual = None
-        for s in self.plan.order:
+        order = self.plan.order
+        ctx.prenormed = None
+        for i, s in enumerate(order):
             plane = self.planes[s.plane] if s.plane is not None else None
             state = self.states[s.plane] if s.plane is not None else None
+            # a hint for blocks that can use it: the first norm of the block that runs next (its arithmetic may be done
+            # by the product that writes the residual stream); the last block has none
+            ctx.next_norm = getattr(self.blocks[order[i + 1].layer], "input_norm", None) if i + 1 < len(order) else None
             hidden, residual = self.blocks[s.layer].forward(hidden, residual, ctx, plane, state, s.write_cache)
+        ctx.next_norm = ctx.prenormed = None
         return hidden, residual
 
     def compute_logits(self, hidden, residual, ctx) -> torch.Tensor:

@@ -16,7 +16,7 @@ import torch
 
 from .. import kernels
 from ..weights.loader import TensorSpec
-from .base import NO_ROTATION, CacheSpec, Mixer, register_part
+from .base import NO_ROTATION, CacheSpec, Mixer, Prenormed, register_part
 from .linear import linear
 
 
@@ -98,20 +98,30 @@ class Attention(Mixer):
         attn = ctx.ws.get("attn_out", T, self.nh * self.hd, stream.dtype)
         return (kernels.gemm_skinny_supported(stream, self.wqkv) and kernels.gemm_skinny_supported(attn, self.wo))
 
-    def forward_on_stream(self, stream, norm, ctx, cache, state=None, write_cache: bool = True) -> None:
+    def forward_on_stream(self, stream, norm, ctx, cache, state=None, write_cache: bool = True, prenormed=None,
+                          emit_norm=None):
         """stream += attention(RMSNorm(stream)): the norm is applied inside the q|k|v product, the sum made by the
-        output product."""
+        output product.  `prenormed` (a `Prenormed` of `norm`, left by the product that wrote the stream) spares the
+        q|k|v product the norm's arithmetic; with `emit_norm` the output product leaves such a half-done norm behind
+        for the part that follows, and it is returned."""
         T = stream.shape[0]
         width = (self.nh + 2 * self.kvh) * self.hd
         qkv = ctx.ws.get("qkv", T, width, stream.dtype)
-        kernels.gemm_skinny(stream, self.wqkv, qkv, kernels.EPI_BF16, ctx.err, norm_weight=norm.weight, eps=norm.eps)
+        if prenormed is not None:
+            kernels.gemm_skinny(prenormed.scaled, self.wqkv, qkv, kernels.EPI_BF16, ctx.err, eps=norm.eps,
+                                prenormed=prenormed.parts)
+        else:
+            kernels.gemm_skinny(stream, self.wqkv, qkv, kernels.EPI_BF16, ctx.err, norm_weight=norm.weight, eps=norm.eps)
         g = cache.group
         kernels.qk_norm_rope_kv_write(qkv, self.bqkv, ctx.positions, ctx.slot_mapping[g], self.wq_norm, self.wk_norm,
                                       self.rotation, cache.k, cache.v, T, self.nh, self.kvh, self.hd, self.eps,
                                       write_cache, ctx.err)
         attn = ctx.ws.get("attn_out", T, self.nh * self.hd, stream.dtype)
         self.attend(qkv, width, attn, cache, ctx, T)
-        kernels.gemm_skinny(attn, self.wo, stream, kernels.EPI_ADD, ctx.err)
+        left = leave_prenormed(emit_norm, "after_mixer", stream, ctx)
+        kernels.gemm_skinny(attn, self.wo, stream, kernels.EPI_ADD, ctx.err,
+                            emit=(emit_norm.weight, left.scaled, left.parts) if left else None)
+        return left
 
     def attend(self, qkv, q_stride, out, cache, ctx, T):
         """bfloat16: decoding requests (one token) go to the split-key tensor-core kernel, requests with a
@@ -136,6 +146,16 @@ class Attention(Mixer):
 
 
 DECODE_BLOCKS_PER_SM = 2   # blocks of the decode attention kernel that fit an SM (its shared memory decides)
+
+
+def leave_prenormed(norm, name: str, stream, ctx) -> Optional[Prenormed]:
+    """Buffers for the half-done norm that a product adding into `stream` leaves for `norm` (None: nothing to leave)."""
+    if norm is None or getattr(norm, "weight", None) is None:
+        return None
+    T, H = stream.shape
+    scaled = ctx.ws.get("stream_scaled_" + name, T, H, stream.dtype)
+    parts = ctx.ws.get_flat("stream_squares_" + name, kernels.gemm_skinny_weight_tiles(H) * 16, torch.float32)
+    return Prenormed(norm, scaled, parts)
 
 
 def decode_splits(num_requests: int, kv_heads: int, max_keys: int, num_sms: int) -> int:

@@ -72,6 +72,16 @@ class CachePlane:
     data: Optional[torch.Tensor] = None
 
 
+@dataclass
+class Prenormed:
+    """One half of an RMSNorm, done ahead by the product that wrote the residual stream: `scaled` = bfloat16(stream *
+    norm.weight) and `parts`, sums of squares of the stream that add up to each token's (see kernels.gemm_skinny).  The
+    product that follows `norm` takes `scaled` as its tokens and applies 1/rms itself."""
+    norm: "Norm"
+    scaled: torch.Tensor
+    parts: torch.Tensor
+
+
 class Workspace:
     """Activation buffers with fixed addresses: allocated once for the largest step and handed out
     by name, so that a step captured in a CUDA graph finds them where they were."""

@@ -17,9 +17,15 @@ from .norm import RMSNorm
 # Decode-sized steps keep the residual stream inside the products of the attention and the feed-forward (see
 # PreNormBlock._keeps_stream); False runs the separate add+norm kernels always.
 STREAM_IN_PRODUCTS = True
-# Measured at Qwen3-8B sizes: 323 against 314 tokens/s at batch 1, 2,385 against 2,306 at batch 8, no gain at batch 16
-# (the norm's arithmetic on 16-token fragments costs what the two kernels saved).
-STREAM_MAX_TOKENS = 8
+# Every step the weight-streaming product takes (up to 16 tokens).  Measured at Qwen3-8B sizes against the separate
+# add+norm kernels: 323 against 314 tokens/s at batch 1, 2,385 against 2,306 at batch 8 with the norm's arithmetic inside
+# the loop of the product that follows the norm (at batch 16 that arithmetic cost what the two kernels saved); with
+# NORM_AHEAD the step takes 3.01 against 3.12 ms at batch 1, 3.27 against 3.42 at batch 8, 3.91 against 4.09 at batch 16.
+STREAM_MAX_TOKENS = 16
+# The product that writes the stream also does the arithmetic of the norm that follows (stream * weight, sums of squares
+# per tile), so the next product runs its plain loop and only scales by 1/rms at its end: about 2 us less for each of
+# the two products a layer that follow a norm.
+NORM_AHEAD = True
 
 
 class PreNormBlock(Block):
@@ -47,9 +53,16 @@ class PreNormBlock(Block):
         `residual` (the stream); this block leaves it so too when its parts can keep the stream inside their products."""
         if (hidden is None or residual is None) and self._keeps_stream(hidden if residual is None else residual, ctx):
             stream = hidden if residual is None else residual
-            self.mixer.forward_on_stream(stream, self.input_norm, ctx, cache, state, write_cache)
-            self.feed_forward.forward_on_stream(stream, self.post_mixer_norm, ctx)
+            # the half of this block's first norm that the block before may have left; what this block leaves for the next
+            ahead = getattr(ctx, "prenormed", None)
+            ahead = ahead if NORM_AHEAD and ahead is not None and ahead.norm is self.input_norm else None
+            after = self.mixer.forward_on_stream(stream, self.input_norm, ctx, cache, state, write_cache, prenormed=ahead,
+                                                 emit_norm=self.post_mixer_norm if NORM_AHEAD else None)
+            nxt = getattr(ctx, "next_norm", None) if NORM_AHEAD else None
+            ctx.prenormed = self.feed_forward.forward_on_stream(stream, self.post_mixer_norm, ctx, prenormed=after,
+                                                                emit_norm=nxt if isinstance(nxt, RMSNorm) else None)
             return None, stream
+        ctx.prenormed = None
         normed, residual = self.input_norm.forward(hidden, residual, ctx)
         mixed = self.mixer.forward(normed, ctx, cache, state, write_cache)
         normed, residual = self.post_mixer_norm.forward(mixed, residual, ctx)

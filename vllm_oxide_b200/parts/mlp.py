@@ -60,12 +60,21 @@ class SwiGLU(FeedForward):
         return (self.interleaved and kernels.gemm_skinny_supported(stream, self.wgu)
                 and kernels.gemm_skinny_supported(act, self.wdown))
 
-    def forward_on_stream(self, stream, norm, ctx) -> None:
+    def forward_on_stream(self, stream, norm, ctx, prenormed=None, emit_norm=None):
         """stream += down(SiLU(gate) * up) of RMSNorm(stream): the norm inside the gate|up product, the sum made by
-        the down product."""
+        the down product.  `prenormed` / `emit_norm` as in the attention part: the norm's arithmetic done by the product
+        before, and left behind for the part after."""
+        from .attention import leave_prenormed
         act = ctx.ws.get("act", stream.shape[0], self.I, stream.dtype)
-        kernels.gemm_skinny(stream, self.wgu, act, kernels.EPI_SWIGLU, ctx.err, norm_weight=norm.weight, eps=norm.eps)
-        kernels.gemm_skinny(act, self.wdown, stream, kernels.EPI_ADD, ctx.err)
+        if prenormed is not None:
+            kernels.gemm_skinny(prenormed.scaled, self.wgu, act, kernels.EPI_SWIGLU, ctx.err, eps=norm.eps,
+                                prenormed=prenormed.parts)
+        else:
+            kernels.gemm_skinny(stream, self.wgu, act, kernels.EPI_SWIGLU, ctx.err, norm_weight=norm.weight, eps=norm.eps)
+        left = leave_prenormed(emit_norm, "after_feed_forward", stream, ctx)
+        kernels.gemm_skinny(act, self.wdown, stream, kernels.EPI_ADD, ctx.err,
+                            emit=(emit_norm.weight, left.scaled, left.parts) if left else None)
+        return left
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -386,23 +386,31 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     const unsigned fo_addr = smem_addr(fo), fl_addr = smem_addr(fl);
     for (int idx = split * DT_THREADS + threadIdx.x; idx < G * HD; idx += num_splits * DT_THREADS) {
       const int r = idx / HD;
-      float M = -INFINITY;
-      for (int sp = 0; sp < num_splits; ++sp) {
-        unsigned ra; float lse;
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(fl_addr + r * 4), "r"(sp));
-        asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(lse) : "r"(ra) : "memory");
-        M = fmaxf(M, lse);
+      // every block's log-sum-exp and value for this output: all the loads from the other blocks' shared memory are
+      // issued before the first result is used (one after the other they cost a round trip across the cluster each,
+      // sixteen of them with eight splits: more than a microsecond)
+      float lse[8], v[8];
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) {
+        lse[sp] = -INFINITY;
+        v[sp] = 0.f;
+        if (sp < num_splits) {
+          unsigned ra, rb;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(fl_addr + r * 4), "r"(sp));
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(rb) : "r"(fo_addr + idx * 4), "r"(sp));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(lse[sp]) : "r"(ra) : "memory");
+          asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v[sp]) : "r"(rb) : "memory");
+        }
       }
+      float M = -INFINITY;
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) M = fmaxf(M, lse[sp]);
       float W = 0.f, O = 0.f;
-      for (int sp = 0; sp < num_splits; ++sp) {
-        unsigned ra, rb; float lse, v;
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(fl_addr + r * 4), "r"(sp));
-        asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(lse) : "r"(ra) : "memory");
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(rb) : "r"(fo_addr + idx * 4), "r"(sp));
-        asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(rb) : "memory");
-        const float w = lse == -INFINITY ? 0.f : fast_exp2(lse - M);
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) {        // in the order of the splits; a split that is not there weighs nothing
+        const float w = lse[sp] == -INFINITY ? 0.f : fast_exp2(lse[sp] - M);
         W += w;
-        O += w * v;
+        O += w * v[sp];
       }
       out[(size_t)t * nh * HD + (size_t)(kh * G) * HD + idx] = __float2bfloat16_rn(W > 0.f ? O / W : 0.f);
     }

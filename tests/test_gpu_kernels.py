@@ -795,7 +795,8 @@ def test_gemm_skinny_swiglu(M, I, K):
     assert torch.allclose(out.cpu().float(), want.float(), rtol=2e-2, atol=2e-2) and err.item() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 6144, 4096), (5, 331, 320), (13, 4096, 1024), (16, 520, 192), (3, 9472, 768)])
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 6144, 4096), (5, 331, 320), (13, 4096, 1024), (16, 520, 192), (3, 9472, 768),
+                                   (12, 6400, 256), (16, 128, 64), (9, 20032, 128)])
 def test_gemm_skinny_with_the_norm_in_front_and_the_residual_behind(M, N, K):
     """The residual stream kept inside the products: RMSNorm of the tokens applied on the way (plain: norm, then the
     product of the rounded result), and the product added to its output in place."""

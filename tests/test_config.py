@@ -94,10 +94,11 @@ def test_decode_attention_split_counts():
     from vllm_oxide_b200.parts.attention import decode_splits
     assert decode_splits(1, 8, 100, 148) == 1 and decode_splits(1, 8, 300, 148) == 2
     assert decode_splits(1, 8, 2304, 148) == 8 and decode_splits(8, 8, 2304, 148) == 4 and decode_splits(64, 8, 2304, 148) == 1
-    assert decode_splits(1, 8, 40960, 148) == 16 and decode_splits(2, 8, 32768, 148) == 16 and decode_splits(3, 8, 32768, 148) == 12
+    assert decode_splits(1, 8, 40960, 148) == 32 and decode_splits(2, 8, 32768, 148) == 16 and decode_splits(3, 8, 32768, 148) == 12
+    assert decode_splits(1, 8, 8192, 148) == 16 and decode_splits(1, 16, 32768, 148) == 16
     assert decode_splits(4, 8, 16384, 148) == 8          # 9 would fit: not enough to leave the cluster for
     assert decode_splits(8, 8, 32768, 148) == 4
     for requests in (1, 2, 3, 5, 8, 13, 40, 300):
         for keys in (1, 63, 64, 65, 1000, 8191, 8192, 100000):
             s = decode_splits(requests, 4, keys, 148)
-            assert 1 <= s <= 16 and (s == 1 or 2 * s <= -(-keys // 64))
+            assert 1 <= s <= 32 and (s == 1 or 2 * s <= -(-keys // 64))

@@ -403,6 +403,7 @@ DECODE_CASES = [  # nh, kvh, hd, block_size, window, ctx_lens, splits
     (32, 8, 128, 256, 0, [2050, 701, 100], 8),
     (8, 2, 64, 64, 0, [1000, 130], 6),
     (32, 8, 128, 256, 0, [2050], 16),            # more: merged by the second kernel
+    (32, 8, 128, 256, 0, [16500], 32),           # one long request: 32 splits of 8 tiles
 ]
 
 

@@ -163,10 +163,12 @@ def decode_splits(num_requests: int, kv_heads: int, max_keys: int, num_sms: int)
     (DECODE_BLOCKS_PER_SM blocks on each of the device's SMs), but at least two 64-key tiles per split.  Up to 8 the blocks of a
     (request, kv head) merge their results as a thread-block cluster, without a second kernel; beyond that a second
     kernel merges them, which pays only for few requests with long contexts (one request of 32,000 keys: 56 us with
-    8 splits, 44 us with 16), so more than 8 are taken only from 8,192 keys on and only if at least 12 fit."""
+    8 splits, 44 us with 16, 37 us with 32), so more than 8 are taken only from 8,192 keys on and only if at least 12
+    fit, and 32 only from 16,384 keys on and only if all 32 fit (with 18 of them two requests were slower than with 16)."""
     tiles = -(-max_keys // 64)
     fit = (DECODE_BLOCKS_PER_SM * num_sms) // max(1, num_requests * kv_heads)
-    splits = max(1, min(fit, tiles // 2, 16 if tiles >= 128 else 8))
+    most = 8 if tiles < 128 else (32 if tiles >= 256 and fit >= 32 else 16)
+    splits = max(1, min(fit, tiles // 2, most))
     return splits if splits <= 8 or splits >= 12 else 8
 
 

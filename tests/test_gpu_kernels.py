@@ -417,6 +417,43 @@ def test_attention_decode(case, use_tma):
     assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
 
 
+MANY_DECODE_CASES = [  # nh, kvh, hd, block_size, window, requests: more (request, kv head) pairs than blocks fit the GPU
+    (16, 8, 128, 16, 0, 75),
+    (32, 8, 128, 256, 0, 80),
+    (8, 8, 64, 48, 30, 90),
+    (16, 16, 64, 64, 0, 40),
+    (32, 2, 128, 64, 0, 160),      # sixteen heads per kv head: the largest merge buffer, fewer blocks fit
+    (12, 4, 192, 32, 100, 100),
+]
+
+
+@pytest.mark.parametrize("case", MANY_DECODE_CASES)
+def test_attention_decode_of_many_requests_with_persistent_blocks(case):
+    """One split and more pairs than resident blocks: persistent blocks take several pairs each, of very different
+    lengths (one key, a page's edge, hundreds of keys), with requests that are no decoding requests among them.
+    The result agrees with the plain formula and, bit for bit, with one block per pair."""
+    from vllm_oxide_b200 import kernels
+    nh, kvh, hd, bs, window, n = case
+    g = torch.Generator().manual_seed(n)
+    ctx_lens = [int(x) for x in torch.randint(1, 500, (n,), generator=g)]
+    ctx_lens[:6] = [1, bs, bs + 1, 63, 64, 65]
+    q_lens = [1] * n
+    for i in range(7, n, 9):               # portions of prompts: the decode kernel leaves their rows alone
+        q_lens[i] = 2
+        ctx_lens[i] = max(ctx_lens[i], 2)
+    fn = decode_attention(1)
+    got, want = run_attention(fn, torch.bfloat16, nh, kvh, hd, bs, window, q_lens, ctx_lens)
+    starts = np.cumsum([0] + q_lens)
+    rows = torch.tensor([int(starts[b]) for b in range(n) if q_lens[b] == 1])
+    assert torch.allclose(got[rows], want[rows], rtol=2e-2, atol=2e-2)
+    kernels.attention_decode_persistent(hd, False)
+    try:
+        per_pair, _ = run_attention(fn, torch.bfloat16, nh, kvh, hd, bs, window, q_lens, ctx_lens)
+    finally:
+        kernels.attention_decode_persistent(hd, True)
+    assert torch.equal(got[rows], per_pair[rows])
+
+
 @pytest.mark.parametrize("key_pos,window,expect_hit", [(3, 0, True), (255, 0, True), (256, 0, True), (511, 0, True),
                                                        (800 - 64, 64, True), (800 - 65, 64, False), (799, 0, True)])
 def test_attention_decode_reads_the_right_far_key(key_pos, window, expect_hit):

@@ -419,6 +419,266 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
+
+// ---- many decoding requests, one split each ---------------------------------------------------------------------------
+// With more (request, kv head) pairs than blocks fit the GPU, a block of the kernel above lives for a dozen tiles, and a
+// good part of that is its start: the look-up of its pages, the first copies, nothing to compute on yet.  Here the blocks
+// are persistent instead.  Block i begins with pair i and takes its further pairs from a counter in device memory (so
+// that requests of very different lengths spread as evenly as blocks given out by the hardware would), and its producer
+// warp runs AHEAD across pairs: the ring of stages never drains between two pairs, so the pages of the next pair are
+// looked up and its first tiles are on their way while the consumer warps still work on the pair before.  The producer
+// tells the consumers which pair a tile opens through a small queue in shared memory, written before the tile's
+// mbarrier is armed; after its last pair it sends an entry that says "no more" the same way.  The four warps' results of a
+// pair meet in a buffer of their own (not in the ring, which is busy), between two barriers of the consumer warps alone.
+// Same tiles, same products, same order of additions as the kernel above with one split: the same bits.
+//
+// The counter: the producer takes from it only after it has waited for the kernels before this one, and a kernel is done
+// only when each of its blocks has; so no launch of an earlier step of the same stream still uses the counter then.  The
+// last block to leave sets it back to zero.  Launches of this kernel that overlap in time (two streams) would share the
+// counter and are not supported: the engine runs its steps on one stream.
+constexpr int DI_MERGE_FLOATS(int G) { return 2 * DEC_WARPS * 16 + DEC_WARPS * G * HD; }
+constexpr int DI_DRAW_AHEAD = 2;                          // tiles before a pair's last at which the next pair is drawn
+constexpr int DI_QUEUE = 8;                               // entries; the producer is at most DT_STAGES + 1 pairs ahead
+static __device__ unsigned vob_decode_pairs_taken[2];     // pairs given out beyond the first of each block; blocks that left
+
+__global__ void __launch_bounds__(DT_THREADS)
+attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                                  const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
+                                  const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
+                                  const int* __restrict__ context_lens, int num_requests, int nh, int kvh, int block_size,
+                                  int window, float scale, long num_pages, int box_keys, int* err) {
+  extern __shared__ __align__(1024) char smem_raw[];
+  char* smem = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int RING_BYTES = DT_STAGES * DT_STAGE_BYTES;
+  const int G = nh / kvh;
+  float* wm = reinterpret_cast<float*>(smem + RING_BYTES);    // [DEC_WARPS][16]
+  float* wl = wm + DEC_WARPS * 16;
+  float* wo = wl + DEC_WARPS * 16;                            // [DEC_WARPS][G][HD]
+  int4* queue = reinterpret_cast<int4*>(wo + DEC_WARPS * G * HD);   // (pair or -1, its token's row, its position, -)
+  uint64_t* full = reinterpret_cast<uint64_t*>(queue + DI_QUEUE);
+  uint64_t* empty = full + DT_STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + DT_STAGES);
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < DT_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], DEC_WARPS); }
+    *abort_flag = 0;
+    tma_prefetch_map(&tmK);
+    tma_prefetch_map(&tmV);
+  }
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  __syncthreads();
+  const int num_items = num_requests * kvh;
+
+  if (warp == DEC_WARPS) {
+    // ------------------------------------------------ producer: lane 0 issues, all lanes look pages up
+    bool ok = true, waited = false;                   // `waited`: this warp has waited for the kernels before this one
+    long ring = 0;                                    // stages armed so far, over all pairs: stage = ring % DT_STAGES
+    int pairs = 0;                                    // pairs announced to the consumers
+    int item = blockIdx.x;
+    while (ok && item < num_items) {
+      // The pair after this one is drawn a few tiles before this one's last, so that the counter's answer is back when
+      // this pair's tiles are out, yet no block holds a pair long before it can begin it (a block that has not waited
+      // yet draws after its tiles: the counter is this launch's only after the launches before it are done).
+      int next = -1;
+      bool drawn = false;
+      const int b = item / kvh, kh = item % kvh;
+      const int t = cu_q[b];
+      if (cu_q[b + 1] - t == 1) {                     // a decoding request (the others are the prefill kernel's)
+        const int pos = context_lens[b] - 1;
+        const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const int start = lo & ~(box_keys - 1);
+        const int end = pos + 1;
+        const int n_tiles = (end - start + DEC_TILE - 1) / DEC_TILE;
+        const int* table = block_tables + (size_t)b * table_stride;
+        WarpPages wp;
+        for (int it = 0; it < n_tiles; ++it, ++ring) {
+          const int s = (int)(ring % DT_STAGES);
+          wp.advance(table, block_size, start, it, lane, lo, end);
+          int pg[4];
+#pragma unroll
+          for (int run = 0; run < 4; ++run) pg[run] = wp.page(it, run);
+          if (waited && !drawn && it + DI_DRAW_AHEAD >= n_tiles) {
+            if (lane == 0) next = (int)min((unsigned)num_items, gridDim.x + atomicAdd(&vob_decode_pairs_taken[0], 1u));
+            drawn = true;
+          }
+          if (lane == 0) {
+            if (ring >= DT_STAGES) ok = mbar_wait(&empty[s], (unsigned)(((ring / DT_STAGES) - 1) & 1), abort_flag, err);
+            if (ok) {
+              const int tile_start = start + it * DEC_TILE;
+              // only the tile that holds this step's key waits for the kernels before this one (once for the block)
+              if (!waited && tile_start + DEC_TILE > pos) { pdl_wait(); waited = true; }
+              if (it == 0) queue[pairs % DI_QUEUE] = make_int4(item, t, pos, 0);   // before the arrival below releases it
+              mbar_expect_tx(&full[s], (unsigned)DT_STAGE_BYTES);
+              char* kt = smem + s * DT_STAGE_BYTES;
+              if (box_keys == DEC_TILE) {
+                const int page = pg[0] != PAGE_NONE ? pg[0] : (pg[1] != PAGE_NONE ? pg[1] : (pg[2] != PAGE_NONE ? pg[2] : pg[3]));
+                const bool page_ok = page >= 0 && page < num_pages;
+                if (!page_ok && page != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
+                const int row = page_ok ? (page * kvh + kh) * block_size + tile_start % block_size : 0;
+                tma_load_3d(kt, &tmK, 0, row, 0, &full[s]);
+                tma_load_3d(kt + DT_TILE_BYTES, &tmV, 0, row, 0, &full[s]);
+              } else {
+#pragma unroll
+                for (int run = 0; run < 4; ++run) {
+                  const bool page_ok = pg[run] >= 0 && pg[run] < num_pages;
+                  if (!page_ok && pg[run] != PAGE_NONE) atomicOr(err, VOB_ERR_PAGE);
+                  const int key0 = tile_start + run * RUN_KEYS;
+                  const int row = page_ok ? (pg[run] * kvh + kh) * block_size + key0 % block_size : 0;
+#pragma unroll
+                  for (int c = 0; c < DT_SLICES; ++c) {
+                    tma_load_3d(kt + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmK, 0, row, c, &full[s]);
+                    tma_load_3d(kt + DT_TILE_BYTES + c * DEC_TILE * 128 + run * RUN_KEYS * 128, &tmV, 0, row, c, &full[s]);
+                  }
+                }
+              }
+            }
+          }
+          const int flags = __shfl_sync(0xffffffffu, (ok ? 1 : 0) | (waited ? 2 : 0), 0);
+          ok = (flags & 1) != 0;
+          waited = (flags & 2) != 0;
+          if (!ok) break;
+        }
+        ++pairs;
+      }
+      if (!ok) break;
+      if (!drawn && lane == 0) {
+        if (!waited) pdl_wait();
+        next = (int)min((unsigned)num_items, gridDim.x + atomicAdd(&vob_decode_pairs_taken[0], 1u));
+      }
+      waited = true;
+      item = __shfl_sync(0xffffffffu, next, 0);
+    }
+    if (lane == 0) {
+      if (ok) {                                       // "no more", in the stage the consumers wait on next
+        const int s = (int)(ring % DT_STAGES);
+        if (ring >= DT_STAGES) ok = mbar_wait(&empty[s], (unsigned)(((ring / DT_STAGES) - 1) & 1), abort_flag, err);
+        if (ok) {
+          queue[pairs % DI_QUEUE] = make_int4(-1, 0, 0, 0);
+          mbar_arrive(&full[s]);
+          ++ring;
+        }
+      }
+      const long first = ring > DT_STAGES ? ring - DT_STAGES : 0;   // copies in flight must land before the block exits
+      for (long j = first; j < ring; ++j) {
+        bool done = false;
+        for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&full[j % DT_STAGES], (unsigned)((j / DT_STAGES) & 1));
+        if (!done) atomicOr(err, VOB_ERR_TIMEOUT_BITS);
+      }
+    }
+  } else {
+    // ------------------------------------------------ consumers: warp w takes keys 16w..16w+15 of every tile
+    // Every pair, and the entry that ends the list, takes a warp through the same two barriers, also a warp whose wait
+    // ran out (it has raised the flag before it arrives); after the second barrier all four see the flag and leave.
+    pdl_wait();
+    const int g = lane >> 2, tq = lane & 3;
+    const float sc = scale * LOG2E;
+    long ring = 0;
+    for (int pair = 0;; ++pair) {
+      bool ok = mbar_wait(&full[ring % DT_STAGES], (unsigned)((ring / DT_STAGES) & 1), abort_flag, err);
+      ok = __all_sync(0xffffffffu, ok);
+      const int4 entry = ok ? queue[pair % DI_QUEUE] : make_int4(-1, 0, 0, 0);
+      const bool more = entry.x >= 0;
+      const int kh = more ? entry.x % kvh : 0, t = entry.y, pos = entry.z;
+      const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+      const int start = lo & ~(box_keys - 1);
+      const int end = pos + 1;
+      const int n_tiles = more ? (end - start + DEC_TILE - 1) / DEC_TILE : 0;
+      WarpSoftmax st;
+      st.clear();
+      if (more) {
+        uint32_t qf[KSTEPS][4];
+        const __nv_bfloat16* qrow0 = q + (size_t)t * q_stride + (size_t)(kh * G + g) * HD;
+        const __nv_bfloat16* qrow1 = qrow0 + (size_t)8 * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          const int d = ks * 16 + tq * 2;
+          qf[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + d) : 0u;
+          qf[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + d) : 0u;
+          qf[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + d + 8) : 0u;
+          qf[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + d + 8) : 0u;
+        }
+        for (int it = 0; it < n_tiles; ++it, ++ring) {
+          const int s = (int)(ring % DT_STAGES);
+          if (it > 0) {
+            ok = mbar_wait(&full[s], (unsigned)((ring / DT_STAGES) & 1), abort_flag, err);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+          }
+          const char* kt = smem + s * DT_STAGE_BYTES;
+          const int k0 = start + it * DEC_TILE + warp * 16;
+          if (k0 < end && k0 + 16 > lo) {
+            float sv[2][4];
+            qk_16keys_swizzled<DEC_TILE>(qf, kt, warp * 16, lane, sv);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const int key = k0 + i * 8 + tq * 2;
+              const bool ok0 = key >= lo && key < end, ok1 = key + 1 >= lo && key + 1 < end;
+              sv[i][0] = ok0 ? sv[i][0] * sc : -INFINITY;
+              sv[i][1] = ok1 ? sv[i][1] * sc : -INFINITY;
+              sv[i][2] = ok0 ? sv[i][2] * sc : -INFINITY;
+              sv[i][3] = ok1 ? sv[i][3] * sc : -INFINITY;
+            }
+            softmax_pv_16keys_swizzled<DEC_TILE>(st, sv, kt + DT_TILE_BYTES, warp * 16, lane);
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty[s]);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 1);
+          st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 2);
+        }
+        if (tq == 0) {
+          wm[warp * 16 + g] = st.m[0]; wm[warp * 16 + g + 8] = st.m[1];
+          wl[warp * 16 + g] = st.l[0]; wl[warp * 16 + g + 8] = st.l[1];
+        }
+#pragma unroll
+        for (int j = 0; j < DTILES; ++j) {
+          if (g < G) {
+            float* r0 = wo + ((size_t)warp * G + g) * HD + j * 8 + tq * 2;
+            r0[0] = st.o[j][0]; r0[1] = st.o[j][1];
+          }
+          if (g + 8 < G) {
+            float* r1 = wo + ((size_t)warp * G + g + 8) * HD + j * 8 + tq * 2;
+            r1[0] = st.o[j][2]; r1[1] = st.o[j][3];
+          }
+        }
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(DEC_WARPS * 32) : "memory");
+      const bool aborted = *abort_flag != 0;
+      if (more && !aborted) {
+        for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32) {
+          const int r = idx / HD, d = idx % HD;
+          float M = -INFINITY;
+#pragma unroll
+          for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, wm[w * 16 + r]);
+          float L = 0.f, O = 0.f;
+#pragma unroll
+          for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = wm[w * 16 + r] == -INFINITY ? 0.f : fast_exp2(wm[w * 16 + r] - M);
+            L += wl[w * 16 + r] * f;
+            O += wo[((size_t)w * G + r) * HD + d] * f;
+          }
+          out[(size_t)t * nh * HD + (size_t)(kh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        }
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(DEC_WARPS * 32) : "memory");   // the buffer is free for the next pair
+      if (!more || aborted) break;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {                             // the last block to leave makes the counter ready for the next launch
+    __threadfence();
+    if (atomicAdd(&vob_decode_pairs_taken[1], 1u) == gridDim.x - 1) {
+      vob_decode_pairs_taken[0] = 0;
+      vob_decode_pairs_taken[1] = 0;
+      __threadfence();
+    }
+  }
+}
 #endif  // VOB_HD % 64 == 0
 
 // Merges the splits of every (decoding request, head): weights 2^(lse - max lse).
@@ -460,6 +720,10 @@ VOB_API long vob_attention_decode_scratch_floats(int num_requests, int nh, int n
   return num_splits > 1 ? (long)num_requests * nh * num_splits * (HD + 1) : 0;
 }
 
+static bool g_decode_items = true;
+// One split and more (request, kv head) pairs than resident blocks: persistent blocks (default) or a block a pair.
+VOB_API void vob_attention_decode_persistent(int on) { g_decode_items = on != 0; }
+
 static bool g_decode_cluster_merge = true;
 // Up to 8 splits merge through a thread-block cluster (default) or through scratch memory and a second kernel.
 VOB_API void vob_attention_decode_cluster_merge(int on) { g_decode_cluster_merge = on != 0; }
@@ -495,6 +759,29 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
       tma_configured = true;
     }
     const int box_keys = block_size % DEC_TILE == 0 ? DEC_TILE : RUN_KEYS;
+    // one split and more (request, kv head) pairs than blocks fit the GPU: persistent blocks, the producer ahead across pairs
+    if (num_splits == 1 && g_decode_items) {
+      const int G = nh / kvh;
+      const int items_smem = 1024 + DT_STAGES * DT_STAGE_BYTES + DI_MERGE_FLOATS(G) * 4 + DI_QUEUE * 16 + 2 * DT_STAGES * 8 + 32;
+      static int resident_of[17] = {0};      // blocks that fit the GPU at once, by heads per kv head (0: not asked yet)
+      if (!resident_of[G]) {
+        static int items_configured = 0;
+        if (items_configured < items_smem) {
+          cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_items_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, items_smem);
+          if (e != cudaSuccess) return (int)e;
+          items_configured = items_smem;
+        }
+        int per_sm = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_tma_items_kernel, DT_THREADS, items_smem);
+        if (e != cudaSuccess) return (int)e;
+        resident_of[G] = (per_sm > 0 ? per_sm : 1) * sm_count();
+      }
+      if ((long)num_requests * kvh > resident_of[G])
+        return launch_kernel(attention_decode_tma_items_kernel, dim3(resident_of[G]), DT_THREADS, items_smem, stream,
+                             *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride,
+                             (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, num_requests, nh, kvh,
+                             block_size, window, scale, num_pages, box_keys, err);
+    }
     // up to 8 splits: the blocks of a (request, kv head) are a cluster and merge through shared memory
     if (num_splits > 1 && num_splits <= 8 && g_decode_cluster_merge)
       return launch_kernel_cluster(attention_decode_tma_kernel, grid, DT_THREADS, tma_smem, stream, (unsigned)num_splits,

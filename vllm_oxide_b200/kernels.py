@@ -215,6 +215,12 @@ def attention_decode_scratch_floats(head_dim: int, num_requests: int, nh: int, n
     return int(attention_lib(head_dim).vob_attention_decode_scratch_floats(num_requests, nh, num_splits))
 
 
+def attention_decode_persistent(head_dim: int, on: bool) -> None:
+    """With one split and more (request, kv head) pairs than blocks fit the GPU, the TMA decode kernel runs as
+    persistent blocks whose producer works ahead across pairs (default); off: one block per pair.  Same bits."""
+    attention_lib(head_dim).vob_attention_decode_persistent(1 if on else 0)
+
+
 def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, nh, kvh, hd,
                      window: int, scale: float, num_splits: int, scratch, err, use_tma: bool = True) -> None:
     """Requests that bring exactly one token; the others are skipped."""

@@ -6,7 +6,9 @@
 //   warps 0 .. 4NQ-1   softmax: warp w of a tile owns rows 32(w%4) .. +31 of it, a thread owns ONE row: it reads the
 //                      row's 64 scores from tensor memory (tcgen05.ld), masks, takes the maximum and the sum without
 //                      any exchange between threads, writes P in bfloat16 back to tensor memory over the scores (the A
-//                      operand of the second product), and at the end divides the row of O by its sum and stores it;
+//                      operand of the second product), and at the end divides the row of O by its sum and stores it
+//                      (32 bytes a store).  From a row's second step on the exponentials are taken against the old
+//                      reference maximum beside the search for the new one, and taken again only if it had to move;
 //   warp 4NQ           producer: looks the pages up a chunk ahead and brings K and V tiles in by TMA into a ring of
 //                      stages (the K tile is the K-major B operand of the first product as it lands, the V tile the
 //                      MN-major B operand of the second one: no transposition anywhere);
@@ -14,6 +16,8 @@
 //                      products, the scores of step j+1 into a second S buffer while the softmax of step j runs;
 //                      tcgen05.commit tells the softmax warps that S is complete and that O has been updated, and
 //                      the producer that the tile is done with a stage.  The tiles do not wait for one another.
+// At a block's start the producer goes for the first keys and values as soon as the barriers exist, while the softmax
+// warps bring the query tiles in (cp.async, all copies in flight at once) and tensor memory is allocated.
 // A wait on an mbarrier goes by the parity of the phase, so it can tell only two states apart: the scores and P have
 // a barrier per buffer (a buffer's next use needs the waiter's own progress).  O's barrier gets a phase per step; a
 // softmax thread that has to rescale O at step i waits on it for step i - 1, when it can be in two states only (that
@@ -119,27 +123,34 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     tma_prefetch_map(&tmV);
   }
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  if (warp == 4 * NQ + 1) t5_alloc(tmem_slot, C::TMEM_COLS);
+  __syncthreads();                              // the barriers are there: the producer starts on the first keys and values
   pdl_wait();                                   // the kernels before this one wrote q and this portion's keys and values
-  if (warp < 4 * NQ) {
-    // the query tile of this warp group into shared memory, rows of 128 bytes per slice, 128-byte swizzled
-    const int qt = warp >> 2, tid = threadIdx.x & 127;
-    char* dst = q_s + qt * F5_Q_BYTES;
-    constexpr int CHUNKS = HD / 8;
-    for (int idx = tid; idx < F5_ROWS * CHUNKS; idx += 128) {
-      const int r = idx / CHUNKS, chunk = idx % CHUNKS;
-      const int row = row0 + qt * F5_ROWS + r;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (row < total_rows)
-        v = *reinterpret_cast<const uint4*>(q + (size_t)(t0 + row / G) * q_stride + (size_t)(kh * G + row % G) * HD + chunk * 8);
-      *reinterpret_cast<uint4*>(dst + (chunk >> 3) * (F5_ROWS * 128) + swizzled_offset(r, chunk & 7)) = v;
+  uint32_t tmem_base = 0;
+  if (warp != 4 * NQ) {
+    if (warp == 4 * NQ + 1) t5_alloc(tmem_slot, C::TMEM_COLS);
+    if (warp < 4 * NQ) {
+      // the query tile of this warp group into shared memory, rows of 128 bytes per slice, 128-byte swizzled; every
+      // copy is on its way before the first one is waited for
+      const int qt = warp >> 2, tid = threadIdx.x & 127;
+      char* dst = q_s + qt * F5_Q_BYTES;
+      constexpr int CHUNKS = HD / 8;
+#pragma unroll 4
+      for (int idx = tid; idx < F5_ROWS * CHUNKS; idx += 128) {
+        const int r = idx / CHUNKS, chunk = idx % CHUNKS;
+        const int row = row0 + qt * F5_ROWS + r;
+        const bool there = row < total_rows;
+        const __nv_bfloat16* src = there ? q + (size_t)(t0 + row / G) * q_stride + (size_t)(kh * G + row % G) * HD + chunk * 8 : q;
+        cp_async16(dst + (chunk >> 3) * (F5_ROWS * 128) + swizzled_offset(r, chunk & 7), src, there);
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
     }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    t5_fence_before();
+    asm volatile("bar.sync 1, %0;\n" ::"n"(5 * NQ * 32) : "memory");   // the softmax and the issuing warps
+    t5_fence_after();
+    tmem_base = *tmem_slot;
   }
-  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-  t5_fence_before();
-  __syncthreads();
-  t5_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 4 * NQ) {
     // ------------------------------------------------ producer: lane 0 issues, all lanes look pages up
@@ -277,52 +288,81 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       t5_fence_after();
-      uint32_t raw[2][32];
-      t5_ld32_issue(lane_base + (i & 1) * F5_TILE, raw[0]);
-      t5_ld32_issue(lane_base + (i & 1) * F5_TILE + 32, raw[1]);
-      t5_wait_ld();
-      float s[64];
       const int k0 = start + j * F5_TILE;
       // mask only where the step touches the diagonal, the window's edge or missing rows
       const bool need_mask = !all_rows || k0 + F5_TILE - 1 > t_pos_lo || (window > 0 && k0 < t_pos_hi - window + 1);
-      float mx = -INFINITY;                                // of the raw scores: the scale is positive
-      if (need_mask) {
+      float s[64];
+      // the row's 64 scores of this step from tensor memory, masked
+      auto load_scores = [&]() {
+        uint32_t raw[2][32];
+        t5_ld32_issue(lane_base + (i & 1) * F5_TILE, raw[0]);
+        t5_ld32_issue(lane_base + (i & 1) * F5_TILE + 32, raw[1]);
+        t5_wait_ld();
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const int key = k0 + c;
-          bool okk = valid && key <= rpos;
-          if (window > 0) okk = okk && key > rpos - window;
-          s[c] = okk ? __uint_as_float(raw[c >> 5][c & 31]) : -INFINITY;
+          for (int c = 0; c < 64; ++c) {
+            const int key = k0 + c;
+            bool okk = valid && key <= rpos;
+            if (window > 0) okk = okk && key > rpos - window;
+            s[c] = okk ? __uint_as_float(raw[c >> 5][c & 31]) : -INFINITY;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) s[c] = __uint_as_float(raw[c >> 5][c & 31]);
         }
-      } else {
+      };
+      // the maximum of the raw scores (the scale is positive): four chains of three-input maxima
+      auto row_max = [&]() {
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 64; ++c) s[c] = __uint_as_float(raw[c >> 5][c & 31]);
-      }
+        for (int c = 0; c < 64; c += 8) {
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) mx = fmaxf(mx, fmaxf(s[c], s[c + 1]));
-      mx *= sc;
-      // the reference maximum moves only when the row's maximum has run ahead of it
-      const bool grow = mx > m_ref + F5_MAX_SLACK;
-      float factor = 1.f;
-      if (grow) {
-        factor = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - mx);
-        m_ref = mx;
-        l *= factor;
-      }
-      const float neg_mu = m_ref == -INFINITY ? 0.f : -m_ref;     // a row that has seen no key yet: a finite stand-in
-      float sum0 = 0.f, sum1 = 0.f;
+          for (int h = 0; h < 4; ++h) m4[h] = max3(m4[h], s[c + 2 * h], s[c + 2 * h + 1]);
+        }
+        return max3(fmaxf(m4[0], m4[1]), m4[2], m4[3]) * sc;
+      };
       uint32_t packed[32];
+      float sum = 0.f;
+      // P = 2^(s * scale - reference) in bfloat16 pairs, and its sum
+      auto exponentials = [&](float neg_mu) {
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        const float p0 = fast_exp2(fmaf(s[c], sc, neg_mu)), p1 = fast_exp2(fmaf(s[c + 1], sc, neg_mu));
-        sum0 += p0;
-        sum1 += p1;
-        packed[c >> 1] = pack_bf16(p0, p1);
+        for (int c = 0; c < 64; c += 2) {
+          const float p0 = fast_exp2(fmaf(s[c], sc, neg_mu)), p1 = fast_exp2(fmaf(s[c + 1], sc, neg_mu));
+          part[(c >> 1) & 1] += p0;
+          part[2 + ((c >> 1) & 1)] += p1;
+          packed[c >> 1] = pack_bf16(p0, p1);
+        }
+        sum = (part[0] + part[1]) + (part[2] + part[3]);
+      };
+      load_scores();
+      // The reference maximum moves only when the row's maximum has run ahead of it, which is rare after a row's
+      // first steps.  So from the second step on the exponentials are taken against the old reference at once, beside
+      // the search for the maximum (the two do not depend on each other, and the chain of maxima hides behind the
+      // exponentials); only if some row of the warp has to move its reference are the scores read again and the
+      // step's exponentials taken anew.
+      float mx = 0.f;
+      bool moved = i == 0;
+      if (i > 0) {
+        exponentials(m_ref == -INFINITY ? 0.f : -m_ref);
+        mx = row_max();
+        moved = __any_sync(0xffffffffu, mx > m_ref + F5_MAX_SLACK);
+        if (moved) load_scores();
+      } else {
+        mx = row_max();
       }
-      const float sum = sum0 + sum1;
+      float factor = 1.f;
+      if (moved) {
+        if (mx > m_ref + F5_MAX_SLACK) {
+          factor = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - mx);
+          m_ref = mx;
+          l *= factor;
+        }
+        exponentials(m_ref == -INFINITY ? 0.f : -m_ref);     // a row that has seen no key yet: a finite stand-in
+      }
       l += sum;
       // O is touched only to rescale it, and then the product of the step before must have updated it
-      const bool rescale = i > 0 && __any_sync(0xffffffffu, grow);
+      const bool rescale = i > 0 && moved;
       if (rescale) {
         ok = mbar_wait(&o_done[qt], (unsigned)((i - 1) & 1), abort_flag, err);
         ok = __all_sync(0xffffffffu, ok);
@@ -355,19 +395,20 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* orow = out + (size_t)(t0 + tok) * nh * HD + (size_t)head * HD;
 #pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 32) {
-          uint32_t o[32];
-          t5_ld32_issue(lane_base + 2 * F5_TILE + c0, o);
+        for (int c0 = 0; c0 < HD; c0 += 64) {
+          uint32_t o[2][32];
+          t5_ld32_issue(lane_base + 2 * F5_TILE + c0, o[0]);
+          t5_ld32_issue(lane_base + 2 * F5_TILE + c0 + 32, o[1]);
           t5_wait_ld();
           if (valid) {
 #pragma unroll
-            for (int c = 0; c < 32; c += 8) {
-              uint4 v;
-              v.x = pack_bf16(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
-              v.y = pack_bf16(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-              v.z = pack_bf16(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
-              v.w = pack_bf16(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + c0 + c) = v;
+            for (int c = 0; c < 64; c += 16) {             // 32 bytes a store: whole sectors
+              uint32_t v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                v[e] = pack_bf16(__uint_as_float(o[c >> 5][(c & 31) + 2 * e]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 2 * e + 1]) * inv);
+              asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n" ::"l"(orow + c0 + c), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                           "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
             }
           }
         }
@@ -402,6 +443,7 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
 #if VOB_HD == 64 || VOB_HD == 128
   if (num_requests <= 0 || max_q <= 1) return 0;
   if (!map_k || !map_v) return VOB_BAD_ARGUMENT;
+  if (((uintptr_t)out & 31) || ((uintptr_t)q & 15)) return VOB_BAD_ARGUMENT;     // 32-byte stores, 16-byte copies
   if (kvh <= 0 || nh % kvh || block_size <= 0 || block_size % 16 || kvh > 65535 || num_requests > 65535 ||
       (query_tiles != 1 && query_tiles != 2) || !(scale > 0.f))   // the kernel takes maxima before it scales
     return VOB_UNSUPPORTED;

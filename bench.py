@@ -306,6 +306,53 @@ def workload_run(name: str, pk=None) -> dict:
                    "pool_pages": w["options"]["num_kv_blocks"], "block_size": w["options"]["block_size"]}}
 
 
+def attention_kernels_run(pk) -> dict:
+    """The prefill attention kernel alone, Qwen3-8B head shapes, one prompt of 2,048 and of 8,192 tokens: the device
+    time of a launch (CUDA events around a graph of 20 launches, so the host's share of a launch is not in it)."""
+    import math
+    import torch
+    from vllm_oxide_b200 import kernels
+    dev = "cuda:0"
+    nh, kvh, hd = QWEN3_8B["num_attention_heads"], QWEN3_8B["num_key_value_heads"], QWEN3_8B["head_dim"]
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = {"only": "attention", "heads": nh, "kv_heads": kvh, "head_dim": hd, "block_size": BLOCK, "launches_per_graph": 20}
+    for T in (2048, 8192):
+        pages = (T + BLOCK - 1) // BLOCK
+        kc = torch.randn(pages, kvh, BLOCK, hd, device=dev).bfloat16()
+        vc = torch.randn(pages, kvh, BLOCK, hd, device=dev).bfloat16()
+        bt = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, pages)
+        q = torch.randn(T, nh * hd, device=dev).bfloat16()
+        o = torch.empty_like(q)
+        cu_q = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        ctx = torch.tensor([T], dtype=torch.int32, device=dev)
+
+        def launch():
+            kernels.attention_prefill(q, nh * hd, o, kc, vc, bt, cu_q, ctx, 1, T, nh, kvh, hd, 0, 1 / math.sqrt(hd), err)
+        for _ in range(3):
+            launch()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(20):
+                launch()
+        graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) / 20)
+        ms = sorted(times)[len(times) // 2]
+        flops = 4 * nh * hd * T * (T + 1) / 2
+        tf = flops / ms / 1e9
+        out[f"prefill_{T}"] = {"us": round(ms * 1e3, 1), "tflops": round(tf, 1), "frac": round(tf / pk["bf16_tflops"], 3)}
+        assert err.item() == 0
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -316,7 +363,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (reported)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None, help="another workload instead of the default run")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "attention"], default=None,
                     help="run one phase and print its time only (for short profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -328,6 +375,9 @@ def main() -> int:
         return 2
     if args.workload:
         print(json.dumps(workload_run(args.workload)))
+        return 0
+    if args.only == "attention":
+        print(json.dumps(attention_kernels_run(peaks())))
         return 0
     import torch
     from vllm_oxide_b200 import LLM, EngineOptions

@@ -307,8 +307,9 @@ def workload_run(name: str, pk=None) -> dict:
 
 
 def attention_kernels_run(pk) -> dict:
-    """The prefill attention kernel alone, Qwen3-8B head shapes, one prompt of 2,048 and of 8,192 tokens: the device
-    time of a launch (CUDA events around a graph of 20 launches, so the host's share of a launch is not in it)."""
+    """The attention kernels alone.  Prefill: Qwen3-8B head shapes, one prompt of 2,048 and of 8,192 tokens, the device
+    time of a launch (CUDA events around a graph of 20 launches, so the host's share of a launch is not in it).
+    Decode: hundreds of requests with one key split each, 50 launches in a row (caches larger than L2)."""
     import math
     import torch
     from vllm_oxide_b200 import kernels
@@ -350,6 +351,42 @@ def attention_kernels_run(pk) -> dict:
         tf = flops / ms / 1e9
         out[f"prefill_{T}"] = {"us": round(ms * 1e3, 1), "tflops": round(tf, 1), "frac": round(tf / pk["bf16_tflops"], 3)}
         assert err.item() == 0
+        del kc, vc, q, o
+    # Decode attention of many requests with one key split each (the serving workload's shape: 16 heads over 8 kv heads,
+    # contexts of 300 to 1,000 keys): persistent blocks against one block per (request, kv head).
+    nh, g = 16, torch.Generator().manual_seed(1)
+    for name, B, lo, hi in (("decode_228x650", 228, 650, 650), ("decode_228x300_1000", 228, 300, 1000), ("decode_512x100_400", 512, 100, 400)):
+        ctx_host = torch.randint(lo, hi + 1, (B,), generator=g).int()
+        per = (hi + BLOCK - 1) // BLOCK
+        kc = torch.randn(B * per, kvh, BLOCK, hd, device=dev).bfloat16()
+        vc = torch.randn(B * per, kvh, BLOCK, hd, device=dev).bfloat16()
+        bt = torch.randperm(B * per, generator=g).int().view(B, per).to(dev)
+        q = torch.randn(B, nh * hd, device=dev).bfloat16()
+        o = torch.empty_like(q)
+        cu_q = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        ctx = ctx_host.to(dev)
+        nbytes = float(ctx_host.sum()) * kvh * hd * 2 * 2
+        row = {}
+        for mode, on in (("persistent", True), ("block_per_pair", False)):
+            kernels.attention_decode_persistent(hd, on)
+
+            def launch():
+                kernels.attention_decode(q, nh * hd, o, kc, vc, bt, cu_q, ctx, B, nh, kvh, hd, 0, 1 / math.sqrt(hd), 1, None, err)
+            for _ in range(5):
+                launch()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(50):
+                launch()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / 50 * 1e3
+            row[mode] = {"us": round(us, 1), "gbs": round(nbytes / us / 1e3), "frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        kernels.attention_decode_persistent(hd, True)
+        out[name] = row
+        assert err.item() == 0
+        del kc, vc
     return out
 
 

@@ -290,6 +290,34 @@ def test_the_same_work_twice_gives_the_same_tokens_bit_for_bit(model_folders):
     assert sure >= 60, f"only {sure} of 180 greedy steps had a clear winner"
 
 
+def test_hundreds_of_requests_decode_through_the_persistent_attention_blocks(model_folders):
+    """160 live requests with two key/value heads are more (request, kv head) pairs than blocks fit the GPU, so decode
+    attention runs as persistent blocks that draw their pairs from a counter: the greedy tokens are the ones the 32-bit
+    path is sure of, and they are the same, bit for bit, with one block per pair."""
+    from vllm_oxide_b200 import SamplingParams, kernels
+    from vllm_oxide_b200.engine.trace import TraceRunner
+    n, new = 160, 6
+    prompts = [tokens_for("D", 3 + (7 * i) % 58, salt=900 + i) for i in range(n)]
+    sp = SamplingParams(max_tokens=new, ignore_eos=True)
+    hd = TINY["D"]["config"]["head_dim"]
+    assert n * TINY["D"]["config"]["num_key_value_heads"] > 2 * kernels.sm_count()
+    runs = []
+    for persistent in (True, False):
+        kernels.attention_decode_persistent(hd, persistent)
+        try:
+            llm = make_llm(model_folders, "D", "bfloat16", max_num_seqs=n, num_kv_blocks=2 * n + 8, max_num_batched_tokens=8192,
+                           enable_prefix_caching=False)
+            runs.append([o.token_ids for o in llm.generate(prompts, [sp] * n)])
+            assert llm.core.graph_replays > 0
+            del llm
+        finally:
+            kernels.attention_decode_persistent(hd, True)
+    assert runs[0] == runs[1]
+    full = TraceRunner(model_folders["D"], "float32", 256, TINY["D"]["block_size"])
+    sure = sum(greedy_tokens_agree_with_32_bit_logits(full, prompts[i], runs[0][i], f"request {i}") for i in range(0, n, 8))
+    assert sure >= 30, f"only {sure} of {new * n // 8} greedy steps had a clear winner"
+
+
 def test_a_decode_graph_padded_beyond_the_step_limits(model_folders):
     """Five requests with max_num_seqs 5 and a budget of 6 tokens decode from the graph for 8 requests: a layout larger
     than any step the limits allow (the staging buffers must hold it), with the same tokens as without graphs."""

@@ -105,6 +105,9 @@ __global__ void __launch_bounds__(NT) add_rmsnorm_kernel(const T* x, T* residual
   const T* xr = x + (size_t)src * H;
   T* rr = residual + (size_t)src * H;
   T* yr = y + (size_t)r * H;
+  // residual' = x + residual goes back to the residual rows, unless rows were picked, or it is x itself (the norm of a
+  // stream that already holds the sum)
+  const bool keep = !rows && (has_residual || (const T*)rr != xr);
   float ss = 0.f;
   if (VEC && REG) {
     constexpr int N = Vec16<T>::N, IT = REG > 0 ? REG : 1;
@@ -128,7 +131,7 @@ __global__ void __launch_bounds__(NT) add_rmsnorm_kernel(const T* x, T* residual
       if (i < H) {
 #pragma unroll
         for (int j = 0; j < N; ++j) ss += v[it][j] * v[it][j];
-        if (!rows) store16<T>(rr + i, v[it]);
+        if (keep) store16<T>(rr + i, v[it]);
       }
     }
     const float total = block_sum<NT>(ss, scratch);
@@ -160,7 +163,7 @@ __global__ void __launch_bounds__(NT) add_rmsnorm_kernel(const T* x, T* residual
       }
 #pragma unroll
       for (int j = 0; j < N; ++j) { srow[i + j] = s[j]; ss += s[j] * s[j]; }
-      if (!rows) store16<T>(rr + i, s);
+      if (keep) store16<T>(rr + i, s);
     }
   } else {
     for (int i = threadIdx.x; i < H; i += NT) {
@@ -168,7 +171,7 @@ __global__ void __launch_bounds__(NT) add_rmsnorm_kernel(const T* x, T* residual
       if (has_residual) s += to_f<T>(rr[i]);
       srow[i] = s;
       ss += s * s;
-      if (!rows) rr[i] = from_f<T>(s);
+      if (keep) rr[i] = from_f<T>(s);
     }
   }
   const float total = block_sum<NT>(ss, scratch);

@@ -17,7 +17,7 @@ import torch
 from .. import kernels
 from ..weights.loader import TensorSpec
 from .base import NO_ROTATION, CacheSpec, Mixer, Prenormed, register_part
-from .linear import linear
+from .linear import linear, linear_into_stream
 
 
 class Attention(Mixer):
@@ -80,7 +80,10 @@ class Attention(Mixer):
         return CacheSpec(self.kvh, self.hd, self.window)
 
     # ---- one step
-    def forward(self, x, ctx, cache, state=None, write_cache: bool = True):
+    adds_into_stream = True
+
+    def forward(self, x, ctx, cache, state=None, write_cache: bool = True, add_into=None):
+        """`add_into`: the residual stream; the output product then adds its result there and nothing is returned."""
         T = x.shape[0]
         width = (self.nh + 2 * self.kvh) * self.hd
         qkv = linear(x, self.wqkv, ctx.ws.get("qkv", T, width, x.dtype), ctx)
@@ -90,6 +93,9 @@ class Attention(Mixer):
                                       write_cache, ctx.err)
         attn = ctx.ws.get("attn_out", T, self.nh * self.hd, x.dtype)
         self.attend(qkv, width, attn, cache, ctx, T)
+        if add_into is not None:
+            linear_into_stream(attn, self.wo, add_into)
+            return None
         return linear(attn, self.wo, ctx.ws.get("attn_proj", T, self.H, x.dtype), ctx)
 
     # ---- the same with the residual stream kept inside the products (decode-sized steps)

@@ -26,6 +26,9 @@ STREAM_MAX_TOKENS = 16
 # per tile), so the next product runs its plain loop and only scales by 1/rms at its end: about 2 us less for each of
 # the two products a layer that follow a norm.
 NORM_AHEAD = True
+# Steps of more than 16 tokens: the library's output and down products add into the residual stream (the stream is their
+# addend), so the add+norm kernels that follow read one tensor and write one instead of reading two and writing two.
+ADD_IN_PRODUCTS = True
 
 
 class PreNormBlock(Block):
@@ -64,9 +67,21 @@ class PreNormBlock(Block):
             return None, stream
         ctx.prenormed = None
         normed, residual = self.input_norm.forward(hidden, residual, ctx)
+        if self._adds_in_products(residual):
+            # larger bfloat16 steps: the library's output and down products take the stream as their addend
+            self.mixer.forward(normed, ctx, cache, state, write_cache, add_into=residual)
+            normed, residual = self.post_mixer_norm.forward(None, residual, ctx)
+            self.feed_forward.forward(normed, ctx, add_into=residual)
+            return None, residual
         mixed = self.mixer.forward(normed, ctx, cache, state, write_cache)
         normed, residual = self.post_mixer_norm.forward(mixed, residual, ctx)
         return self.feed_forward.forward(normed, ctx), residual
+
+    def _adds_in_products(self, stream) -> bool:
+        """bfloat16 steps too large for the weight-streaming kernel, with a mixer and a feed-forward that can add their
+        result into the stream themselves (`adds_into_stream`, `forward(..., add_into=stream)`)."""
+        return (ADD_IN_PRODUCTS and stream.dtype == torch.bfloat16 and stream.shape[0] > STREAM_MAX_TOKENS
+                and getattr(self.mixer, "adds_into_stream", False) and getattr(self.feed_forward, "adds_into_stream", False))
 
     def _keeps_stream(self, stream, ctx) -> bool:
         """Decode-sized bfloat16 steps whose norms are RMSNorm and whose mixer and feed-forward offer

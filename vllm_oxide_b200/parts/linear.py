@@ -49,3 +49,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, ctx=None) -
     elif not tc5_product(x, weight, out, kernels.EPI_BF16, ctx):
         torch.mm(x, weight.t(), out=out)
     return out
+
+
+def linear_into_stream(x: torch.Tensor, weight: torch.Tensor, stream: torch.Tensor) -> None:
+    """stream += x @ weight^T by the library's product with the stream as its addend (bfloat16 steps of more than 16
+    tokens): the sum is made in float inside the product and rounded once, as the weight-streaming kernel's adding
+    epilogue does for smaller steps, and the add+norm kernel that follows has one tensor less to read and none to
+    write back."""
+    torch.addmm(stream, x, weight.t(), out=stream)

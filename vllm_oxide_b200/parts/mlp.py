@@ -9,7 +9,7 @@ import torch
 from .. import kernels
 from ..weights.loader import TensorSpec
 from .base import FeedForward, register_part
-from .linear import linear, tc5_product
+from .linear import linear, linear_into_stream, tc5_product
 
 
 class SwiGLU(FeedForward):
@@ -40,7 +40,10 @@ class SwiGLU(FeedForward):
             self.wgu = torch.cat([gate, up], dim=0).contiguous()
         self.wdown = tensors[p + "down_proj.weight"].contiguous()
 
-    def forward(self, x, ctx):
+    adds_into_stream = True
+
+    def forward(self, x, ctx, add_into=None):
+        """`add_into`: the residual stream; the down product then adds its result there and nothing is returned."""
         T = x.shape[0]
         act = ctx.ws.get("act", T, self.I, x.dtype)
         if self.interleaved and kernels.gemm_skinny_supported(x, self.wgu):
@@ -51,8 +54,10 @@ class SwiGLU(FeedForward):
         else:
             gu = linear(x, self.wgu, ctx.ws.get("gate_up", T, 2 * self.I, x.dtype), ctx)
             kernels.silu_mul(gu, act, T, self.interleaved)
+        if add_into is not None:
+            linear_into_stream(act, self.wdown, add_into)
+            return None
         return linear(act, self.wdown, ctx.ws.get("mlp_out", T, self.H, x.dtype), ctx)
-
 
     # ---- the same with the residual stream kept inside the products (decode-sized steps)
     def can_forward_on_stream(self, stream, ctx) -> bool:

@@ -201,8 +201,8 @@ def build_attention(head_dim: int, force: bool = False) -> str:
                                [f"-DVOB_HD={head_dim}"], f"the attention kernels for head size {head_dim}", force)
 
 
-def build_all(force: bool = False) -> None:
+def build_all(force: bool = False, head_dims=None) -> None:
     build_host(force)
     build_kernels(force)
-    for hd in DEFAULT_HEAD_DIMS:
+    for hd in head_dims or DEFAULT_HEAD_DIMS:
         build_attention(hd, force)

@@ -53,13 +53,14 @@ template <int NQ> struct F5 {
   static constexpr int TILE_COLS = 2 * F5_TILE + HD;       // tensor-memory columns of a query tile: S, S, O
   static constexpr int TMEM_COLS = NQ * TILE_COLS <= 256 ? 256 : 512;
   static constexpr int DATA_BYTES = NQ * F5_Q_BYTES + STAGES * F5_STAGE_BYTES;
-  static constexpr int NUM_BARRIERS = 2 * STAGES + 6 * NQ + 1;
+  static constexpr int NUM_BARRIERS = 2 * STAGES + 7 * NQ + 1;
   static constexpr int SMEM_BYTES = 1024 + DATA_BYTES + NUM_BARRIERS * 8 + 16;
 };
 
 template <int NQ>
 __global__ void __launch_bounds__(F5<NQ>::THREADS, F5<NQ>::BLOCKS_PER_SM)
 attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                             const __grid_constant__ CUtensorMap tmQ, int q_by_tma,
                              const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
                              const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                              const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
@@ -77,7 +78,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   uint64_t* o_done = p_full + 2 * NQ;                       // [NQ] O holds the step's contribution
   uint64_t* o_final = o_done + NQ;                          // [NQ] O holds the last step's contribution (one phase)
   uint64_t* drained = o_final + NQ;                         // every product issued has completed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 1);
+  uint64_t* q_full = drained + 1;                           // [NQ] the query tile has landed (when TMA brings it)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + NQ);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   pdl_launch_dependents();
@@ -116,11 +118,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   if (threadIdx.x == 0) {
     for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], NQ); }
     for (int i = 0; i < 2 * NQ; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); }
-    for (int i = 0; i < NQ; ++i) { mbar_init(&o_done[i], 1); mbar_init(&o_final[i], 1); }
+    for (int i = 0; i < NQ; ++i) { mbar_init(&o_done[i], 1); mbar_init(&o_final[i], 1); mbar_init(&q_full[i], 1); }
     mbar_init(drained, NQ);
     *abort_flag = 0;
     tma_prefetch_map(&tmK);
     tma_prefetch_map(&tmV);
+    if (q_by_tma) tma_prefetch_map(&tmQ);
   }
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   __syncthreads();                              // the barriers are there: the producer starts on the first keys and values
@@ -128,9 +131,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   uint32_t tmem_base = 0;
   if (warp != 4 * NQ) {
     if (warp == 4 * NQ + 1) t5_alloc(tmem_slot, C::TMEM_COLS);
-    if (warp < 4 * NQ) {
+    if (warp < 4 * NQ && !q_by_tma) {
       // the query tile of this warp group into shared memory, rows of 128 bytes per slice, 128-byte swizzled; every
-      // copy is on its way before the first one is waited for
+      // copy is on its way before the first one is waited for (cp.async moves 16 bytes a clock: 4,000 cycles for two
+      // tiles, which is why the copy engine brings them where it can)
       const int qt = warp >> 2, tid = threadIdx.x & 127;
       char* dst = q_s + qt * F5_Q_BYTES;
       constexpr int CHUNKS = HD / 8;
@@ -154,6 +158,20 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
 
   if (warp == 4 * NQ) {
     // ------------------------------------------------ producer: lane 0 issues, all lanes look pages up
+    if (q_by_tma && lane == 0) {
+      // The query tiles by the copy engine: the tensor map sees q as (head size, heads, tokens), a box is 64 columns of
+      // the G heads of a kv head for 128 / G tokens, which lands as 128 rows of 128 bytes in the order (token, head of
+      // the group): the tile's rows.  Tokens past the step's last read as zeros; rows past the request's are masked.
+#pragma unroll
+      for (int qt = 0; qt < NQ; ++qt) {
+        if (jhi[qt] > jlo[qt]) {
+          mbar_expect_tx(&q_full[qt], (unsigned)F5_Q_BYTES);
+#pragma unroll
+          for (int c = 0; c < F5_SLICES; ++c)
+            tma_load_3d(q_s + qt * F5_Q_BYTES + c * (F5_ROWS * 128), &tmQ, c * 64, kh * G, t0 + (row0 + qt * F5_ROWS) / G, &q_full[qt]);
+        }
+      }
+    }
     WarpPages wp;
     bool ok = true;
     int it = 0;
@@ -198,6 +216,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       if (!ok) break;
     }
     if (lane == 0) {
+      if (q_by_tma) {                              // (the query tiles too, should their tile have given up before it saw them)
+#pragma unroll
+        for (int qt = 0; qt < NQ; ++qt) {
+          bool done = jhi[qt] <= jlo[qt];
+          for (unsigned i = 0; i < MBAR_SPIN_LIMIT && !done; ++i) done = mbar_try_wait(&q_full[qt], 0u);
+          if (!done) atomicOr(err, VOB_ERR_TIMEOUT_BITS);
+        }
+      }
       const int first = it > ST ? it - ST : 0;     // copies in flight must land before the block exits
       for (int j = first; j < it; ++j) {
         bool done = false;
@@ -218,6 +244,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       const uint64_t k_desc0 = t5_smem_desc(kv_s);
       const uint64_t v_desc0 = t5_smem_desc_mn(kv_s + F5_KV_BYTES, F5_TILE * 128, 1024);
       bool ok = true;
+      if (q_by_tma && hi > lo) ok = mbar_wait(&q_full[qt], 0u, abort_flag, err);
       // S[buffer] = Q K_j^T
       auto scores = [&](int j) {
         const int i = j - lo;
@@ -426,6 +453,18 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
 
 using namespace vob;
 
+// Heads in a box of the query's tensor map (vob_tensor_map_bf16_heads with boxes of this many heads and 128 / this many
+// tokens), or 0 if the query tiles of these head counts cannot come by TMA (the group must divide 128 rows).
+VOB_API int vob_attention_prefill_q_box_heads(int nh, int kvh) {
+#if VOB_HD == 64 || VOB_HD == 128
+  if (kvh <= 0 || nh % kvh) return 0;
+  const int G = nh / kvh;
+  return F5_ROWS % G == 0 ? G : 0;
+#else
+  return 0;
+#endif
+}
+
 VOB_API int vob_attention_prefill_has_tc5() {
 #if VOB_HD == 64 || VOB_HD == 128
   return 1;
@@ -436,7 +475,7 @@ VOB_API int vob_attention_prefill_has_tc5() {
 
 // As vob_attention_prefill_tma (same tensor maps: 64-column slices, boxes of vob_attention_decode_box_keys rows), for
 // head sizes 64 and 128.  `query_tiles` is 1 or 2: how many tiles of 128 query rows a block takes.
-VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
+VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, const void* map_q, const void* q, long q_stride, void* out,
                                       const int* block_tables, int table_stride, const int* cu_q, const int* context_lens,
                                       int num_requests, int max_q, int nh, int kvh, int block_size, int window, float scale,
                                       long num_pages, int query_tiles, int* err, cudaStream_t stream) {
@@ -449,6 +488,8 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
     return VOB_UNSUPPORTED;
   const long rows = (long)max_q * (nh / kvh);
   const int box_keys = block_size % F5_TILE == 0 ? F5_TILE : RUN_KEYS;
+  // the query tiles come by TMA when a map was given and the heads of a group divide a tile's rows
+  const int q_by_tma = map_q != nullptr && vob_attention_prefill_q_box_heads(nh, kvh) > 0;
   static bool configured[2] = {false, false};
   if (query_tiles == 1) {
     if (!configured[0]) {
@@ -458,7 +499,8 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
     }
     dim3 grid((unsigned)((rows + F5_ROWS - 1) / F5_ROWS) * kvh, 1, num_requests);
     return launch_kernel(attention_prefill_tc5_kernel<1>, grid, F5<1>::THREADS, F5<1>::SMEM_BYTES, stream,
-                         *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride,
+                         *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, *(const CUtensorMap*)(q_by_tma ? map_q : map_k), q_by_tma,
+                         (const __nv_bfloat16*)q, q_stride,
                          (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size, window,
                          scale, num_pages, box_keys, err);
   }
@@ -469,7 +511,8 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
   }
   dim3 grid((unsigned)((rows + 2 * F5_ROWS - 1) / (2 * F5_ROWS)) * kvh, 1, num_requests);
   return launch_kernel(attention_prefill_tc5_kernel<2>, grid, F5<2>::THREADS, F5<2>::SMEM_BYTES, stream,
-                       *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride,
+                       *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, *(const CUtensorMap*)(q_by_tma ? map_q : map_k), q_by_tma,
+                       (const __nv_bfloat16*)q, q_stride,
                        (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size, window,
                        scale, num_pages, box_keys, err);
 #else

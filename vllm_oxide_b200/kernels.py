@@ -257,8 +257,11 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
         keys, slices = L.vob_attention_decode_box_keys(bs), L.vob_attention_decode_box_slices(bs)
         map_k, map_v = tensor_map(kcache.view(-1, hd), keys, slices), tensor_map(vcache.view(-1, hd), keys, slices)
         if use_tc5 and L.vob_attention_prefill_has_tc5() and q_stride % 8 == 0:
+            # the query tiles come by TMA too where the heads of a group divide a tile's 128 rows
+            box_heads = L.vob_attention_prefill_q_box_heads(nh, kvh)
+            map_q = tensor_map_heads(q, q_stride, nh, hd, box_heads, 128 // box_heads) if box_heads > 0 else None
             _check(L.vob_attention_prefill_tc5(
-                map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(block_tables), block_tables.shape[-1], _p(cu_q),
+                map_k, map_v, map_q, _p(q), ctypes.c_long(q_stride), _p(out), _p(block_tables), block_tables.shape[-1], _p(cu_q),
                 _p(context_lens), num_requests, max_q, nh, kvh, bs, window, ctypes.c_float(scale),
                 ctypes.c_long(kcache.shape[0]), query_tiles, _p(err), _stream()), "attention_prefill_tc5")
             return
@@ -301,6 +304,24 @@ def tensor_map(t: torch.Tensor, box_rows: int, box_slices: int):
                                                 ctypes.c_long(t.shape[1]), ctypes.c_long(t.stride(0)), box_rows, box_slices)
         if code != 0:
             raise KernelError(f"tensor map for a [{t.shape[0]}, {t.shape[1]}] matrix: {lib().vob_error_string(code).decode()}")
+        if len(_tensor_maps) > 4096:
+            _tensor_maps.clear()
+        hit = _tensor_maps[key] = (raw, ctypes.c_void_p(addr))
+    return hit[1]
+
+
+def tensor_map_heads(t: torch.Tensor, token_stride: int, heads: int, head_dim: int, box_heads: int, box_tokens: int):
+    """A TMA descriptor (host memory, cached) of token rows that begin with `heads` heads of `head_dim` bfloat16 each: one
+    copy brings a 64-column slice of `box_heads` heads for `box_tokens` tokens, as rows in the order (token, head)."""
+    key = (t.data_ptr(), t.shape[0], token_stride, heads, head_dim, box_heads, box_tokens, "heads")
+    hit = _tensor_maps.get(key)
+    if hit is None:
+        raw = (ctypes.c_char * 256)()
+        addr = (ctypes.addressof(raw) + 63) & ~63
+        code = lib().vob_tensor_map_bf16_heads(ctypes.c_void_p(addr), _p(t), ctypes.c_long(t.shape[0]), heads, head_dim,
+                                               ctypes.c_long(token_stride), box_heads, box_tokens)
+        if code != 0:
+            raise KernelError(f"tensor map for {t.shape[0]} token rows of {heads} heads: {lib().vob_error_string(code).decode()}")
         if len(_tensor_maps) > 4096:
             _tensor_maps.clear()
         hit = _tensor_maps[key] = (raw, ctypes.c_void_p(addr))

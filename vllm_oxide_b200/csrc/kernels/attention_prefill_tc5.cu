@@ -115,6 +115,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     jhi[qt] = (pos_hi - start) / F5_TILE + 1;
   }
 
+  // the producer asks for the pages of its first tiles now (the block tables were written before the step began), so
+  // that the look-up runs beside the set-up below
+  WarpPages wp;
+  if (warp == 4 * NQ) wp.advance(table, block_size, start, 0, lane, key_lo, key_end);
   if (threadIdx.x == 0) {
     for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], NQ); }
     for (int i = 0; i < 2 * NQ; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); }
@@ -172,12 +176,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
         }
       }
     }
-    WarpPages wp;
     bool ok = true;
     int it = 0;
     for (; it < n_tiles; ++it) {
       const int s = it % ST;
-      wp.advance(table, block_size, start, it, lane, key_lo, key_end);
+      if (it > 0) wp.advance(table, block_size, start, it, lane, key_lo, key_end);
       int pg[4];
 #pragma unroll
       for (int run = 0; run < 4; ++run) pg[run] = wp.page(it, run);

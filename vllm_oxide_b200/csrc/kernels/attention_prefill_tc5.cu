@@ -61,6 +61,7 @@ template <int NQ>
 __global__ void __launch_bounds__(F5<NQ>::THREADS, F5<NQ>::BLOCKS_PER_SM)
 attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                              const __grid_constant__ CUtensorMap tmQ, int q_by_tma,
+                             const __grid_constant__ CUtensorMap tmO, int o_by_tma,
                              const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
                              const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                              const int* __restrict__ context_lens, int nh, int kvh, int block_size, int window, float scale,
@@ -128,6 +129,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     tma_prefetch_map(&tmK);
     tma_prefetch_map(&tmV);
     if (q_by_tma) tma_prefetch_map(&tmQ);
+    if (o_by_tma) tma_prefetch_map(&tmO);
   }
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   __syncthreads();                              // the barriers are there: the producer starts on the first keys and values
@@ -424,6 +426,38 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
         t5_fence_after();
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* orow = out + (size_t)(t0 + tok) * nh * HD + (size_t)head * HD;
+        if (o_by_tma && all_rows) {
+          // A whole tile leaves through shared memory and the copy engine: its rows go, in the layout a load would have
+          // written them, where the query tile lay (every product that read it has completed), and one thread sends
+          // each 64-column slice with one copy.  A tile with rows past the request's end stores its rows itself.
+          char* stage = q_s + qt * F5_Q_BYTES;
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 64) {
+            uint32_t o[2][32];
+            t5_ld32_issue(lane_base + 2 * F5_TILE + c0, o[0]);
+            t5_ld32_issue(lane_base + 2 * F5_TILE + c0 + 32, o[1]);
+            t5_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 64; c += 8) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(o[c >> 5][(c & 31)]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 1]) * inv);
+              v.y = pack_bf16(__uint_as_float(o[c >> 5][(c & 31) + 2]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 3]) * inv);
+              v.z = pack_bf16(__uint_as_float(o[c >> 5][(c & 31) + 4]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 5]) * inv);
+              v.w = pack_bf16(__uint_as_float(o[c >> 5][(c & 31) + 6]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 7]) * inv);
+              *reinterpret_cast<uint4*>(stage + (c0 >> 6) * (F5_ROWS * 128) + swizzled_offset(r, c >> 3)) = v;
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+          if (qt == 0) asm volatile("bar.sync 2, 128;\n" ::: "memory");          // the tile's four warps
+          else asm volatile("bar.sync 3, 128;\n" ::: "memory");
+          if ((warp & 3) == 0 && lane == 0) {
+#pragma unroll
+            for (int c = 0; c < F5_SLICES; ++c)
+              tma_store_3d(&tmO, stage + c * (F5_ROWS * 128), c * 64, kh * G, t0 + r_first / G);
+            tma_store_commit();
+            tma_store_wait_read();
+          }
+        } else
 #pragma unroll
         for (int c0 = 0; c0 < HD; c0 += 64) {
           uint32_t o[2][32];
@@ -478,7 +512,7 @@ VOB_API int vob_attention_prefill_has_tc5() {
 
 // As vob_attention_prefill_tma (same tensor maps: 64-column slices, boxes of vob_attention_decode_box_keys rows), for
 // head sizes 64 and 128.  `query_tiles` is 1 or 2: how many tiles of 128 query rows a block takes.
-VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, const void* map_q, const void* q, long q_stride, void* out,
+VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, const void* map_q, const void* map_o, const void* q, long q_stride, void* out,
                                       const int* block_tables, int table_stride, const int* cu_q, const int* context_lens,
                                       int num_requests, int max_q, int nh, int kvh, int block_size, int window, float scale,
                                       long num_pages, int query_tiles, int* err, cudaStream_t stream) {
@@ -493,6 +527,7 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
   const int box_keys = block_size % F5_TILE == 0 ? F5_TILE : RUN_KEYS;
   // the query tiles come by TMA when a map was given and the heads of a group divide a tile's rows
   const int q_by_tma = map_q != nullptr && vob_attention_prefill_q_box_heads(nh, kvh) > 0;
+  const int o_by_tma = map_o != nullptr && vob_attention_prefill_q_box_heads(nh, kvh) > 0;   // whole output tiles leave the same way
   static bool configured[2] = {false, false};
   if (query_tiles == 1) {
     if (!configured[0]) {
@@ -503,6 +538,7 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
     dim3 grid((unsigned)((rows + F5_ROWS - 1) / F5_ROWS) * kvh, 1, num_requests);
     return launch_kernel(attention_prefill_tc5_kernel<1>, grid, F5<1>::THREADS, F5<1>::SMEM_BYTES, stream,
                          *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, *(const CUtensorMap*)(q_by_tma ? map_q : map_k), q_by_tma,
+                         *(const CUtensorMap*)(o_by_tma ? map_o : map_k), o_by_tma,
                          (const __nv_bfloat16*)q, q_stride,
                          (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size, window,
                          scale, num_pages, box_keys, err);
@@ -515,6 +551,7 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
   dim3 grid((unsigned)((rows + 2 * F5_ROWS - 1) / (2 * F5_ROWS)) * kvh, 1, num_requests);
   return launch_kernel(attention_prefill_tc5_kernel<2>, grid, F5<2>::THREADS, F5<2>::SMEM_BYTES, stream,
                        *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, *(const CUtensorMap*)(q_by_tma ? map_q : map_k), q_by_tma,
+                         *(const CUtensorMap*)(o_by_tma ? map_o : map_k), o_by_tma,
                        (const __nv_bfloat16*)q, q_stride,
                        (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, nh, kvh, block_size, window,
                        scale, num_pages, box_keys, err);

@@ -260,8 +260,10 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
             # the query tiles come by TMA too where the heads of a group divide a tile's 128 rows
             box_heads = L.vob_attention_prefill_q_box_heads(nh, kvh)
             map_q = tensor_map_heads(q, q_stride, nh, hd, box_heads, 128 // box_heads) if box_heads > 0 else None
+            map_o = (tensor_map_heads(out, nh * hd, nh, hd, box_heads, 128 // box_heads)
+                     if box_heads > 0 and out.is_contiguous() and out.data_ptr() % 16 == 0 else None)
             _check(L.vob_attention_prefill_tc5(
-                map_k, map_v, map_q, _p(q), ctypes.c_long(q_stride), _p(out), _p(block_tables), block_tables.shape[-1], _p(cu_q),
+                map_k, map_v, map_q, map_o, _p(q), ctypes.c_long(q_stride), _p(out), _p(block_tables), block_tables.shape[-1], _p(cu_q),
                 _p(context_lens), num_requests, max_q, nh, kvh, bs, window, ctypes.c_float(scale),
                 ctypes.c_long(kcache.shape[0]), query_tiles, _p(err), _stream()), "attention_prefill_tc5")
             return

@@ -6,18 +6,23 @@
 //   warps 0 .. 4NQ-1   softmax: warp w of a tile owns rows 32(w%4) .. +31 of it, a thread owns ONE row: it reads the
 //                      row's 64 scores from tensor memory (tcgen05.ld), masks, takes the maximum and the sum without
 //                      any exchange between threads, writes P in bfloat16 back to tensor memory over the scores (the A
-//                      operand of the second product), and at the end divides the row of O by its sum and stores it
-//                      (32 bytes a store).  From a row's second step on the exponentials are taken against the old
-//                      reference maximum beside the search for the new one, and taken again only if it had to move;
-//   warp 4NQ           producer: looks the pages up a chunk ahead and brings K and V tiles in by TMA into a ring of
+//                      operand of the second product), and at the end divides the row of O by its sum and stores it:
+//                      a whole tile through shared memory (where the query tile lay) and one TMA store a 64-column
+//                      slice, a tile with rows past the request's end row by row (32 bytes a store).  From a row's
+//                      second step on the exponentials are taken against the old reference maximum beside the search
+//                      for the new one, and taken again only if it had to move;
+//   warp 4NQ           producer: brings the query tiles in (TMA: the tensor map sees q as head size x heads x tokens, a
+//                      box is 64 columns of a group's heads for 128 / group tokens and lands as the tile's rows; where
+//                      the group does not divide 128 the softmax warps bring them by cp.async instead),
+//                      looks the pages up a chunk ahead and brings K and V tiles in by TMA into a ring of
 //                      stages (the K tile is the K-major B operand of the first product as it lands, the V tile the
 //                      MN-major B operand of the second one: no transposition anywhere);
 //   warps 4NQ+1 ..     one per query tile (the first of them allocates tensor memory): a thread issues the tile's
 //                      products, the scores of step j+1 into a second S buffer while the softmax of step j runs;
 //                      tcgen05.commit tells the softmax warps that S is complete and that O has been updated, and
 //                      the producer that the tile is done with a stage.  The tiles do not wait for one another.
-// At a block's start the producer goes for the first keys and values as soon as the barriers exist, while the softmax
-// warps bring the query tiles in (cp.async, all copies in flight at once) and tensor memory is allocated.
+// At a block's start the producer asks for its first pages before the barriers are set up and goes for the query
+// tiles and the first keys and values as soon as they exist, while tensor memory is allocated.
 // A wait on an mbarrier goes by the parity of the phase, so it can tell only two states apart: the scores and P have
 // a barrier per buffer (a buffer's next use needs the waiter's own progress).  O's barrier gets a phase per step; a
 // softmax thread that has to rescale O at step i waits on it for step i - 1, when it can be in two states only (that

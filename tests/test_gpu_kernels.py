@@ -465,7 +465,10 @@ def test_attention_decode_reads_the_right_far_key(key_pos, window, expect_hit):
 # the kernels behind attention_prefill: tcgen05 with one or two query tiles a block (head sizes 64 and 128),
 # mma.sync with TMA copies (head sizes that are a multiple of 64), mma.sync with cp.async (every head size)
 PREFILL_KERNELS = {"tc5x2": dict(query_tiles=2), "tc5x1": dict(query_tiles=1), "tma": dict(use_tc5=False),
-                   "cp.async": dict(use_tc5=False, use_tma=False)}
+                   "cp.async": dict(use_tc5=False, use_tma=False),
+                   # the tcgen05 kernel with its query tiles by cp.async and its output stored row by row, as for groups
+                   # of heads that do not divide a tile's 128 rows
+                   "tc5x2-rows": dict(query_tiles=2, tiles_by_tma=False)}
 
 
 def prefill_attention(q, out, kc, vc, bt, cu_q, ctx, T, nh, kvh, hd, window, err, kernel="tc5x2", **_):
@@ -502,6 +505,19 @@ def test_attention_prefill(case, kernel):
     got, want = run_attention(functools.partial(prefill_attention, kernel=kernel), torch.bfloat16, nh, kvh, hd, bs,
                               window, q_lens, ctx_lens)
     assert torch.allclose(got, want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("case", [c for c in PREFILL_CASES if c[2] in (64, 128) and 128 % (c[0] // c[1]) == 0])
+def test_attention_prefill_tiles_by_tma_are_the_same_bits(case):
+    """How the query tiles come in and how whole output tiles leave (copy engine, or cp.async and row stores) changes no
+    arithmetic: the two give the same bits, for whole tiles and for tiles that end inside a request."""
+    import functools
+    nh, kvh, hd, bs, window, q_lens, ctx_lens = case
+    a, _ = run_attention(functools.partial(prefill_attention, kernel="tc5x2"), torch.bfloat16, nh, kvh, hd, bs, window,
+                         q_lens, ctx_lens)
+    b, _ = run_attention(functools.partial(prefill_attention, kernel="tc5x2-rows"), torch.bfloat16, nh, kvh, hd, bs, window,
+                         q_lens, ctx_lens)
+    assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("key_pos,window,expect_hit", [(3, 0, True), (63, 0, True), (64, 0, True), (791, 0, True),

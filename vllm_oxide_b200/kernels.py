@@ -246,9 +246,11 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, conte
 
 def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, max_q, nh, kvh,
                       hd, window: int, scale: float, err, use_tma: bool = True, use_tc5: bool = True,
-                      query_tiles: int = 2) -> None:
+                      query_tiles: int = 2, tiles_by_tma: bool = True) -> None:
     """Requests that bring more than one token; the others are skipped.  Head sizes 64 and 128 run on the tcgen05
-    tensor cores (`use_tc5`), other multiples of 64 on mma.sync with TMA copies (`use_tma`), the rest with cp.async."""
+    tensor cores (`use_tc5`; `tiles_by_tma` False makes that kernel bring its query tiles in by cp.async and store its
+    output row by row also where TMA could), other multiples of 64 on mma.sync with TMA copies (`use_tma`), the rest with
+    cp.async."""
     _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens)
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
     L = attention_lib(hd)
@@ -258,7 +260,7 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
         map_k, map_v = tensor_map(kcache.view(-1, hd), keys, slices), tensor_map(vcache.view(-1, hd), keys, slices)
         if use_tc5 and L.vob_attention_prefill_has_tc5() and q_stride % 8 == 0:
             # the query tiles come by TMA too where the heads of a group divide a tile's 128 rows
-            box_heads = L.vob_attention_prefill_q_box_heads(nh, kvh)
+            box_heads = L.vob_attention_prefill_q_box_heads(nh, kvh) if tiles_by_tma else 0
             map_q = tensor_map_heads(q, q_stride, nh, hd, box_heads, 128 // box_heads) if box_heads > 0 else None
             map_o = (tensor_map_heads(out, nh * hd, nh, hd, box_heads, 128 // box_heads)
                      if box_heads > 0 and out.is_contiguous() and out.data_ptr() % 16 == 0 else None)

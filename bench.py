@@ -469,6 +469,10 @@ def main() -> int:
         opts = EngineOptions(max_model_len=long_ctx + 2 * BLOCK, block_size=BLOCK, num_kv_blocks=pages, max_num_seqs=8,
                              max_num_batched_tokens=8192, dtype="bfloat16")
         llm = LLM("<random weights>", opts, _model=(config, model))
+        # a longer prompt in one step (attention is a larger share of it)
+        p_ms = prefill_run(llm, 8192, reps=2, warmup=1)
+        points["prefill_8192"] = round(8192 * 1000.0 / p_ms, 1)
+        points["frac_prefill_8192"] = round(prefill_flops(cfg, 8192) / (p_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
         for ctx0 in (8192, long_ctx):
             for b in (1, 8):
                 pms, _, ctx = decode_run(llm, b, 16, warmup, ctx0)

@@ -304,6 +304,45 @@ def test_the_program_itself(model_folders, plain_models, tmp_path):
     assert sorted(os.listdir(out)) == ["0.f32", "1.f32", "2.f32", "3.f32"]
 
 
+def test_the_program_step_by_step(model_folders, plain_models, tmp_path):
+    """The next step is written only after `done <step>` of the one before has been read (a pipe, no end of input in
+    between): the step's file is complete by then, in bfloat16, with the default pages of 64 tokens and a pool so small
+    that the second request lands on the first one's pages."""
+    name, dtype = "D", "bfloat16"
+    a, b = tokens_for(name, 100, salt=11), tokens_for(name, 90, salt=12)
+    steps = [
+        dict(step=0, entries=[dict(id="a", tokens=a[:64], want=[63])], end=[]),
+        dict(step=1, entries=[dict(id="a", tokens=a[64:66], want=[1])], end=[]),
+        dict(step=2, entries=[dict(id="a", tokens=a[66:], want=[0, 33])], end=["a"]),
+        dict(step=3, entries=[dict(id="b", tokens=b[:89], want=[])], end=[]),
+        dict(step=4, entries=[dict(id="b", tokens=b[89:], want=[0])], end=["b"]),
+    ]
+    out = tmp_path / "out"
+    proc = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_folders[name],
+                             "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
+                            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
+    V = TINY[name]["config"]["vocab_size"]
+    pa, pb = plain_logits(plain_models, name, a, dtype), plain_logits(plain_models, name, b, dtype)
+    expect = {0: pa[63:64], 1: pa[65:66], 2: pa[[66, 99]], 4: pb[89:90]}
+    try:
+        for s_ in steps:
+            proc.stdin.write(json.dumps(s_) + "\n")
+            proc.stdin.flush()
+            line = proc.stdout.readline()
+            while line and not line.startswith("done"):
+                line = proc.stdout.readline()          # lines of the first build, if any
+            assert line.strip() == f"done {s_['step']}"
+            if s_["step"] in expect:
+                got = np.fromfile(out / f"{s_['step']}.f32", dtype="<f4").reshape(-1, V)
+                check(got, expect[s_["step"]], dtype, f"step {s_['step']}")
+        proc.stdin.close()
+        assert proc.wait(timeout=120) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    assert sorted(os.listdir(out)) == ["0.f32", "1.f32", "2.f32", "4.f32"]
+
+
 def test_running_out_of_pages_is_an_error_not_a_wrong_result(model_folders):
     r = runner(model_folders, "A", "float32", 32)
     r.step([dict(id="a", tokens=list(range(30)), want=[])], [])

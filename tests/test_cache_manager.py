@@ -134,6 +134,31 @@ def test_prefix_cache_hits_share_full_pages_but_never_the_last():
     m.free_request(6)
 
 
+def test_what_could_be_restored_is_a_question_that_takes_nothing():
+    """`restorable_tokens` answers what `lookup_prefix` would give a new request, and leaves every count as it was;
+    with a window group (prefix caching off) nothing can be restored."""
+    m = mgr(((4, 8, 0), (4, 8, 0)), prefix=True)
+    toks = list(range(200, 214))
+    assert m.restorable_tokens(toks) == 0
+    m.add_request(1)
+    m.ensure(1, 0, 14)
+    m.commit(1, toks, 14)
+    free = (m.num_free_blocks(0), m.num_free_blocks(1))
+    page = m.block_table(1, 0)[0]
+    assert m.restorable_tokens(toks) == 12 and m.restorable_tokens(toks[:12]) == 8     # never the page of the last token
+    assert m.restorable_tokens(toks[:4] + [1, 2, 3, 4, 5]) == 4 and m.restorable_tokens([7] + toks) == 0
+    assert (m.num_free_blocks(0), m.num_free_blocks(1)) == free and m.ref_count(0, page) == 1
+    m.add_request(2)
+    assert m.lookup_prefix(2, toks) == 12            # the same answer, and now the pages are taken
+    m.free_request(1); m.free_request(2)
+    assert m.restorable_tokens(toks) == 12 and m.check_invariants() == ""
+    w = mgr(((4, 8, 0), (4, 8, 6)), prefix=True)
+    w.add_request(1)
+    w.ensure(1, 0, 14)
+    w.commit(1, toks, 14)
+    assert w.restorable_tokens(toks) == 0
+
+
 def test_prefix_cache_is_off_with_windows():
     assert not mgr(((4, 8, 0), (4, 8, 6)), prefix=True).prefix_caching
     assert mgr(((4, 8, 0), (4, 9, 0)), prefix=True).prefix_caching

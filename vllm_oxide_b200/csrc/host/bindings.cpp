@@ -62,6 +62,9 @@ PYBIND11_MODULE(_host, m) {
       .def("lookup_prefix", [](KvCacheManager& k, int64_t id, const std::vector<int32_t>& t) {
         return k.lookup_prefix(id, t.data(), static_cast<int>(t.size()));
       })
+      .def("restorable_tokens", [](const KvCacheManager& k, const std::vector<int32_t>& t) {
+        return k.restorable_tokens(t.data(), static_cast<int>(t.size()));
+      })
       .def("pages_needed", &KvCacheManager::pages_needed)
       .def("can_ensure", &KvCacheManager::can_ensure)
       .def("ensure", &KvCacheManager::ensure)

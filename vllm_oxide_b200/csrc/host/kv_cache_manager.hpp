@@ -99,6 +99,26 @@ class KvCacheManager {
     return hits * bs;
   }
 
+  // "Restorable at which position?": how many leading tokens of `tokens` a new request could take from cached pages
+  // right now, in every group at once (what lookup_prefix would return), without taking anything.  0 when prefix
+  // caching is off, which it is whenever some group keeps a window only or has pages of another size, and which the
+  // engine asks for when a part keeps per-request state (nothing of a state survives outside its slot, so such a
+  // request can only be computed from its first token).  A scheduler can price an admission with it.
+  int restorable_tokens(const int32_t* tokens, int n) const {
+    if (!prefix_caching_) return 0;
+    const int bs = specs_[0].block_size;
+    int64_t prev = -1;
+    int hits = 0;
+    for (int i = 0; (i + 1) * bs < n; ++i) {
+      const int64_t h = chain_hash(prev, tokens + i * bs, bs);
+      for (size_t g = 0; g < specs_.size(); ++g)
+        if (pools_[g].lookup(h, tokens + i * bs, bs) < 0) return hits * bs;
+      prev = h;
+      ++hits;
+    }
+    return hits * bs;
+  }
+
   // New pages that positions [start, start+n) need, per group.
   std::vector<int> pages_needed(int64_t id, int start, int n) const {
     const Req& r = req(id);

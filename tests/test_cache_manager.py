@@ -152,16 +152,57 @@ def test_what_could_be_restored_is_a_question_that_takes_nothing():
     assert m.lookup_prefix(2, toks) == 12            # the same answer, and now the pages are taken
     m.free_request(1); m.free_request(2)
     assert m.restorable_tokens(toks) == 12 and m.check_invariants() == ""
-    w = mgr(((4, 8, 0), (4, 8, 6)), prefix=True)
-    w.add_request(1)
-    w.ensure(1, 0, 14)
-    w.commit(1, toks, 14)
-    assert w.restorable_tokens(toks) == 0
+    u = mgr(((4, 8, 0), (8, 8, 0)), prefix=True)     # pages of two sizes: no hits
+    u.add_request(1)
+    u.ensure(1, 0, 14)
+    u.commit(1, toks, 14)
+    assert u.restorable_tokens(toks) == 0
 
 
-def test_prefix_cache_is_off_with_windows():
-    assert not mgr(((4, 8, 0), (4, 8, 6)), prefix=True).prefix_caching
+def test_prefix_cache_is_off_with_pages_of_two_sizes():
+    assert not mgr(((4, 8, 0), (8, 8, 0)), prefix=True).prefix_caching
     assert mgr(((4, 8, 0), (4, 9, 0)), prefix=True).prefix_caching
+    assert mgr(((4, 8, 0), (4, 8, 6)), prefix=True).prefix_caching
+
+
+def test_a_prefix_hit_in_a_window_group_takes_only_the_pages_a_later_query_reads():
+    """Pages of 4, a group that keeps all keys and one with a window of 6.  After 14 tokens the window group has given
+    pages 0 and 1 back, but a freed page stays discoverable until it is used again; a new request with the same
+    tokens takes pages 0..2 of the first group and, of the window group, pages 1 and 2 (a query at position 12 reads
+    keys 7..11), leaving entry 0 empty.  Once the window group's old pages have been overwritten, the hit shrinks to
+    what every group can still supply."""
+    m = mgr(((4, 16, 0), (4, 6, 6)), prefix=True)
+    toks = list(range(300, 314))
+    m.add_request(1)
+    m.ensure(1, 0, 14)
+    m.commit(1, toks, 14)
+    m.advance(1, 14)
+    t_full, t_win = list(m.block_table(1, 0)), list(m.block_table(1, 1))
+    assert [b >= 0 for b in t_win] == [False, False, True, True]
+    first_pages = [m.slot_mapping(1, 1, 8, 1)[0] // 4]                     # the window group's page of positions 8..11
+    assert m.restorable_tokens(toks) == 12
+    m.add_request(2)
+    assert m.lookup_prefix(2, toks) == 12
+    assert m.block_table(2, 0) == t_full[:3]
+    w2 = m.block_table(2, 1)
+    assert w2[0] == -1 and w2[1] >= 0 and w2[2] == first_pages[0] and m.ref_count(1, w2[2]) == 2
+    assert m.ensure(2, 12, 2)
+    m.commit(2, toks, 14)
+    m.advance(2, 14)                                                      # starts releasing where the hit began
+    assert [b >= 0 for b in m.block_table(2, 1)] == [False, False, True, True] and m.check_invariants() == ""
+    m.free_request(1); m.free_request(2)
+    assert m.num_free_blocks(1) == 6 and m.restorable_tokens(toks) == 12   # still discoverable
+    m.add_request(3)
+    assert m.ensure(3, 0, 24)                                             # takes all six pages of the window group
+    m.free_request(3)
+    assert m.restorable_tokens(toks) == 0 and m.check_invariants() == ""
+    # a window as long as the prefix: the window group needs every page too
+    k = mgr(((4, 16, 0), (4, 16, 40)), prefix=True)
+    k.add_request(1)
+    k.ensure(1, 0, 14)
+    k.commit(1, toks, 14)
+    k.add_request(2)
+    assert k.lookup_prefix(2, toks) == 12 and all(b >= 0 for b in k.block_table(2, 1))
 
 
 def test_state_slots():
@@ -185,7 +226,15 @@ def test_random_orders_lose_no_page(seed):
     no page is lost, held twice or freed twice, and slot maps of live requests never collide."""
     rng = random.Random(seed)
     groups = ((4, 24, 0), (4, 24, 9)) if seed % 2 else ((8, 20, 0),)
-    m = mgr(groups, slots=5, prefix=(seed % 2 == 0))
+    m = mgr(groups, slots=5, prefix=(seed % 2 == 0 or seed >= 3))        # seeds 3 and 5: hits in a window group too
+
+    def readable(rid, done):
+        """Every position that a query at position `done` reads has a page, in every group."""
+        for g in range(m.num_groups):
+            w = m.group(g).window
+            lo = max(0, done - w + 1) if w > 0 else 0
+            if done > lo:
+                assert all(s >= 0 for s in m.slot_mapping(rid, g, lo, done - lo)), (rid, g, lo, done)
     live = {}
     next_id = 0
     for _ in range(600):
@@ -194,6 +243,8 @@ def test_random_orders_lose_no_page(seed):
             if m.add_request(next_id):
                 toks = [rng.randrange(6) for _ in range(rng.randrange(1, 70))]
                 live[next_id] = dict(tokens=toks, done=m.lookup_prefix(next_id, toks))
+                assert live[next_id]["done"] < len(toks)
+                readable(next_id, live[next_id]["done"])
                 next_id += 1
         elif op < 0.8 and live:
             rid = rng.choice(list(live))
@@ -208,10 +259,12 @@ def test_random_orders_lose_no_page(seed):
                 r["done"] += n
                 m.commit(rid, r["tokens"], r["done"])
                 m.advance(rid, r["done"])
+                readable(rid, r["done"])
         elif op < 0.9 and live:
             rid = rng.choice(list(live))
             m.release_pages(rid)                      # preempted: pages back, request stays
             live[rid]["done"] = m.lookup_prefix(rid, live[rid]["tokens"])
+            readable(rid, live[rid]["done"])
         elif live:
             rid = rng.choice(list(live))
             m.free_request(rid)

@@ -222,12 +222,14 @@ def test_first_tokens_of_a_sequence(model_folders, plain_models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_prefix_hits_start_on_another_requests_pages(model_folders, plain_models, name, dtype):
     """With the prefix cache on, a request whose first tokens another request has computed starts on that request's
     pages: while the other is live (shared pages, counted twice), after it has ended (pages taken back out of the free
     list), and not at all once the pages have been handed out again (stale hashes must not be found).  Every wanted
-    row against the plain implementation of the request's own tokens."""
+    row against the plain implementation of the request's own tokens.  C and D have layers with a window beside layers
+    that keep all keys: their window group supplies the pages that a query after the hit still reads, some of which
+    the first request has already given back."""
     from vllm_oxide_b200.engine.trace import TraceRunner
     bs = TINY[name]["block_size"]
     shared = tokens_for(name, 3 * bs + 5, salt=31)

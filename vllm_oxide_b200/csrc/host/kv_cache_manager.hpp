@@ -39,9 +39,9 @@ class KvCacheManager {
     for (const auto& g : groups) {
       if (g.window < 0) throw PoolError("KvCacheManager: negative window");
       pools_.emplace_back(g.num_blocks, g.block_size);
-      same = same && g.window == 0 && g.block_size == groups[0].block_size;
+      same = same && g.block_size == groups[0].block_size;
     }
-    // A prefix hit must hold in every group at once; with windows or unequal page sizes it is off.
+    // A prefix hit must hold in every group at once, page for page; with unequal page sizes it is off.
     prefix_caching_ = prefix_caching && same;
     for (int s = num_state_slots - 1; s >= 0; --s) free_slots_.push_back(s);
     num_state_slots_ = num_state_slots;
@@ -71,52 +71,38 @@ class KvCacheManager {
 
   // Takes the pages of the longest cached prefix of `tokens` into the (empty) block tables
   // and returns how many tokens they cover. The page that holds the last token is never taken.
+  // A group that keeps all keys takes every page of the prefix; a window group only those that a
+  // query after the prefix can still read (the earlier entries of its table stay empty, as if
+  // the window had passed them).
   int lookup_prefix(int64_t id, const int32_t* tokens, int n) {
     Req& r = req(id);
     if (!prefix_caching_) return 0;
     for (auto& t : r.tables)
       if (!t.empty()) throw PoolError("KvCacheManager: lookup_prefix on a request that already holds pages");
-    const int bs = specs_[0].block_size;
-    int64_t prev = -1;
-    int hits = 0;
-    for (int i = 0; (i + 1) * bs < n; ++i) {
-      int64_t h = chain_hash(prev, tokens + i * bs, bs);
-      std::vector<int> ids(specs_.size());
-      bool all = true;
-      for (size_t g = 0; g < specs_.size() && all; ++g) {
-        ids[g] = pools_[g].lookup(h, tokens + i * bs, bs);
-        all = ids[g] >= 0;
+    std::vector<int64_t> hashes;
+    std::vector<std::vector<int>> found;
+    const int hits = cached_prefix_pages(tokens, n, &hashes, &found);
+    for (size_t g = 0; g < specs_.size(); ++g) {
+      const int lo = first_page_needed(g, hits);
+      r.tables[g].assign(hits, -1);
+      for (int i = lo; i < hits; ++i) {
+        pools_[g].retain(found[g][i]);
+        r.tables[g][i] = found[g][i];
       }
-      if (!all) break;
-      for (size_t g = 0; g < specs_.size(); ++g) {
-        pools_[g].retain(ids[g]);
-        r.tables[g].push_back(ids[g]);
-      }
-      r.page_hashes.push_back(h);
-      prev = h;
-      ++hits;
+      if (specs_[g].window > 0) r.released_upto[g] = lo;
     }
-    return hits * bs;
+    r.page_hashes.assign(hashes.begin(), hashes.begin() + hits);
+    return hits * specs_[0].block_size;
   }
 
   // "Restorable at which position?": how many leading tokens of `tokens` a new request could take from cached pages
   // right now, in every group at once (what lookup_prefix would return), without taking anything.  0 when prefix
-  // caching is off, which it is whenever some group keeps a window only or has pages of another size, and which the
-  // engine asks for when a part keeps per-request state (nothing of a state survives outside its slot, so such a
-  // request can only be computed from its first token).  A scheduler can price an admission with it.
+  // caching is off, which it is when the groups' pages are of different sizes, and which the engine asks for when a
+  // part keeps per-request state (nothing of a state survives outside its slot, so such a request can only be
+  // computed from its first token).  A scheduler can price an admission with it.
   int restorable_tokens(const int32_t* tokens, int n) const {
     if (!prefix_caching_) return 0;
-    const int bs = specs_[0].block_size;
-    int64_t prev = -1;
-    int hits = 0;
-    for (int i = 0; (i + 1) * bs < n; ++i) {
-      const int64_t h = chain_hash(prev, tokens + i * bs, bs);
-      for (size_t g = 0; g < specs_.size(); ++g)
-        if (pools_[g].lookup(h, tokens + i * bs, bs) < 0) return hits * bs;
-      prev = h;
-      ++hits;
-    }
-    return hits * bs;
+    return cached_prefix_pages(tokens, n, nullptr, nullptr) * specs_[0].block_size;
   }
 
   // New pages that positions [start, start+n) need, per group.
@@ -266,6 +252,50 @@ class KvCacheManager {
   }
 
  private:
+  // The first page of group g that a query at a position >= pages * block_size can read (0 for a group that keeps
+  // all keys): the same rule by which advance() gives pages back.
+  int first_page_needed(size_t g, int pages) const {
+    const int w = specs_[g].window;
+    if (w <= 0) return 0;
+    const int first_needed = pages * specs_[g].block_size - w + 1;
+    return first_needed <= 0 ? 0 : std::min(pages, first_needed / specs_[g].block_size);
+  }
+
+  // The most leading pages of `tokens` (never the one of the last token) that every group can supply: all of them in
+  // a group that keeps all keys, the ones a later query can still read in a window group.  `found[g][i]` is group g's
+  // page for page i of the prefix or -1, `hashes[i]` the chained hash of page i.
+  int cached_prefix_pages(const int32_t* tokens, int n, std::vector<int64_t>* hashes,
+                          std::vector<std::vector<int>>* found) const {
+    const int bs = specs_[0].block_size;
+    std::vector<int64_t> hs;
+    std::vector<std::vector<int>> ids(specs_.size());
+    int64_t prev = -1;
+    int limit = 0;
+    for (int i = 0; (i + 1) * bs < n; ++i) {
+      const int64_t h = chain_hash(prev, tokens + i * bs, bs);
+      bool all = true;
+      for (size_t g = 0; g < specs_.size(); ++g) {
+        const int page = pools_[g].lookup(h, tokens + i * bs, bs);
+        ids[g].push_back(page);
+        all = all && (page >= 0 || specs_[g].window > 0);
+      }
+      if (!all) break;
+      hs.push_back(h);
+      prev = h;
+      limit = i + 1;
+    }
+    int hits = limit;
+    for (; hits > 0; --hits) {
+      bool ok = true;
+      for (size_t g = 0; g < specs_.size() && ok; ++g)
+        for (int i = first_page_needed(g, hits); i < hits && ok; ++i) ok = ids[g][i] >= 0;
+      if (ok) break;
+    }
+    if (hashes) *hashes = std::move(hs);
+    if (found) *found = std::move(ids);
+    return hits;
+  }
+
   struct Req {
     std::vector<std::vector<int>> tables;
     std::map<size_t, int> released_upto;  // per window group: first table index not yet released

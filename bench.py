@@ -367,11 +367,11 @@ def attention_kernels_run(pk) -> dict:
         ctx = ctx_host.to(dev)
         nbytes = float(ctx_host.sum()) * kvh * hd * 2 * 2
         row = {}
-        for mode, on in (("persistent", True), ("block_per_pair", False)):
-            kernels.attention_decode_persistent(hd, on)
+        for mode, pairs in (("persistent", kernels.decode_pairs_counter(dev)), ("block_per_pair", None)):
 
             def launch():
-                kernels.attention_decode(q, nh * hd, o, kc, vc, bt, cu_q, ctx, B, nh, kvh, hd, 0, 1 / math.sqrt(hd), 1, None, err)
+                kernels.attention_decode(q, nh * hd, o, kc, vc, bt, cu_q, ctx, B, nh, kvh, hd, 0, 1 / math.sqrt(hd), 1, None, err,
+                                         pairs=pairs)
             for _ in range(5):
                 launch()
             torch.cuda.synchronize()
@@ -383,7 +383,6 @@ def attention_kernels_run(pk) -> dict:
             torch.cuda.synchronize()
             us = e0.elapsed_time(e1) / 50 * 1e3
             row[mode] = {"us": round(us, 1), "gbs": round(nbytes / us / 1e3), "frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
-        kernels.attention_decode_persistent(hd, True)
         out[name] = row
         assert err.item() == 0
         del kc, vc

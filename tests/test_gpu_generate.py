@@ -299,19 +299,20 @@ def test_hundreds_of_requests_decode_through_the_persistent_attention_blocks(mod
     n, new = 160, 6
     prompts = [tokens_for("D", 3 + (7 * i) % 58, salt=900 + i) for i in range(n)]
     sp = SamplingParams(max_tokens=new, ignore_eos=True)
-    hd = TINY["D"]["config"]["head_dim"]
     assert n * TINY["D"]["config"]["num_key_value_heads"] > 2 * kernels.sm_count()
     runs = []
     for persistent in (True, False):
-        kernels.attention_decode_persistent(hd, persistent)
-        try:
-            llm = make_llm(model_folders, "D", "bfloat16", max_num_seqs=n, num_kv_blocks=2 * n + 8, max_num_batched_tokens=8192,
-                           enable_prefix_caching=False)
-            runs.append([o.token_ids for o in llm.generate(prompts, [sp] * n)])
-            assert llm.core.graph_replays > 0
-            del llm
-        finally:
-            kernels.attention_decode_persistent(hd, True)
+        llm = make_llm(model_folders, "D", "bfloat16", max_num_seqs=n, num_kv_blocks=2 * n + 8, max_num_batched_tokens=8192,
+                       enable_prefix_caching=False)
+        mixers = [p for b in llm.model.blocks for p in b.parts() if hasattr(p, "_pairs")]
+        assert mixers and all(m._pairs is not None for m in mixers)
+        if not persistent:
+            for m in mixers:
+                m._pairs = None                    # without its counter a layer runs one block per pair
+        runs.append([o.token_ids for o in llm.generate(prompts, [sp] * n)])
+        assert llm.core.graph_replays > 0
+        assert all(m._pairs is None or m._pairs.tolist() == [0, 0] for m in mixers)
+        del llm
     assert runs[0] == runs[1]
     full = TraceRunner(model_folders["D"], "float32", 256, TINY["D"]["block_size"])
     sure = sum(greedy_tokens_agree_with_32_bit_logits(full, prompts[i], runs[0][i], f"request {i}") for i in range(0, n, 8))

@@ -377,14 +377,19 @@ def test_attention_generic_does_not_depend_on_the_batch():
     assert torch.equal(out[1:4].cpu(), a_got)
 
 
-def decode_attention(num_splits, use_tma=True):
+def decode_attention(num_splits, use_tma=True, persistent=False):
     def fn(q, out, kc, vc, bt, cu_q, ctx, T, nh, kvh, hd, window, err, **_):
         from vllm_oxide_b200 import kernels
         B = ctx.shape[0]
         n = kernels.attention_decode_scratch_floats(hd, B, nh, num_splits)
         scratch = torch.full((max(n, 1),), float("nan"), device=DEV)
-        kernels.attention_decode(q.reshape(T, nh * hd), nh * hd, out, kc, vc, bt, cu_q, ctx, B, nh, kvh, hd, window,
-                                 1.0 / math.sqrt(hd), num_splits, scratch if n else None, err, use_tma=use_tma)
+        pairs = kernels.decode_pairs_counter(DEV) if persistent else None
+        for _ in range(2 if persistent else 1):          # twice over one counter: the kernel leaves it at zero
+            kernels.attention_decode(q.reshape(T, nh * hd), nh * hd, out, kc, vc, bt, cu_q, ctx, B, nh, kvh, hd, window,
+                                     1.0 / math.sqrt(hd), num_splits, scratch if n else None, err, use_tma=use_tma,
+                                     pairs=pairs)
+        if persistent:
+            assert pairs.tolist() == [0, 0]
     return fn
 
 
@@ -429,7 +434,7 @@ MANY_DECODE_CASES = [  # nh, kvh, hd, block_size, window, requests: more (reques
 
 @pytest.mark.parametrize("case", MANY_DECODE_CASES)
 def test_attention_decode_of_many_requests_with_persistent_blocks(case):
-    """One split and more pairs than resident blocks: persistent blocks take several pairs each, of very different
+    """One split, more pairs than resident blocks and a counter: persistent blocks take several pairs each, of very different
     lengths (one key, a page's edge, hundreds of keys), with requests that are no decoding requests among them.
     The result agrees with the plain formula and, bit for bit, with one block per pair."""
     from vllm_oxide_b200 import kernels
@@ -441,16 +446,11 @@ def test_attention_decode_of_many_requests_with_persistent_blocks(case):
     for i in range(7, n, 9):               # portions of prompts: the decode kernel leaves their rows alone
         q_lens[i] = 2
         ctx_lens[i] = max(ctx_lens[i], 2)
-    fn = decode_attention(1)
-    got, want = run_attention(fn, torch.bfloat16, nh, kvh, hd, bs, window, q_lens, ctx_lens)
+    got, want = run_attention(decode_attention(1, persistent=True), torch.bfloat16, nh, kvh, hd, bs, window, q_lens, ctx_lens)
     starts = np.cumsum([0] + q_lens)
     rows = torch.tensor([int(starts[b]) for b in range(n) if q_lens[b] == 1])
     assert torch.allclose(got[rows], want[rows], rtol=2e-2, atol=2e-2)
-    kernels.attention_decode_persistent(hd, False)
-    try:
-        per_pair, _ = run_attention(fn, torch.bfloat16, nh, kvh, hd, bs, window, q_lens, ctx_lens)
-    finally:
-        kernels.attention_decode_persistent(hd, True)
+    per_pair, _ = run_attention(decode_attention(1), torch.bfloat16, nh, kvh, hd, bs, window, q_lens, ctx_lens)
     assert torch.equal(got[rows], per_pair[rows])
 
 

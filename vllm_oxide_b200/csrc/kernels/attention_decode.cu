@@ -432,21 +432,22 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
 // pair meet in a buffer of their own (not in the ring, which is busy), between two barriers of the consumer warps alone.
 // Same tiles, same products, same order of additions as the kernel above with one split: the same bits.
 //
-// The counter: the producer takes from it only after it has waited for the kernels before this one, and a kernel is done
-// only when each of its blocks has; so no launch of an earlier step of the same stream still uses the counter then.  The
-// last block to leave sets it back to zero.  Launches of this kernel that overlap in time (two streams) would share the
-// counter and are not supported: the engine runs its steps on one stream.
+// The counter is the caller's: two words of device memory, zero before the first launch; the last block to leave sets
+// them back to zero.  Launches that may overlap in time (two streams) need counters of their own; the engine gives every
+// attention layer one.  The producer takes from it only after it has waited for the kernels before this one, and a
+// kernel is done only when each of its blocks has; so a launch of an earlier step of the same stream has left the
+// counter at zero by then.
 constexpr int DI_MERGE_FLOATS(int G) { return 2 * DEC_WARPS * 16 + DEC_WARPS * G * HD; }
 constexpr int DI_DRAW_AHEAD = 2;                          // tiles before a pair's last at which the next pair is drawn
 constexpr int DI_QUEUE = 8;                               // entries; the producer is at most DT_STAGES + 1 pairs ahead
-static __device__ unsigned vob_decode_pairs_taken[2];     // pairs given out beyond the first of each block; blocks that left
 
 __global__ void __launch_bounds__(DT_THREADS)
 attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                                   const __nv_bfloat16* q, long q_stride, __nv_bfloat16* out,
                                   const int* __restrict__ block_tables, int table_stride, const int* __restrict__ cu_q,
                                   const int* __restrict__ context_lens, int num_requests, int nh, int kvh, int block_size,
-                                  int window, float scale, long num_pages, int box_keys, int* err) {
+                                  int window, float scale, long num_pages, int box_keys, unsigned* pairs_taken, int* err) {
+  // pairs_taken[0]: pairs given out beyond the first of each block; [1]: blocks that have left
   extern __shared__ __align__(1024) char smem_raw[];
   char* smem = reinterpret_cast<char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int RING_BYTES = DT_STAGES * DT_STAGE_BYTES;
@@ -500,7 +501,7 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
 #pragma unroll
           for (int run = 0; run < 4; ++run) pg[run] = wp.page(it, run);
           if (waited && !drawn && it + DI_DRAW_AHEAD >= n_tiles) {
-            if (lane == 0) next = (int)min((unsigned)num_items, gridDim.x + atomicAdd(&vob_decode_pairs_taken[0], 1u));
+            if (lane == 0) next = (int)min((unsigned)num_items, gridDim.x + atomicAdd(&pairs_taken[0], 1u));
             drawn = true;
           }
           if (lane == 0) {
@@ -545,7 +546,7 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
       if (!ok) break;
       if (!drawn && lane == 0) {
         if (!waited) pdl_wait();
-        next = (int)min((unsigned)num_items, gridDim.x + atomicAdd(&vob_decode_pairs_taken[0], 1u));
+        next = (int)min((unsigned)num_items, gridDim.x + atomicAdd(&pairs_taken[0], 1u));
       }
       waited = true;
       item = __shfl_sync(0xffffffffu, next, 0);
@@ -672,9 +673,9 @@ attention_decode_tma_items_kernel(const __grid_constant__ CUtensorMap tmK, const
   __syncthreads();
   if (threadIdx.x == 0) {                             // the last block to leave makes the counter ready for the next launch
     __threadfence();
-    if (atomicAdd(&vob_decode_pairs_taken[1], 1u) == gridDim.x - 1) {
-      vob_decode_pairs_taken[0] = 0;
-      vob_decode_pairs_taken[1] = 0;
+    if (atomicAdd(&pairs_taken[1], 1u) == gridDim.x - 1) {
+      pairs_taken[0] = 0;
+      pairs_taken[1] = 0;
       __threadfence();
     }
   }
@@ -720,10 +721,6 @@ VOB_API long vob_attention_decode_scratch_floats(int num_requests, int nh, int n
   return num_splits > 1 ? (long)num_requests * nh * num_splits * (HD + 1) : 0;
 }
 
-static bool g_decode_items = true;
-// One split and more (request, kv head) pairs than resident blocks: persistent blocks (default) or a block a pair.
-VOB_API void vob_attention_decode_persistent(int on) { g_decode_items = on != 0; }
-
 static bool g_decode_cluster_merge = true;
 // Up to 8 splits merge through a thread-block cluster (default) or through scratch memory and a second kernel.
 VOB_API void vob_attention_decode_cluster_merge(int on) { g_decode_cluster_merge = on != 0; }
@@ -732,7 +729,7 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
                                    const void* kcache, const void* vcache, const int* block_tables, int table_stride,
                                    const int* cu_q, const int* context_lens, int num_requests, int nh, int kvh,
                                    int block_size, int window, float scale, long num_pages, int num_splits, float* scratch,
-                                   int* err, cudaStream_t stream) {
+                                   unsigned* pairs_counter, int* err, cudaStream_t stream) {
   if (num_requests <= 0) return 0;
   if (kvh <= 0 || nh % kvh || nh / kvh > 16 || block_size <= 0 || num_splits < 1 || num_splits > 65535) return VOB_UNSUPPORTED;
   static bool configured = false;
@@ -760,7 +757,7 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
     }
     const int box_keys = block_size % DEC_TILE == 0 ? DEC_TILE : RUN_KEYS;
     // one split and more (request, kv head) pairs than blocks fit the GPU: persistent blocks, the producer ahead across pairs
-    if (num_splits == 1 && g_decode_items) {
+    if (num_splits == 1 && pairs_counter) {
       const int G = nh / kvh;
       const int items_smem = 1024 + DT_STAGES * DT_STAGE_BYTES + DI_MERGE_FLOATS(G) * 4 + DI_QUEUE * 16 + 2 * DT_STAGES * 8 + 32;
       static int resident_of[17] = {0};      // blocks that fit the GPU at once, by heads per kv head (0: not asked yet)
@@ -780,7 +777,7 @@ static int attention_decode_launch(const void* map_k, const void* map_v, const v
         return launch_kernel(attention_decode_tma_items_kernel, dim3(resident_of[G]), DT_THREADS, items_smem, stream,
                              *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, (const __nv_bfloat16*)q, q_stride,
                              (__nv_bfloat16*)out, block_tables, table_stride, cu_q, context_lens, num_requests, nh, kvh,
-                             block_size, window, scale, num_pages, box_keys, err);
+                             block_size, window, scale, num_pages, box_keys, pairs_counter, err);
     }
     // up to 8 splits: the blocks of a (request, kv head) are a cluster and merge through shared memory
     if (num_splits > 1 && num_splits <= 8 && g_decode_cluster_merge)
@@ -816,20 +813,23 @@ VOB_API int vob_attention_decode(const void* q, long q_stride, void* out, const 
                                  long num_pages, int num_splits, float* scratch, int* err, cudaStream_t stream) {
   return attention_decode_launch(nullptr, nullptr, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
                                  context_lens, num_requests, nh, kvh, block_size, window, scale, num_pages, num_splits,
-                                 scratch, err, stream);
+                                 scratch, nullptr, err, stream);
 }
 
 // The same with the caches also given as tensor maps (vob_tensor_map_bf16_sliced over [pages*kvh*block_size, HD] with
 // boxes of vob_attention_decode_box_keys(block_size) rows and vob_attention_decode_box_slices(block_size) slices): head
 // sizes that are a multiple of 64 then bring keys and values in by TMA.  Null maps fall back to cp.async.
+// pairs_counter (may be null): two words of device memory, zero before the first call and left at zero by every call,
+// not shared with a call that may run at the same time.  With it, one split and more (request, kv head) pairs than
+// blocks fit the GPU run as persistent blocks that draw their pairs from it; without it, as one block per pair.
 VOB_API int vob_attention_decode_tma(const void* map_k, const void* map_v, const void* q, long q_stride, void* out,
                                      const void* kcache, const void* vcache, const int* block_tables, int table_stride,
                                      const int* cu_q, const int* context_lens, int num_requests, int nh, int kvh,
                                      int block_size, int window, float scale, long num_pages, int num_splits,
-                                     float* scratch, int* err, cudaStream_t stream) {
+                                     float* scratch, unsigned* pairs_counter, int* err, cudaStream_t stream) {
   return attention_decode_launch(map_k, map_v, q, q_stride, out, kcache, vcache, block_tables, table_stride, cu_q,
                                  context_lens, num_requests, nh, kvh, block_size, window, scale, num_pages, num_splits,
-                                 scratch, err, stream);
+                                 scratch, pairs_counter, err, stream);
 }
 
 VOB_API int vob_attention_decode_has_tma() { return VOB_HD % 64 == 0 ? 1 : 0; }

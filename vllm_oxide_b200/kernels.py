@@ -215,16 +215,14 @@ def attention_decode_scratch_floats(head_dim: int, num_requests: int, nh: int, n
     return int(attention_lib(head_dim).vob_attention_decode_scratch_floats(num_requests, nh, num_splits))
 
 
-def attention_decode_persistent(head_dim: int, on: bool) -> None:
-    """With one split and more (request, kv head) pairs than blocks fit the GPU, the TMA decode kernel runs as
-    persistent blocks whose producer works ahead across pairs (default); off: one block per pair.  Same bits."""
-    attention_lib(head_dim).vob_attention_decode_persistent(1 if on else 0)
-
-
 def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, nh, kvh, hd,
-                     window: int, scale: float, num_splits: int, scratch, err, use_tma: bool = True) -> None:
-    """Requests that bring exactly one token; the others are skipped."""
-    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, scratch)
+                     window: int, scale: float, num_splits: int, scratch, err, use_tma: bool = True, pairs=None) -> None:
+    """Requests that bring exactly one token; the others are skipped.  `pairs`: two int32 zeros on the device that belong
+    to this caller (`decode_pairs_counter`); with it, one split and more (request, kv head) pairs than blocks fit the GPU
+    run as persistent blocks that draw their pairs from it (the kernel leaves it at zero), without it as one block per
+    pair.  Same bits either way."""
+    _cuda(q, out, kcache, vcache, block_tables, cu_q, context_lens, scratch, pairs)
+    assert pairs is None or (pairs.dtype == torch.int32 and pairs.numel() >= 2)
     assert q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
     L = attention_lib(hd)
     if use_tma and L.vob_attention_decode_has_tma() and kcache.is_contiguous() and vcache.is_contiguous():
@@ -235,13 +233,19 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_tables, cu_q, conte
         _check(L.vob_attention_decode_tma(
             map_k, map_v, _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables),
             block_tables.shape[-1], _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[2], window,
-            ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(err), _stream()),
+            ctypes.c_float(scale), ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(pairs), _p(err), _stream()),
             "attention_decode_tma")
         return
     _check(L.vob_attention_decode(
         _p(q), ctypes.c_long(q_stride), _p(out), _p(kcache), _p(vcache), _p(block_tables), block_tables.shape[-1],
         _p(cu_q), _p(context_lens), num_requests, nh, kvh, kcache.shape[2], window, ctypes.c_float(scale),
         ctypes.c_long(kcache.shape[0]), num_splits, _p(scratch), _p(err), _stream()), "attention_decode")
+
+
+def decode_pairs_counter(device) -> torch.Tensor:
+    """The counter that `attention_decode(pairs=...)` draws (request, kv head) pairs from: one per caller whose launches
+    do not overlap in time (the engine keeps one per attention layer)."""
+    return torch.zeros(2, dtype=torch.int32, device=device)
 
 
 def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, context_lens, num_requests, max_q, nh, kvh,

@@ -42,6 +42,7 @@ class Attention(Mixer):
         self.prefix, self.dtype, self.device = prefix, dtype, device
         self.scale = 1.0 / math.sqrt(head_dim)   # qwen3.rs:204
         self.wqkv = self.wo = self.bqkv = self.wq_norm = self.wk_norm = None
+        self._pairs = None      # this layer's counter for decode attention of many requests (made with the weights)
 
     # ---- tensors
     def _names(self):
@@ -75,6 +76,9 @@ class Attention(Mixer):
         if self.qk_norm:
             self.wq_norm = tensors[n["q_norm.weight"]].contiguous()
             self.wk_norm = tensors[n["k_norm.weight"]].contiguous()
+        if self.wo.is_cuda:
+            # a counter of this layer's own, so that no two launches that could overlap ever share one
+            self._pairs = kernels.decode_pairs_counter(self.wo.device)
 
     def cache_spec(self) -> CacheSpec:
         return CacheSpec(self.kvh, self.hd, self.window)
@@ -145,7 +149,7 @@ class Attention(Mixer):
             n = kernels.attention_decode_scratch_floats(self.hd, B, self.nh, splits)
             scratch = ctx.ws.get_flat("attention_decode_scratch", n, torch.float32) if n else None
             kernels.attention_decode(qkv, q_stride, out, cache.k, cache.v, tables, ctx.cu_q, ctx.context_lens, B, self.nh,
-                                     self.kvh, self.hd, self.window, self.scale, splits, scratch, ctx.err)
+                                     self.kvh, self.hd, self.window, self.scale, splits, scratch, ctx.err, pairs=self._pairs)
         if ctx.max_q > 1:
             kernels.attention_prefill(qkv, q_stride, out, cache.k, cache.v, tables, ctx.cu_q, ctx.context_lens, B,
                                       ctx.max_q, self.nh, self.kvh, self.hd, self.window, self.scale, ctx.err)

@@ -2,7 +2,8 @@
 // 64 and 128: S = Q K^T and O = P V are tcgen05.mma products with S and O in tensor memory.
 //
 // A block takes NQ tiles of 128 query rows (a row is a (token, head of the group) pair, so the heads that share a
-// key/value head share every key and value brought in) and walks the keys in steps of 64:
+// key/value head share every key and value brought in; a tile holds whole tokens, 128 / group of them, and leaves the
+// rows that remain, two of 128 with three heads a group, as zeros) and walks the keys in steps of 64:
 //   warps 0 .. 4NQ-1   softmax: warp w of a tile owns rows 32(w%4) .. +31 of it, a thread owns ONE row: it reads the
 //                      row's 64 scores from tensor memory (tcgen05.ld), masks, takes the maximum and the sum without
 //                      any exchange between threads, writes P in bfloat16 back to tensor memory over the scores (the A
@@ -12,8 +13,8 @@
 //                      second step on the exponentials are taken against the old reference maximum beside the search
 //                      for the new one, and taken again only if it had to move;
 //   warp 4NQ           producer: brings the query tiles in (TMA: the tensor map sees q as head size x heads x tokens, a
-//                      box is 64 columns of a group's heads for 128 / group tokens and lands as the tile's rows; where
-//                      the group does not divide 128 the softmax warps bring them by cp.async instead),
+//                      box is 64 columns of a group's heads for a tile's tokens and lands as the tile's rows; for a
+//                      caller without that map the softmax warps bring them by cp.async instead),
 //                      looks the pages up a chunk ahead and brings K and V tiles in by TMA into a ring of
 //                      stages (the K tile is the K-major B operand of the first product as it lands, the V tile the
 //                      MN-major B operand of the second one: no transposition anywhere);
@@ -95,15 +96,16 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   const int t0 = cu_q[b];
   const int n = cu_q[b + 1] - t0;
   const int G = nh / kvh;
-  const int total_rows = n * G;
-  // later row blocks see more keys: they go first, so that the short ones fill the end of the grid
-  const int row0 = (int)(gridDim.x / kvh - 1 - blockIdx.x / kvh) * NQ * F5_ROWS;
-  if (n <= 1 || row0 >= total_rows) { pdl_wait(); return; }       // a decoding request, or nothing left (uniform)
+  // A tile holds whole tokens: TT of them, TR = TT * G rows (126 of the 128 with three heads a group; the rows that are
+  // left are zeros that nobody reads).  So a tile never ends inside a token, and one box of a tensor map is a tile.
+  const int TT = F5_ROWS / G, TR = TT * G;
+  // later blocks of tokens see more keys: they go first, so that the short ones fill the end of the grid
+  const int tok_base = (int)(gridDim.x / kvh - 1 - blockIdx.x / kvh) * NQ * TT;
+  if (n <= 1 || tok_base >= n) { pdl_wait(); return; }             // a decoding request, or nothing left (uniform)
   const int ctx = context_lens[b];
   const int first_pos = ctx - n;
   const int* table = block_tables + (size_t)b * table_stride;
-  const int last_row = min(row0 + NQ * F5_ROWS, total_rows) - 1;
-  const int blk_pos_lo = first_pos + row0 / G, blk_pos_hi = first_pos + last_row / G;
+  const int blk_pos_lo = first_pos + tok_base, blk_pos_hi = first_pos + min(tok_base + NQ * TT, n) - 1;
   const int key_lo = window > 0 ? max(0, blk_pos_lo - window + 1) : 0;
   const int key_end = blk_pos_hi + 1;
   const int start = key_lo / F5_TILE * F5_TILE;
@@ -112,10 +114,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   int jlo[NQ], jhi[NQ];
 #pragma unroll
   for (int qt = 0; qt < NQ; ++qt) {
-    const int r_first = row0 + qt * F5_ROWS;
-    if (r_first >= total_rows) { jlo[qt] = jhi[qt] = 0; continue; }
-    const int r_last = min(r_first + F5_ROWS, total_rows) - 1;
-    const int pos_lo = first_pos + r_first / G, pos_hi = first_pos + r_last / G;
+    const int tok_first = tok_base + qt * TT;
+    if (tok_first >= n) { jlo[qt] = jhi[qt] = 0; continue; }
+    const int pos_lo = first_pos + tok_first, pos_hi = first_pos + min(tok_first + TT, n) - 1;
     const int klo = window > 0 ? max(0, pos_lo - window + 1) : 0;
     jlo[qt] = (klo - start) / F5_TILE;
     jhi[qt] = (pos_hi - start) / F5_TILE + 1;
@@ -142,6 +143,15 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   uint32_t tmem_base = 0;
   if (warp != 4 * NQ) {
     if (warp == 4 * NQ + 1) t5_alloc(tmem_slot, C::TMEM_COLS);
+    if (warp < 4 * NQ && TR < F5_ROWS) {
+      // the rows of a tile that hold no token: zeros (finite scores that nobody reads)
+      const int qt = warp >> 2, tid = threadIdx.x & 127;
+      for (int idx = tid; idx < F5_SLICES * (F5_ROWS - TR) * 8; idx += 128) {
+        const int c = idx / ((F5_ROWS - TR) * 8), rest = idx % ((F5_ROWS - TR) * 8);
+        *reinterpret_cast<uint4*>(q_s + qt * F5_Q_BYTES + c * (F5_ROWS * 128) + (TR + rest / 8) * 128 + (rest % 8) * 16) =
+            make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
     if (warp < 4 * NQ && !q_by_tma) {
       // the query tile of this warp group into shared memory, rows of 128 bytes per slice, 128-byte swizzled; every
       // copy is on its way before the first one is waited for (cp.async moves 16 bytes a clock: 4,000 cycles for two
@@ -150,11 +160,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       char* dst = q_s + qt * F5_Q_BYTES;
       constexpr int CHUNKS = HD / 8;
 #pragma unroll 4
-      for (int idx = tid; idx < F5_ROWS * CHUNKS; idx += 128) {
+      for (int idx = tid; idx < TR * CHUNKS; idx += 128) {
         const int r = idx / CHUNKS, chunk = idx % CHUNKS;
-        const int row = row0 + qt * F5_ROWS + r;
-        const bool there = row < total_rows;
-        const __nv_bfloat16* src = there ? q + (size_t)(t0 + row / G) * q_stride + (size_t)(kh * G + row % G) * HD + chunk * 8 : q;
+        const int tok = tok_base + qt * TT + r / G;
+        const bool there = tok < n;
+        const __nv_bfloat16* src = there ? q + (size_t)(t0 + tok) * q_stride + (size_t)(kh * G + r % G) * HD + chunk * 8 : q;
         cp_async16(dst + (chunk >> 3) * (F5_ROWS * 128) + swizzled_offset(r, chunk & 7), src, there);
       }
       cp_async_commit();
@@ -171,15 +181,15 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     // ------------------------------------------------ producer: lane 0 issues, all lanes look pages up
     if (q_by_tma && lane == 0) {
       // The query tiles by the copy engine: the tensor map sees q as (head size, heads, tokens), a box is 64 columns of
-      // the G heads of a kv head for 128 / G tokens, which lands as 128 rows of 128 bytes in the order (token, head of
-      // the group): the tile's rows.  Tokens past the step's last read as zeros; rows past the request's are masked.
+      // the G heads of a kv head for TT tokens, which lands as TR rows of 128 bytes in the order (token, head of the
+      // group): the tile's rows.  Tokens past the step's last read as zeros; rows past the request's are masked.
 #pragma unroll
       for (int qt = 0; qt < NQ; ++qt) {
         if (jhi[qt] > jlo[qt]) {
-          mbar_expect_tx(&q_full[qt], (unsigned)F5_Q_BYTES);
+          mbar_expect_tx(&q_full[qt], (unsigned)(F5_SLICES * TR * 128));
 #pragma unroll
           for (int c = 0; c < F5_SLICES; ++c)
-            tma_load_3d(q_s + qt * F5_Q_BYTES + c * (F5_ROWS * 128), &tmQ, c * 64, kh * G, t0 + (row0 + qt * F5_ROWS) / G, &q_full[qt]);
+            tma_load_3d(q_s + qt * F5_Q_BYTES + c * (F5_ROWS * 128), &tmQ, c * 64, kh * G, t0 + tok_base + qt * TT, &q_full[qt]);
         }
       }
     }
@@ -307,13 +317,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
     // ------------------------------------------------ softmax: a thread owns a row
     const int qt = warp >> 2;
     const int r = (warp & 3) * 32 + lane;                   // row of the tile = lane of tensor memory
-    const int row = row0 + qt * F5_ROWS + r;
-    const bool valid = row < total_rows;
-    const int tok = valid ? row / G : 0, head = kh * G + (valid ? row % G : 0);
+    const int tok_first = tok_base + qt * TT;                // the tile's first token
+    const bool valid = r < TR && tok_first + r / G < n;
+    const int tok = valid ? tok_first + r / G : 0, head = kh * G + (valid ? r % G : 0);
     const int rpos = first_pos + tok;
-    const int r_first = row0 + qt * F5_ROWS, r_last = min(r_first + F5_ROWS, total_rows) - 1;
-    const int t_pos_lo = first_pos + r_first / G, t_pos_hi = first_pos + r_last / G;
-    const bool all_rows = r_first + F5_ROWS <= total_rows;
+    const int t_pos_lo = first_pos + tok_first, t_pos_hi = first_pos + min(tok_first + TT, n) - 1;
+    const bool all_rows = tok_first + TT <= n;               // every token of the tile is the request's
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + qt * C::TILE_COLS;
     const float sc = scale * LOG2E;
     float m_ref = -INFINITY, l = 0.f;
@@ -328,6 +337,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
       const int k0 = start + j * F5_TILE;
       // mask only where the step touches the diagonal, the window's edge or missing rows
       const bool need_mask = !all_rows || k0 + F5_TILE - 1 > t_pos_lo || (window > 0 && k0 < t_pos_hi - window + 1);
+      // (the rows past TR of a whole tile hold zeros: their scores are finite and go nowhere)
       float s[64];
       // the row's 64 scores of this step from tensor memory, masked
       auto load_scores = [&]() {
@@ -458,7 +468,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
           if ((warp & 3) == 0 && lane == 0) {
 #pragma unroll
             for (int c = 0; c < F5_SLICES; ++c)
-              tma_store_3d(&tmO, stage + c * (F5_ROWS * 128), c * 64, kh * G, t0 + r_first / G);
+              tma_store_3d(&tmO, stage + c * (F5_ROWS * 128), c * 64, kh * G, t0 + tok_first);
             tma_store_commit();
             tma_store_wait_read();
           }
@@ -495,13 +505,13 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
 
 using namespace vob;
 
-// Heads in a box of the query's tensor map (vob_tensor_map_bf16_heads with boxes of this many heads and 128 / this many
-// tokens), or 0 if the query tiles of these head counts cannot come by TMA (the group must divide 128 rows).
+// Heads in a box of the query's and the output's tensor maps (vob_tensor_map_bf16_heads with boxes of this many heads and
+// 128 / this many tokens, rounded down: a tile holds whole tokens), or 0 if this kernel does not take these head counts.
 VOB_API int vob_attention_prefill_q_box_heads(int nh, int kvh) {
 #if VOB_HD == 64 || VOB_HD == 128
   if (kvh <= 0 || nh % kvh) return 0;
   const int G = nh / kvh;
-  return F5_ROWS % G == 0 ? G : 0;
+  return G <= F5_ROWS ? G : 0;
 #else
   return 0;
 #endif
@@ -528,9 +538,10 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
   if (kvh <= 0 || nh % kvh || block_size <= 0 || block_size % 16 || kvh > 65535 || num_requests > 65535 ||
       (query_tiles != 1 && query_tiles != 2) || !(scale > 0.f))   // the kernel takes maxima before it scales
     return VOB_UNSUPPORTED;
-  const long rows = (long)max_q * (nh / kvh);
+  if (nh / kvh > F5_ROWS) return VOB_UNSUPPORTED;
+  const long tiles = ((long)max_q + F5_ROWS / (nh / kvh) - 1) / (F5_ROWS / (nh / kvh));   // tiles of whole tokens
   const int box_keys = block_size % F5_TILE == 0 ? F5_TILE : RUN_KEYS;
-  // the query tiles come by TMA when a map was given and the heads of a group divide a tile's rows
+  // the query tiles come by TMA when a map was given
   const int q_by_tma = map_q != nullptr && vob_attention_prefill_q_box_heads(nh, kvh) > 0;
   const int o_by_tma = map_o != nullptr && vob_attention_prefill_q_box_heads(nh, kvh) > 0;   // whole output tiles leave the same way
   static bool configured[2] = {false, false};
@@ -540,7 +551,7 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
       if (e != cudaSuccess) return (int)e;
       configured[0] = true;
     }
-    dim3 grid((unsigned)((rows + F5_ROWS - 1) / F5_ROWS) * kvh, 1, num_requests);
+    dim3 grid((unsigned)tiles * kvh, 1, num_requests);
     return launch_kernel(attention_prefill_tc5_kernel<1>, grid, F5<1>::THREADS, F5<1>::SMEM_BYTES, stream,
                          *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, *(const CUtensorMap*)(q_by_tma ? map_q : map_k), q_by_tma,
                          *(const CUtensorMap*)(o_by_tma ? map_o : map_k), o_by_tma,
@@ -553,7 +564,7 @@ VOB_API int vob_attention_prefill_tc5(const void* map_k, const void* map_v, cons
     if (e != cudaSuccess) return (int)e;
     configured[1] = true;
   }
-  dim3 grid((unsigned)((rows + 2 * F5_ROWS - 1) / (2 * F5_ROWS)) * kvh, 1, num_requests);
+  dim3 grid((unsigned)((tiles + 1) / 2) * kvh, 1, num_requests);
   return launch_kernel(attention_prefill_tc5_kernel<2>, grid, F5<2>::THREADS, F5<2>::SMEM_BYTES, stream,
                        *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, *(const CUtensorMap*)(q_by_tma ? map_q : map_k), q_by_tma,
                          *(const CUtensorMap*)(o_by_tma ? map_o : map_k), o_by_tma,

@@ -263,7 +263,7 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_tables, cu_q, cont
         keys, slices = L.vob_attention_decode_box_keys(bs), L.vob_attention_decode_box_slices(bs)
         map_k, map_v = tensor_map(kcache.view(-1, hd), keys, slices), tensor_map(vcache.view(-1, hd), keys, slices)
         if use_tc5 and L.vob_attention_prefill_has_tc5() and q_stride % 8 == 0:
-            # the query tiles come by TMA too where the heads of a group divide a tile's 128 rows
+            # the query tiles come and whole output tiles leave by TMA too (a tile holds whole tokens: 128 // group of them)
             box_heads = L.vob_attention_prefill_q_box_heads(nh, kvh) if tiles_by_tma else 0
             map_q = tensor_map_heads(q, q_stride, nh, hd, box_heads, 128 // box_heads) if box_heads > 0 else None
             map_o = (tensor_map_heads(out, nh * hd, nh, hd, box_heads, 128 // box_heads)

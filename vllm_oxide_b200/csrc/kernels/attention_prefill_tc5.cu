@@ -59,7 +59,7 @@ template <int NQ> struct F5 {
   static constexpr int TILE_COLS = 2 * F5_TILE + HD;       // tensor-memory columns of a query tile: S, S, O
   static constexpr int TMEM_COLS = NQ * TILE_COLS <= 256 ? 256 : 512;
   static constexpr int DATA_BYTES = NQ * F5_Q_BYTES + STAGES * F5_STAGE_BYTES;
-  static constexpr int NUM_BARRIERS = 2 * STAGES + 7 * NQ + 1;
+  static constexpr int NUM_BARRIERS = 2 * STAGES + 8 * NQ + 1;
   static constexpr int SMEM_BYTES = 1024 + DATA_BYTES + NUM_BARRIERS * 8 + 16;
 };
 
@@ -86,7 +86,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   uint64_t* o_final = o_done + NQ;                          // [NQ] O holds the last step's contribution (one phase)
   uint64_t* drained = o_final + NQ;                         // every product issued has completed
   uint64_t* q_full = drained + 1;                           // [NQ] the query tile has landed (when TMA brings it)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + NQ);
+  uint64_t* o_staged = q_full + NQ;                         // [NQ] the tile's four warps have put their rows of O in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_staged + NQ);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   pdl_launch_dependents();
@@ -129,7 +130,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
   if (threadIdx.x == 0) {
     for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], NQ); }
     for (int i = 0; i < 2 * NQ; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); }
-    for (int i = 0; i < NQ; ++i) { mbar_init(&o_done[i], 1); mbar_init(&o_final[i], 1); mbar_init(&q_full[i], 1); }
+    for (int i = 0; i < NQ; ++i) {
+      mbar_init(&o_done[i], 1); mbar_init(&o_final[i], 1); mbar_init(&q_full[i], 1); mbar_init(&o_staged[i], 4);
+    }
     mbar_init(drained, NQ);
     *abort_flag = 0;
     tma_prefetch_map(&tmK);
@@ -462,10 +465,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tmK, const __gr
               *reinterpret_cast<uint4*>(stage + (c0 >> 6) * (F5_ROWS * 128) + swizzled_offset(r, c >> 3)) = v;
             }
           }
+          // the tile's four warps meet on an mbarrier, not on a block barrier: a warp that gave up above never comes,
+          // and then the wait runs out (bounded, like every wait here) instead of holding the others for ever
           asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-          if (qt == 0) asm volatile("bar.sync 2, 128;\n" ::: "memory");          // the tile's four warps
-          else asm volatile("bar.sync 3, 128;\n" ::: "memory");
-          if ((warp & 3) == 0 && lane == 0) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&o_staged[qt]);
+          if ((warp & 3) == 0 && lane == 0 && mbar_wait(&o_staged[qt], 0u, abort_flag, err)) {
 #pragma unroll
             for (int c = 0; c < F5_SLICES; ++c)
               tma_store_3d(&tmO, stage + c * (F5_ROWS * 128), c * 64, kh * G, t0 + tok_first);

@@ -136,6 +136,10 @@ __global__ void __launch_bounds__(NT) add_rmsnorm_kernel(const T* x, T* residual
     }
     const float total = block_sum<NT>(ss, scratch);
     const float denom = sqrtf(total / (float)H + eps);
+    // 16-bit types: x * (1 / rms) for x / rms, at most one float unit away before the rounding to 16 bits (a float
+    // division is ten instructions an element: the kernel was bound by them, 9.1 us for 2,048 rows of 4,096 against
+    // 6.2 so); the 32-bit path divides
+    const float inv = 1.f / denom;
 #pragma unroll
     for (int it = 0; it < IT; ++it) {
       const int i = (threadIdx.x + it * NT) * N;
@@ -144,7 +148,7 @@ __global__ void __launch_bounds__(NT) add_rmsnorm_kernel(const T* x, T* residual
 #pragma unroll
         for (int j = 0; j < N; j += 4) *reinterpret_cast<float4*>(wv + j) = *reinterpret_cast<const float4*>(w + i + j);
 #pragma unroll
-        for (int j = 0; j < N; ++j) o[j] = round_to<T>(v[it][j] / denom) * wv[j];
+        for (int j = 0; j < N; ++j) o[j] = round_to<T>(sizeof(T) == 2 ? v[it][j] * inv : v[it][j] / denom) * wv[j];
         store16<T>(yr + i, o);
       }
     }
@@ -176,16 +180,18 @@ __global__ void __launch_bounds__(NT) add_rmsnorm_kernel(const T* x, T* residual
   }
   const float total = block_sum<NT>(ss, scratch);
   const float denom = sqrtf(total / (float)H + eps);
+  const float inv = 1.f / denom;                  // as above: 16-bit types multiply, the 32-bit path divides
   if (VEC) {
     constexpr int N = Vec16<T>::N;
     for (int i = threadIdx.x * N; i < H; i += NT * N) {
       float o[N];
 #pragma unroll
-      for (int j = 0; j < N; ++j) o[j] = round_to<T>(srow[i + j] / denom) * w[i + j];
+      for (int j = 0; j < N; ++j) o[j] = round_to<T>(sizeof(T) == 2 ? srow[i + j] * inv : srow[i + j] / denom) * w[i + j];
       store16<T>(yr + i, o);
     }
   } else {
-    for (int i = threadIdx.x; i < H; i += NT) yr[i] = from_f<T>(round_to<T>(srow[i] / denom) * w[i]);
+    for (int i = threadIdx.x; i < H; i += NT)
+      yr[i] = from_f<T>(round_to<T>(sizeof(T) == 2 ? srow[i] * inv : srow[i] / denom) * w[i]);
   }
 }
 

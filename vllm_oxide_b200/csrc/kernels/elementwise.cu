@@ -208,7 +208,8 @@ __global__ void silu_mul_kernel(const T* gu, T* out, int I, size_t total, int in
     const size_t groups = total / N;
     const int per_row = I / N;
     for (size_t gidx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; gidx < groups; gidx += (size_t)gridDim.x * blockDim.x) {
-      const size_t t = gidx / per_row;
+      // (a 64-bit division is some forty instructions; the groups of nearly every step fit 32 bits)
+      const size_t t = groups <= 0xffffffffull ? (size_t)((unsigned)gidx / (unsigned)per_row) : gidx / per_row;
       const int i = (int)(gidx - t * per_row) * N;
       const T* row = gu + t * 2 * I;
       const T* gp = row + (interleaved ? 2 * i : i);
